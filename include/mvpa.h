@@ -1,0 +1,118 @@
+/*
+ * mvpa.h — C ABI of the B200 multi-variate parallel attention (Flash-MVPA) library.
+ *
+ * The library replaces the device side of the reference operator
+ * `attentions.flashmvpa` (`attentions/attn.py:1317-1366`): its Triton forward
+ * kernel (`attentions/attn.py:38-347`), the materialised relative-score
+ * matrices of `_rel_bias` (`attentions/attn.py:1305-1314`), its Triton backward
+ * kernels (`attentions/attn.py:350-1010`) and the autograd that runs through
+ * `_rel_bias` afterwards.  Every entry point takes plain device pointers, sizes
+ * and a CUDA stream; the caller owns every buffer, including the workspace.
+ * Nothing here allocates device memory, synchronises the device or keeps
+ * state between calls (except where an entry point says otherwise).
+ *
+ * Token order is time-major: token n = t*C + c, N = T*C.
+ *
+ *   S[i,k] = sm_scale * ( win(i,k) * (q_i+u).K_k
+ *                         + (q_i+vt).r_time[T-1-(t_i-t_k)]
+ *                         + (q_i+z).r_chan[C-1-|c_i-c_k|] ),   -inf where t_k > t_i
+ *   win    = window <= 0  or  |t_i-t_k| <= window  or  t_i == T-1
+ *   O      = softmax_k(S) V ;  lse[i] = log2( sum_k 2^(S[i,k]*log2 e) )
+ *
+ * Return value: MVPA_OK (0) or a negative MVPA_ERR_* code; the text of the last
+ * error on the calling thread is returned by mvpa_last_error_string().
+ */
+#ifndef MVPA_H_
+#define MVPA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MVPA_OK 0
+#define MVPA_ERR_SHAPE (-1)       /* a size is zero/negative, H % Hkv != 0, unsupported D */
+#define MVPA_ERR_DTYPE (-2)       /* unknown element type */
+#define MVPA_ERR_ALIGNMENT (-3)   /* a pointer or stride breaks the 16-byte rule */
+#define MVPA_ERR_WORKSPACE (-4)   /* workspace missing or smaller than *_workspace_bytes() */
+#define MVPA_ERR_CUDA (-5)        /* a CUDA runtime / driver call failed */
+#define MVPA_ERR_UNSUPPORTED (-6) /* shape outside what the selected kernel handles */
+#define MVPA_ERR_DEVICE (-7)      /* a kernel reported a non-zero status word (bounded wait ran out) */
+
+/* Element type of q, k, v, u, vt, z, r_time, r_chan, o, dO, dq, dk, dv. */
+#define MVPA_F32 0  /* fp32 I/O, fp32 arithmetic on CUDA cores                      */
+#define MVPA_BF16 1 /* bf16 I/O, tcgen05 tensor cores with fp32 accumulation in TMEM */
+
+/* Problem description.  Mirrors the constexpr arguments of the reference launch
+ * (`attentions/attn.py:1103-1120`: Z, H_Q, H_KV, N_CTX, TIME_CTX, CHANNEL_CTX,
+ * WINDOW_SIZE, BLOCK_DMODEL) plus sm_scale. */
+typedef struct mvpa_problem {
+  int32_t B;      /* batch                                                        */
+  int32_t H;      /* query heads                                                  */
+  int32_t Hkv;    /* key/value heads, H % Hkv == 0                                */
+  int32_t T;      /* time segments  (rows of r_time)                              */
+  int32_t C;      /* channels       (rows of r_chan)                              */
+  int32_t D;      /* head dim: 16, 32, 64 or 128 (`attentions/attn.py:1043`)      */
+  int32_t window; /* content-window half width in time steps; <= 0: no window     */
+  int32_t dtype;  /* MVPA_F32 or MVPA_BF16                                        */
+  float sm_scale; /* applied to the sum of the three score terms                  */
+  int32_t flags;  /* reserved, must be 0                                          */
+} mvpa_problem;
+
+/* A (batch, head, token, D) tensor with D contiguous; strides in elements.
+ * The reference passes contiguous (B,H,N,D) tensors (`layers/mvpa.py:382-397`);
+ * strides let a caller hand over the projection output without a permute copy. */
+typedef struct mvpa_tensor {
+  void* ptr;
+  int64_t stride_b, stride_h, stride_n;
+} mvpa_tensor;
+
+/* Bytes of caller-owned scratch mvpa_fwd / mvpa_bwd need for this problem (may be 0). */
+size_t mvpa_fwd_workspace_bytes(const mvpa_problem* p);
+size_t mvpa_bwd_workspace_bytes(const mvpa_problem* p);
+
+/*
+ * Forward.  Replaces `_rel_bias` + `FlashMVPA.forward` + `_fwd_kernel`
+ * (`attentions/attn.py:1305-1314, 1013-1138, 38-347`).
+ *   q (B,H,N,D); k, v (B,Hkv,N,D); u, vt, z (Hkv,D) contiguous;
+ *   r_time (Hkv,T,D), r_chan (Hkv,C,D) contiguous; o (B,H,N,D);
+ *   lse (B*H, N) fp32, may be NULL when no backward will follow.
+ */
+int mvpa_fwd(const mvpa_problem* p, const mvpa_tensor* q, const mvpa_tensor* k,
+             const mvpa_tensor* v, const void* u, const void* vt, const void* z,
+             const void* r_time, const void* r_chan, const mvpa_tensor* o, float* lse,
+             void* workspace, size_t workspace_bytes, void* cuda_stream);
+
+/*
+ * Backward.  Replaces `FlashMVPA.backward` + `_bwd_kernel`
+ * (`attentions/attn.py:1140-1302, 776-1010, 350-773`) and the autograd through
+ * `_rel_bias` that follows it (`attentions/attn.py:1305-1314`).
+ *   o, lse: outputs of mvpa_fwd;  d_o (B,H,N,D) upstream gradient.
+ *   dq (B,H,N,D), dk, dv (B,Hkv,N,D) in the element type of the inputs;
+ *   du, dvt, dz (Hkv,D), dr_time (Hkv,T,D), dr_chan (Hkv,C,D) fp32, overwritten.
+ */
+int mvpa_bwd(const mvpa_problem* p, const mvpa_tensor* q, const mvpa_tensor* k,
+             const mvpa_tensor* v, const void* u, const void* vt, const void* z,
+             const void* r_time, const void* r_chan, const mvpa_tensor* o, const float* lse,
+             const mvpa_tensor* d_o, const mvpa_tensor* dq, const mvpa_tensor* dk,
+             const mvpa_tensor* dv, float* du, float* dvt, float* dz, float* dr_time,
+             float* dr_chan, void* workspace, size_t workspace_bytes, void* cuda_stream);
+
+/* Text of the last error raised on this host thread ("" if none).
+ * Stands where the reference raises RuntimeError / assert
+ * (`attentions/attn.py:1034-1045, 1339, 1344`). */
+const char* mvpa_last_error_string(void);
+
+/* Number of kernels this library has launched on the calling process so far
+ * (all threads); bench harnesses use the difference around a timed region. */
+uint64_t mvpa_launch_count(void);
+
+/* Library ABI version (bumped when a signature above changes). */
+int mvpa_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MVPA_H_ */

@@ -1,0 +1,129 @@
+"""`flash_mvpa` — drop-in for the reference operator of the same name
+(`attentions/attn.py:1317-1366`), backed by the sm_100a CUDA library.
+
+Same signature and argument meaning as the reference.  What differs inside:
+the relative-score matrices of `_rel_bias` (`attentions/attn.py:1305-1314`) are
+never materialised, the Triton kernels are replaced by the C-ABI calls
+`mvpa_fwd` / `mvpa_bwd` (``include/mvpa.h``), and the backward returns the
+gradients of all eight tensors directly instead of leaving part of the work to
+autograd.  There is no CPU path: tensors must live on a CUDA device.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+import mvpa_native as _nat
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return _nat.MVPA_BF16
+    if t.dtype == torch.float32:
+        return _nat.MVPA_F32
+    raise RuntimeError(f"flash_mvpa: dtype {t.dtype} not supported (bfloat16 or float32)")
+
+
+def _tensor(t: torch.Tensor) -> _nat.Tensor:
+    return _nat.Tensor(t.data_ptr(), t.stride(0), t.stride(1), t.stride(2))
+
+
+def _rows(t: torch.Tensor) -> torch.Tensor:
+    """(B,H,N,D) with a contiguous last dim and 16-byte aligned strides, copying only if needed."""
+    es = t.element_size()
+    if t.stride(-1) != 1 or any((s * es) % 16 for s in t.stride()[:-1]) or t.data_ptr() % 16:
+        t = t.contiguous()
+    return t
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _problem(q, k, r_time, r_chan, sm_scale, window) -> _nat.Problem:
+    B, H, N, D = q.shape
+    return _nat.Problem(B, H, k.shape[1], r_time.shape[-2], r_chan.shape[-2], D, int(window),
+                        _dtype_code(q), float(sm_scale), 0)
+
+
+class FlashMVPA(torch.autograd.Function):
+    """Autograd wrapper; the counterpart of the reference's `FlashMVPA`
+    (`attentions/attn.py:1013-1302`), taking the relative keys themselves instead of
+    pre-multiplied score matrices."""
+
+    @staticmethod
+    def forward(ctx, q, u, vt, z, k, r_time, r_chan, v, sm_scale, window):
+        if not q.is_cuda:
+            raise RuntimeError("flash_mvpa: tensors must be on a CUDA device (no CPU path)")
+        lib = _nat.lib()
+        q, k, v = _rows(q), _rows(k), _rows(v)
+        u, vt, z, r_time, r_chan = (x.contiguous() for x in (u, vt, z, r_time, r_chan))
+        prob = _problem(q, k, r_time, r_chan, sm_scale, window)
+        o = torch.empty_like(q)
+        lse = torch.empty((q.shape[0] * q.shape[1], q.shape[2]), device=q.device, dtype=torch.float32)
+        nbytes = lib.mvpa_fwd_workspace_bytes(ctypes.byref(prob))
+        ws = torch.empty(max(nbytes, 16), device=q.device, dtype=torch.uint8)
+        tq, tk, tv, to = _tensor(q), _tensor(k), _tensor(v), _tensor(o)
+        with torch.cuda.device(q.device):
+            st = lib.mvpa_fwd(ctypes.byref(prob), ctypes.byref(tq), ctypes.byref(tk), ctypes.byref(tv),
+                              u.data_ptr(), vt.data_ptr(), z.data_ptr(), r_time.data_ptr(),
+                              r_chan.data_ptr(), ctypes.byref(to), lse.data_ptr(), ws.data_ptr(),
+                              nbytes, _stream())
+        _nat.check(st, "mvpa_fwd")
+        ctx.save_for_backward(q, u, vt, z, k, r_time, r_chan, v, o, lse)
+        ctx.sm_scale, ctx.window = sm_scale, window
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, u, vt, z, k, r_time, r_chan, v, o, lse = ctx.saved_tensors
+        lib = _nat.lib()
+        do = _rows(do)
+        prob = _problem(q, k, r_time, r_chan, ctx.sm_scale, ctx.window)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        f32 = dict(device=q.device, dtype=torch.float32)
+        du, dvt, dz = (torch.empty(u.shape, **f32) for _ in range(3))
+        drt, drc = torch.empty(r_time.shape, **f32), torch.empty(r_chan.shape, **f32)
+        nbytes = lib.mvpa_bwd_workspace_bytes(ctypes.byref(prob))
+        ws = torch.empty(max(nbytes, 16), device=q.device, dtype=torch.uint8)
+        T = [_tensor(x) for x in (q, k, v, o, do, dq, dk, dv)]
+        r = [ctypes.byref(x) for x in T]
+        with torch.cuda.device(q.device):
+            st = lib.mvpa_bwd(ctypes.byref(prob), r[0], r[1], r[2], u.data_ptr(), vt.data_ptr(),
+                              z.data_ptr(), r_time.data_ptr(), r_chan.data_ptr(), r[3], lse.data_ptr(),
+                              r[4], r[5], r[6], r[7], du.data_ptr(), dvt.data_ptr(), dz.data_ptr(),
+                              drt.data_ptr(), drc.data_ptr(), ws.data_ptr(), nbytes, _stream())
+        _nat.check(st, "mvpa_bwd")
+        dt = q.dtype
+        return (dq, du.to(dt), dvt.to(dt), dz.to(dt), dk, drt.to(dt), drc.to(dt), dv, None, None)
+
+
+def flash_mvpa(q, q_bias, q_btime, q_bchan, k_glob, k_time, k_chan, v, causal, sm_scale,
+               window_size=0, p_drop=0.0, sequence_parallel=False, rel_bias_time=True,
+               rel_bias_chan=True, generator=None):
+    """Fused multi-variate parallel attention.
+
+    q (B,H,N,D); q_bias/q_btime/q_bchan (1,Hkv,1,D) = u/v/z; k_glob, v (B,Hkv,N,D);
+    k_time (1,Hkv,T,D); k_chan (1,Hkv,C,D); N == T*C, token n = t*C + c.  Returns o (B,H,N,D).
+
+    As in the reference, causality is forced on whenever a relative term is used
+    (`attentions/attn.py:1335-1336`) and the same shape checks raise
+    (`:1339, 1344`).  `sequence_parallel` only chose a launch geometry in the
+    reference (`:1165-1172`) and is accepted and ignored.  Structured attention dropout
+    (`:1052-1062`) and runs without the relative terms are not implemented: they raise.
+    """
+    if not (rel_bias_time and rel_bias_chan):
+        raise NotImplementedError("flash_mvpa: both relative terms are required (as the layer uses it)")
+    if p_drop and p_drop > 0:
+        raise NotImplementedError("flash_mvpa: attention dropout is not implemented; use p_drop=0")
+    q_heads, kv_heads = q.shape[1], v.shape[1]
+    assert q_heads % kv_heads == 0, "Q heads must be divisible by KV heads."
+    n_ctx, time_ctx, chan_ctx = q.shape[2], k_time.shape[2], k_chan.shape[2]
+    assert n_ctx == time_ctx * chan_ctx
+    assert q.shape[-1] == k_glob.shape[-1] == v.shape[-1]
+    assert q.shape[-1] in {16, 32, 64, 128}
+    D = q.shape[-1]
+    u, vt, z = (x.reshape(kv_heads, D) for x in (q_bias, q_btime, q_bchan))
+    return FlashMVPA.apply(q, u, vt, z, k_glob, k_time.reshape(kv_heads, time_ctx, D),
+                           k_chan.reshape(kv_heads, chan_ctx, D), v, sm_scale, window_size)

@@ -1,0 +1,83 @@
+// Shared declarations of the Flash-MVPA library: the internal problem record
+// every kernel family receives, error plumbing and the launch counter.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "mvpa.h"
+
+namespace mvpa {
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+// Flattened view of the C-ABI arguments (include/mvpa.h) handed to kernels.
+struct Args {
+  const void *q, *k, *v, *u, *vt, *z, *rt, *rc;
+  void* o;
+  float* lse;
+  int64_t q_sb, q_sh, q_sn;
+  int64_t k_sb, k_sh, k_sn;
+  int64_t v_sb, v_sh, v_sn;
+  int64_t o_sb, o_sh, o_sn;
+  int B, H, Hkv, T, C, D, N, g, window;
+  float sm_scale;  // natural-log domain scale of the score sum
+  float c2;        // sm_scale * log2(e): scores are kept in base 2
+};
+
+struct BwdArgs {
+  Args a;
+  const void* d_o;
+  int64_t do_sb, do_sh, do_sn;
+  void *dq, *dk, *dv;
+  int64_t dq_sb, dq_sh, dq_sn;
+  int64_t dk_sb, dk_sh, dk_sn;
+  int64_t dv_sb, dv_sh, dv_sn;
+  float *du, *dvt, *dz, *drt, *drc;
+  // workspace carve-up (fp32 elements)
+  float *tbg, *cbg;    // (B*H, N, T), (B*H, N, C) relative scores, base-2 scaled
+  float *dtbg, *dcbg;  // gradients w.r.t. the unscaled relative scores
+  float* delta;        // (B*H, N)
+  float* partial;      // (B*H*nQT, 3, D) per-tile column sums for du/dvt/dz
+};
+
+void set_error(const char* fmt, ...);
+void count_launch(int n = 1);
+
+// fp32 CUDA-core kernels (any T, C; D in {16,32,64,128}); element type float or bf16.
+int simt_fwd(const Args& a, int dtype, cudaStream_t s);
+int simt_bwd(const BwdArgs& b, int dtype, cudaStream_t s);
+size_t simt_bwd_workspace_floats(const mvpa_problem* p);
+void simt_bwd_carve(BwdArgs& b, float* ws);
+
+// tcgen05 / TMEM / TMA forward for bf16 (mvpa_tc_fwd.cu).
+bool tc_fwd_supported(const Args& a);
+size_t tc_fwd_workspace_bytes(const mvpa_problem* p);
+int tc_fwd(const Args& a, void* workspace, size_t workspace_bytes, cudaStream_t s);
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T x);
+template <>
+__device__ __forceinline__ float to_f32<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T>
+__device__ __forceinline__ T from_f32(float x);
+template <>
+__device__ __forceinline__ float from_f32<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+}  // namespace mvpa
+
+#define MVPA_CUDA_CHECK(expr)                                                        \
+  do {                                                                               \
+    cudaError_t err__ = (expr);                                                      \
+    if (err__ != cudaSuccess) {                                                      \
+      ::mvpa::set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(err__),   \
+                        __FILE__, __LINE__);                                         \
+      return MVPA_ERR_CUDA;                                                          \
+    }                                                                                \
+  } while (0)

@@ -1,0 +1,134 @@
+"""Loader and builder of the Flash-MVPA shared library (C ABI in ``include/mvpa.h``).
+
+The library is compiled in-tree with ``nvcc`` for sm_100a only and bound through
+``ctypes``; PyTorch supplies device memory and the CUDA stream, nothing else.
+There is no fallback: if the library is missing and cannot be built, importing
+callers get an ``ImportError``.
+"""
+from __future__ import annotations
+
+import ctypes
+import hashlib
+import os
+import shutil
+import subprocess
+import threading
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_CSRC = os.path.join(_HERE, "csrc")
+_INCLUDE = os.path.join(os.path.dirname(_HERE), "include")
+LIB_PATH = os.path.join(_HERE, "libmvpa_b200.so")
+HASH_PATH = LIB_PATH + ".srchash"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC", "-shared", "--use_fast_math",
+]
+
+MVPA_F32, MVPA_BF16 = 0, 1
+
+_lock = threading.Lock()
+_lib = None
+
+
+def sources():
+    return sorted(os.path.join(_CSRC, f) for f in os.listdir(_CSRC) if f.endswith(".cu"))
+
+
+def _source_hash() -> str:
+    """Digest of everything the binary depends on (file times do not survive a copy)."""
+    h = hashlib.sha256(" ".join(NVCC_FLAGS).encode())
+    deps = sorted(os.path.join(_CSRC, f) for f in os.listdir(_CSRC)) + [os.path.join(_INCLUDE, "mvpa.h")]
+    for d in deps:
+        h.update(os.path.basename(d).encode())
+        with open(d, "rb") as f:
+            h.update(f.read())
+    return h.hexdigest()
+
+
+def _stale() -> bool:
+    if not (os.path.exists(LIB_PATH) and os.path.exists(HASH_PATH)):
+        return True
+    with open(HASH_PATH) as f:
+        return f.read().strip() != _source_hash()
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compile ``csrc/*.cu`` into ``libmvpa_b200.so`` (cross-compiles without a GPU)."""
+    if not force and not _stale():
+        return LIB_PATH
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        raise ImportError("nvcc not found: cannot build libmvpa_b200.so")
+    tmp = LIB_PATH + ".tmp"
+    cmd = [nvcc, *NVCC_FLAGS, "-I", _INCLUDE, "-I", _CSRC, *sources(), "-o", tmp]
+    if verbose:
+        cmd.insert(1, "-Xptxas=-v")
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise ImportError("building libmvpa_b200.so failed:\n" + res.stdout + res.stderr)
+    os.replace(tmp, LIB_PATH)
+    with open(HASH_PATH, "w") as f:
+        f.write(_source_hash())
+    if verbose:
+        print(res.stderr)
+    return LIB_PATH
+
+
+class Problem(ctypes.Structure):
+    _fields_ = [("B", ctypes.c_int32), ("H", ctypes.c_int32), ("Hkv", ctypes.c_int32),
+                ("T", ctypes.c_int32), ("C", ctypes.c_int32), ("D", ctypes.c_int32),
+                ("window", ctypes.c_int32), ("dtype", ctypes.c_int32),
+                ("sm_scale", ctypes.c_float), ("flags", ctypes.c_int32)]
+
+
+class Tensor(ctypes.Structure):
+    _fields_ = [("ptr", ctypes.c_void_p), ("stride_b", ctypes.c_int64),
+                ("stride_h", ctypes.c_int64), ("stride_n", ctypes.c_int64)]
+
+
+EXPORTS = ("mvpa_fwd", "mvpa_bwd", "mvpa_fwd_workspace_bytes", "mvpa_bwd_workspace_bytes",
+           "mvpa_last_error_string", "mvpa_launch_count", "mvpa_abi_version")
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded library; builds it first when the sources are newer than the binary."""
+    global _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if _stale():
+            try:
+                build()
+            except ImportError:
+                if not os.path.exists(LIB_PATH):
+                    raise
+        try:
+            L = ctypes.CDLL(LIB_PATH)
+        except OSError as e:  # no silent fallback: the CUDA library is the product
+            raise ImportError(f"cannot load {LIB_PATH}: {e}") from e
+        P, Tn, vp = ctypes.POINTER(Problem), ctypes.POINTER(Tensor), ctypes.c_void_p
+        L.mvpa_fwd_workspace_bytes.restype = ctypes.c_size_t
+        L.mvpa_fwd_workspace_bytes.argtypes = [P]
+        L.mvpa_bwd_workspace_bytes.restype = ctypes.c_size_t
+        L.mvpa_bwd_workspace_bytes.argtypes = [P]
+        L.mvpa_fwd.restype = ctypes.c_int
+        L.mvpa_fwd.argtypes = [P, Tn, Tn, Tn, vp, vp, vp, vp, vp, Tn, vp, vp, ctypes.c_size_t, vp]
+        L.mvpa_bwd.restype = ctypes.c_int
+        L.mvpa_bwd.argtypes = [P, Tn, Tn, Tn, vp, vp, vp, vp, vp, Tn, vp, Tn, Tn, Tn, Tn,
+                               vp, vp, vp, vp, vp, vp, ctypes.c_size_t, vp]
+        L.mvpa_last_error_string.restype = ctypes.c_char_p
+        L.mvpa_launch_count.restype = ctypes.c_uint64
+        L.mvpa_abi_version.restype = ctypes.c_int
+        _lib = L
+        return L
+
+
+def last_error() -> str:
+    return lib().mvpa_last_error_string().decode()
+
+
+def check(status: int, what: str) -> None:
+    """Raise like the reference does (`attentions/attn.py:1034-1045`): RuntimeError."""
+    if status != 0:
+        raise RuntimeError(f"{what} failed (status {status}): {last_error()}")

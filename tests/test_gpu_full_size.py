@@ -1,0 +1,89 @@
+"""GPU: size-independent properties at BASELINE's full kernel configurations, where the CPU
+oracle would take minutes: row-stochasticity, linearity in V, causality, batch/head
+independence, and agreement of the tensor-core path with the fp32 CUDA-core path on one slice."""
+import numpy as np
+import pytest
+import torch
+
+import mvpa_oracle as mo
+
+pytestmark = pytest.mark.gpu
+
+
+def make(dev, seed, B, H, Hkv, T, C, D, dtype=torch.bfloat16):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    N = T * C
+    r = lambda *s: torch.randn(*s, generator=g).to(dtype).to(dev)
+    return dict(q=r(B, H, N, D), u=r(1, Hkv, 1, D), v=r(1, Hkv, 1, D), z=r(1, Hkv, 1, D),
+                k=r(B, Hkv, N, D), rt=r(1, Hkv, T, D), rc=r(1, Hkv, C, D), val=r(B, Hkv, N, D))
+
+
+def run(t, **over):
+    import attentions
+    a = dict(t, **over)
+    D = a["q"].shape[-1]
+    return attentions.flashmvpa(a["q"], a["u"], a["v"], a["z"], a["k"], a["rt"], a["rc"], a["val"],
+                                causal=True, sm_scale=D ** -0.5, window_size=10)
+
+
+CFG2 = (4, 16, 16, 64, 64, 64)     # BASELINE config 2 (MHA)
+CFG2_GQA = (4, 16, 8, 64, 64, 64)
+CFG3 = (8, 16, 16, 128, 32, 64)    # BASELINE config 3
+LONG = (1, 4, 2, 128, 128, 128)    # 16k tokens, D=128 (per-sample slice of config 5)
+
+
+@pytest.mark.parametrize("cfg", [CFG2, CFG2_GQA, CFG3, LONG])
+def test_rows_sum_to_one_and_linearity(cuda, cfg):
+    t = make(cuda, 1, *cfg)
+    ones = torch.ones_like(t["val"])
+    o1 = run(t, val=ones).float()
+    assert (o1 - 1).abs().max() <= 1e-2            # softmax rows sum to one
+    a = run(t).float()
+    b = run(t, val=(2 * t["val"])).float()
+    assert (b - 2 * a).abs().max() <= 2e-2         # exact scaling of V by 2 commutes with rounding
+    assert torch.isfinite(a).all()
+
+
+@pytest.mark.parametrize("cfg", [CFG2, LONG])
+def test_causality_and_batch_independence(cuda, cfg):
+    B, H, Hkv, T, C, D = cfg
+    t = make(cuda, 2, *cfg)
+    a = run(t)
+    t_cut = T // 2
+    k2, v2 = t["k"].clone(), t["val"].clone()
+    k2[:, :, t_cut * C:] += 1.0                     # change every key/value of the later half
+    v2[:, :, t_cut * C:] *= -1.0
+    b = run(t, k=k2, val=v2)
+    assert torch.equal(a[:, :, : t_cut * C], b[:, :, : t_cut * C])
+    assert not torch.equal(a[:, :, t_cut * C:], b[:, :, t_cut * C:])
+    if B > 1:                                       # batch elements do not interact
+        perm = torch.arange(B - 1, -1, -1, device=cuda)
+        c = run(t, q=t["q"][perm].contiguous(), k=t["k"][perm].contiguous(),
+                val=t["val"][perm].contiguous())
+        assert torch.equal(c[perm], a)
+
+
+@pytest.mark.parametrize("cfg", [CFG2, CFG3, LONG])
+def test_tensor_core_path_vs_fp32_path_on_a_slice(cuda, cfg):
+    """One (batch, kv-group) slice: bf16 tensor-core result vs the fp32 CUDA-core kernels fed the
+    same bf16-rounded values (the fp32 path itself is pinned to the oracle in test_gpu_op)."""
+    B, H, Hkv, T, C, D = cfg
+    g = H // Hkv
+    t = make(cuda, 3, *cfg)
+    a = run(t)[:1, :g].float()
+    sl = dict(q=t["q"][:1, :g], k=t["k"][:1, :1], val=t["val"][:1, :1], u=t["u"][:, :1],
+              v=t["v"][:, :1], z=t["z"][:, :1], rt=t["rt"][:, :1], rc=t["rc"][:, :1])
+    b = run({k: x.float().contiguous() for k, x in sl.items()})
+    assert (a - b).abs().max() <= 2e-2
+
+
+def test_oracle_on_rows_of_config2(cuda):
+    """A few query rows of config 2 against the numpy oracle (row-chunked, one head)."""
+    B, H, Hkv, T, C, D = CFG2
+    t = make(cuda, 4, *CFG2)
+    o = run(t)[0, 0].float().cpu().numpy()
+    f = lambda x: x.float().cpu().numpy()
+    ref, _ = mo.mvpa_forward(f(t["q"][:1, :1]), f(t["u"][0, :1, 0]), f(t["v"][0, :1, 0]), f(t["z"][0, :1, 0]),
+                             f(t["k"][:1, :1]), f(t["rt"][0, :1]), f(t["rc"][0, :1]), f(t["val"][:1, :1]),
+                             D ** -0.5, row_chunk=512)
+    assert np.abs(o - ref[0, 0]).max() <= 2e-2

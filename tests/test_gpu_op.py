@@ -1,0 +1,164 @@
+"""GPU parity tests of the operator, through `attentions.flashmvpa` -> ctypes -> C ABI.
+
+Tolerances (against the fp32/fp64 oracle on the same inputs):
+  fp32 I/O : max-abs error <= 1e-4 * max|reference|
+  bf16 I/O : max-abs error <= 2e-2   (inputs rounded to bf16 first, oracle fed the rounded values)
+"""
+import numpy as np
+import pytest
+import torch
+
+import mvpa_oracle as mo
+from conftest import golden_op_cases, load_golden
+
+pytestmark = pytest.mark.gpu
+
+GRADS = ("dq", "du", "dv", "dz", "dk", "dr_time", "dr_chan", "dval")
+F32_REL = 1e-4
+BF16_ABS = 2e-2
+
+
+def _op(dev, g, dtype, grads=False, window=10):
+    import attentions
+    B, H, Hkv, T, C, D = (int(x) for x in g["dims"])
+    t = {k: torch.tensor(np.asarray(g[k], np.float32), device=dev, dtype=dtype, requires_grad=grads)
+         for k in ("q", "u", "v", "z", "k", "r_time", "r_chan", "val")}
+    o = attentions.flashmvpa(
+        t["q"], t["u"].view(1, Hkv, 1, D), t["v"].view(1, Hkv, 1, D), t["z"].view(1, Hkv, 1, D),
+        t["k"], t["r_time"].view(1, Hkv, T, D), t["r_chan"].view(1, Hkv, C, D), t["val"],
+        causal=True, sm_scale=float(g["sm_scale"]), window_size=window, p_drop=0,
+        rel_bias_chan=True, rel_bias_time=True)
+    return o, t
+
+
+def _np(x):
+    return x.detach().float().cpu().numpy()
+
+
+def _rounded(g):
+    """Copy of a case with every input rounded to bf16 (what the bf16 kernels actually see)."""
+    r = dict(g)
+    for k in ("q", "u", "v", "z", "k", "r_time", "r_chan", "val", "do"):
+        if k in r:
+            r[k] = torch.tensor(r[k]).to(torch.bfloat16).float().numpy()
+    return r
+
+
+def random_case(seed, B, H, Hkv, T, C, D, scale=1.0):
+    rng = np.random.default_rng(seed)
+    N = T * C
+    f = lambda *s: (scale * rng.standard_normal(s)).astype(np.float32)
+    return dict(q=f(B, H, N, D), k=f(B, Hkv, N, D), val=f(B, Hkv, N, D), u=f(Hkv, D), v=f(Hkv, D),
+                z=f(Hkv, D), r_time=f(Hkv, T, D), r_chan=f(Hkv, C, D), do=f(B, H, N, D),
+                dims=np.array([B, H, Hkv, T, C, D]), sm_scale=np.float64(D ** -0.5))
+
+
+def _oracle_args(g):
+    return (g["q"], g["u"], g["v"], g["z"], g["k"], g["r_time"], g["r_chan"], g["val"])
+
+
+@pytest.mark.parametrize("name", golden_op_cases())
+def test_fp32_forward_vs_reference_golden(cuda, name):
+    g = load_golden(name)
+    o, _ = _op(cuda, g, torch.float32)
+    assert np.abs(_np(o) - g["o"]).max() <= F32_REL * np.abs(g["o"]).max()
+
+
+@pytest.mark.parametrize("name", [n for n in golden_op_cases() if n != "cfg1"])
+def test_fp32_backward_vs_reference_golden(cuda, name):
+    g = load_golden(name)
+    o, t = _op(cuda, g, torch.float32, grads=True)
+    o.backward(torch.tensor(g["do"], device=cuda))
+    for key, gk in zip(("q", "u", "v", "z", "k", "r_time", "r_chan", "val"), GRADS):
+        ref = g[gk]
+        err = np.abs(_np(t[key].grad).reshape(ref.shape) - ref).max()
+        assert err <= F32_REL * max(1.0, np.abs(ref).max()), (gk, err)
+
+
+@pytest.mark.parametrize("name", golden_op_cases())
+def test_bf16_forward_vs_oracle_on_golden_inputs(cuda, name):
+    g = _rounded(load_golden(name))
+    ref, _ = mo.mvpa_forward(*_oracle_args(g), float(g["sm_scale"]))
+    o, _ = _op(cuda, g, torch.bfloat16)
+    assert np.abs(_np(o) - ref).max() <= BF16_ABS
+
+
+@pytest.mark.parametrize("name", ["gqa2_t24_c5", "t11_c4", "t16_c16_d64", "t6_c22_d64", "t2_c128_d128"])
+def test_bf16_backward_vs_oracle_on_golden_inputs(cuda, name):
+    g = _rounded(load_golden(name))
+    ref = mo.mvpa_backward(*_oracle_args(g), g["do"], float(g["sm_scale"]))
+    o, t = _op(cuda, g, torch.bfloat16, grads=True)
+    o.backward(torch.tensor(g["do"], device=cuda, dtype=torch.bfloat16))
+    for key, gk in zip(("q", "u", "v", "z", "k", "r_time", "r_chan", "val"), GRADS):
+        r = ref[gk]
+        err = np.abs(_np(t[key].grad).reshape(r.shape) - r).max()
+        assert err <= BF16_ABS * max(1.0, np.abs(r).max()), (gk, err)
+
+
+SHAPES = [  # B, H, Hkv, T, C, D
+    (1, 2, 2, 24, 32, 64),    # mixed window tiles
+    (2, 2, 1, 13, 64, 64),    # GQA g=2, two time steps per 128-key tile
+    (1, 2, 2, 14, 128, 64),   # one time step per tile, light tiles appear (t >= 11)
+    (1, 2, 1, 12, 128, 128),  # D=128
+    (1, 3, 1, 16, 22, 64),    # g=3, ragged channels
+    (1, 1, 1, 30, 16, 64),
+    (1, 2, 2, 3, 100, 128),
+    (1, 1, 1, 40, 7, 32),
+    (1, 1, 1, 9, 130, 16),
+]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_forward_random_shapes_vs_oracle(cuda, shape, dtype):
+    g = random_case(100 + sum(shape), *shape)
+    dt = getattr(torch, dtype)
+    if dt == torch.bfloat16:
+        g = _rounded(g)
+    ref, lse = mo.mvpa_forward(*_oracle_args(g), float(g["sm_scale"]))
+    o, _ = _op(cuda, g, dt)
+    err = np.abs(_np(o) - ref).max()
+    assert err <= (BF16_ABS if dt == torch.bfloat16 else F32_REL * np.abs(ref).max()), err
+
+
+@pytest.mark.parametrize("shape", [(1, 2, 1, 13, 16, 64), (1, 2, 2, 12, 32, 32), (1, 1, 1, 3, 128, 128)])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_backward_random_shapes_vs_oracle(cuda, shape, dtype):
+    g = random_case(200 + sum(shape), *shape)
+    dt = getattr(torch, dtype)
+    if dt == torch.bfloat16:
+        g = _rounded(g)
+    ref = mo.mvpa_backward(*_oracle_args(g), g["do"], float(g["sm_scale"]))
+    o, t = _op(cuda, g, dt, grads=True)
+    o.backward(torch.tensor(g["do"], device=cuda, dtype=dt))
+    tol = BF16_ABS if dt == torch.bfloat16 else F32_REL
+    for key, gk in zip(("q", "u", "v", "z", "k", "r_time", "r_chan", "val"), GRADS):
+        r = ref[gk]
+        err = np.abs(_np(t[key].grad).reshape(r.shape) - r).max()
+        assert err <= tol * max(1.0, np.abs(r).max()), (gk, err)
+
+
+def test_no_window_flag(cuda):
+    g = random_case(7, 1, 2, 2, 14, 8, 32)
+    ref, _ = mo.mvpa_forward(*_oracle_args(g), float(g["sm_scale"]), window=10 ** 6)
+    o, _ = _op(cuda, g, torch.float32, window=0)   # reference: window_size=0 means not windowed
+    assert np.abs(_np(o) - ref).max() <= F32_REL * np.abs(ref).max()
+
+
+def test_strided_inputs_match_contiguous(cuda):
+    """Heads may be handed over as strided views of a (B, N, H, D) buffer."""
+    import attentions
+    g = random_case(9, 2, 4, 2, 6, 16, 64)
+    B, H, Hkv, T, C, D = (int(x) for x in g["dims"])
+    tt = {k: torch.tensor(g[k], device=cuda) for k in g if k not in ("dims", "sm_scale")}
+    kw = dict(causal=True, sm_scale=float(g["sm_scale"]), window_size=10)
+    bias = [tt[k].view(1, Hkv, 1, D) for k in ("u", "v", "z")]
+    rel = [tt["r_time"].view(1, Hkv, T, D), tt["r_chan"].view(1, Hkv, C, D)]
+    o1 = attentions.flashmvpa(tt["q"], *bias, tt["k"], *rel, tt["val"], **kw)
+    qs = tt["q"].permute(0, 2, 1, 3).contiguous().permute(0, 2, 1, 3)
+    ks = tt["k"].permute(0, 2, 1, 3).contiguous().permute(0, 2, 1, 3)
+    vs = tt["val"].permute(0, 2, 1, 3).contiguous().permute(0, 2, 1, 3)
+    assert not qs.is_contiguous()
+    o2 = attentions.flashmvpa(qs, *bias, ks, *rel, vs, **kw)
+    assert o2.stride() == qs.stride()
+    assert torch.equal(o1, o2)
