@@ -100,6 +100,12 @@ int mvpa_bwd(const mvpa_problem* p, const mvpa_tensor* q, const mvpa_tensor* k,
              const mvpa_tensor* dv, float* du, float* dvt, float* dz, float* dr_time,
              float* dr_chan, void* workspace, size_t workspace_bytes, void* cuda_stream);
 
+/* Reads back the status word the kernels of the last mvpa_fwd call left at the start of
+ * `workspace` (every device-side wait is bounded; one that runs out records a code there and
+ * the kernel returns instead of hanging).  Synchronises `cuda_stream`.  Returns MVPA_OK, or
+ * MVPA_ERR_DEVICE with the code in the error text.  Has no counterpart in the reference. */
+int mvpa_workspace_status(const void* workspace, size_t workspace_bytes, void* cuda_stream);
+
 /* Text of the last error raised on this host thread ("" if none).
  * Stands where the reference raises RuntimeError / assert
  * (`attentions/attn.py:1034-1045, 1339, 1344`). */

@@ -11,10 +11,15 @@ autograd.  There is no CPU path: tensors must live on a CUDA device.
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
 import mvpa_native as _nat
+
+
+# MVPA_CHECK_STATUS=1: read the kernels' status word back after every forward (synchronises).
+_CHECK_STATUS = os.environ.get("MVPA_CHECK_STATUS", "0") == "1"
 
 
 def _dtype_code(t: torch.Tensor) -> int:
@@ -71,6 +76,8 @@ class FlashMVPA(torch.autograd.Function):
                               r_chan.data_ptr(), ctypes.byref(to), lse.data_ptr(), ws.data_ptr(),
                               nbytes, _stream())
         _nat.check(st, "mvpa_fwd")
+        if _CHECK_STATUS and nbytes:  # debugging aid: synchronises the stream
+            _nat.check(lib.mvpa_workspace_status(ws.data_ptr(), nbytes, _stream()), "mvpa_fwd kernels")
         ctx.save_for_backward(q, u, vt, z, k, r_time, r_chan, v, o, lse)
         ctx.sm_scale, ctx.window = sm_scale, window
         return o

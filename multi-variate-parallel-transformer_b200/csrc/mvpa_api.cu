@@ -185,6 +185,19 @@ int mvpa_bwd(const mvpa_problem* p, const mvpa_tensor* q, const mvpa_tensor* k, 
   return simt_bwd(b, p->dtype, (cudaStream_t)cuda_stream);
 }
 
+int mvpa_workspace_status(const void* workspace, size_t workspace_bytes, void* cuda_stream) {
+  if (workspace == nullptr || workspace_bytes < sizeof(int)) return MVPA_OK;  // nothing was recorded
+  int code = 0;
+  cudaStream_t s = (cudaStream_t)cuda_stream;
+  MVPA_CUDA_CHECK(cudaMemcpyAsync(&code, workspace, sizeof(int), cudaMemcpyDeviceToHost, s));
+  MVPA_CUDA_CHECK(cudaStreamSynchronize(s));
+  if (code != 0) {
+    set_error("a kernel gave up a bounded wait (code %d) and returned early; outputs are invalid", code);
+    return MVPA_ERR_DEVICE;
+  }
+  return MVPA_OK;
+}
+
 const char* mvpa_last_error_string(void) { return g_error; }
 
 uint64_t mvpa_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }

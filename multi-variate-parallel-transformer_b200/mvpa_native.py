@@ -88,7 +88,8 @@ class Tensor(ctypes.Structure):
 
 
 EXPORTS = ("mvpa_fwd", "mvpa_bwd", "mvpa_fwd_workspace_bytes", "mvpa_bwd_workspace_bytes",
-           "mvpa_last_error_string", "mvpa_launch_count", "mvpa_abi_version")
+           "mvpa_last_error_string", "mvpa_launch_count", "mvpa_abi_version",
+           "mvpa_workspace_status")
 
 
 def lib() -> ctypes.CDLL:
@@ -117,6 +118,8 @@ def lib() -> ctypes.CDLL:
         L.mvpa_bwd.restype = ctypes.c_int
         L.mvpa_bwd.argtypes = [P, Tn, Tn, Tn, vp, vp, vp, vp, vp, Tn, vp, Tn, Tn, Tn, Tn,
                                vp, vp, vp, vp, vp, vp, ctypes.c_size_t, vp]
+        L.mvpa_workspace_status.restype = ctypes.c_int
+        L.mvpa_workspace_status.argtypes = [vp, ctypes.c_size_t, vp]
         L.mvpa_last_error_string.restype = ctypes.c_char_p
         L.mvpa_launch_count.restype = ctypes.c_uint64
         L.mvpa_abi_version.restype = ctypes.c_int

@@ -5,6 +5,8 @@ import sys
 import numpy as np
 import pytest
 
+os.environ.setdefault("MVPA_CHECK_STATUS", "1")  # tests read the kernels' status word back
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 PKG = os.path.join(ROOT, "multi-variate-parallel-transformer_b200")
 for p in (PKG, os.path.join(ROOT, "oracle"), ROOT):
