@@ -1,0 +1,283 @@
+#!/usr/bin/env python
+"""Flash-MVPA forward benchmark (one JSON line on rank 0).
+
+Workload: BASELINE config 2 per GPU — bf16 forward, batch 4, 64 channels x 64 time segments
+(4096 tokens), 16 heads (MHA), head_dim 64, window 10; Q/K/V, relative keys and biases ~ N(0,1),
+seed 1.  With N GPUs every rank runs that workload on its own batch shard (weak scaling, no
+data-path collective: batch elements are independent).
+
+  value     whole-job TFLOP/s with inputs resident in HBM, counted with the window-aware
+            algorithmic flop count F_alg = 2D(P_c+P_w) + 2DN(T+C) per (batch, head)
+  e2e       same metric through `attentions.flashmvpa` with HOST buffers: pinned host->device
+            copies of q/k/v and the device->host read of o are inside the timed region
+  roofline  dominant kernel vs the measured dense bf16 peak (MEASURED_PEAKS.json, burst figure)
+  cpu_baseline  the materialised PyTorch attention (oracle/mvpa_port_torch.py, a port of the
+            reference's `_rel_attn`) on the host cores, on a bounded sample of the same workload
+
+`--impl reference` times only that CPU port (rank 0), as the reference arm.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "multi-variate-parallel-transformer_b200"))
+
+WORKLOAD = dict(B=4, H=16, Hkv=16, T=64, C=64, D=64, window=10)
+NAME = "cfg2: bf16 fwd, B4 x 16 heads (MHA) x 4096 tokens (64 ch x 64 seg), head_dim 64, window 10"
+METRIC = "flash_mvpa_fwd_tflops"
+UNIT = "TFLOP/s (F_alg)"
+
+
+def flops(B, H, T, C, D, window=10, **_):
+    N = T * C
+    p_c = C * C * T * (T + 1) // 2
+    p_w = C * C * (sum(min(t, window) + 1 for t in range(T - 1)) + T)
+    return dict(f_alg=B * H * (2 * D * (p_c + p_w) + 2 * D * N * (T + C)), f_dense=B * H * 4 * D * p_c)
+
+
+def peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            m = json.load(f)
+        return float(m["bf16_tflops"]), "measured (MEASURED_PEAKS.json bf16_tflops, burst)"
+    except Exception:
+        return 1590.0, "fallback (1.59 PFLOP/s, earlier pool measurement)"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 6 for n, v in zip(names, r[2:6]) if v == "Active"})
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def cpu_port_time(sample, reps=1, seed=1):
+    """Seconds per pass of the materialised PyTorch attention over `sample` on the host cores."""
+    import torch
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import mvpa_port_torch as port
+    B, H, Hkv, T, C, D = (sample[k] for k in ("B", "H", "Hkv", "T", "C", "D"))
+    g = torch.Generator().manual_seed(seed)
+    N = T * C
+    r = lambda *s: torch.randn(*s, generator=g)
+    args = (r(B, H, N, D), r(Hkv, D), r(Hkv, D), r(Hkv, D), r(B, Hkv, N, D), r(Hkv, T, D), r(Hkv, C, D),
+            r(B, Hkv, N, D))
+    ts = []
+    with torch.no_grad():
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            port.rel_attn(*args, D ** -0.5, sample["window"])
+            ts.append(time.perf_counter() - t0)
+    return statistics.median(ts), torch.get_num_threads()
+
+
+def run_reference(args):
+    """Reference arm: the CPU port of the reference attention on the box's host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample = dict(WORKLOAD, B=1, H=4, Hkv=4)   # one batch element, 4 of its 16 heads per step
+    for _ in range(min(args.warmup, 2)):
+        cpu_port_time(dict(sample, H=1, Hkv=1))
+    t0 = time.perf_counter()
+    per, cores = [], 1
+    for _ in range(args.steps):
+        t, cores = cpu_port_time(sample)
+        per.append(t)
+    total = sum(per)
+    f = flops(**sample)["f_alg"] * args.steps
+    val = f / total / 1e12
+    desc = "1 batch element x 4 heads of the workload per step (1/16 of it)"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": {"workload": NAME, "sample": desc},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "wall_s": time.perf_counter() - t0,
+    }))
+
+
+def make_inputs(torch, dev, w, seed, pinned=False):
+    g = torch.Generator().manual_seed(seed)
+    N = w["T"] * w["C"]
+    B, H, Hkv, T, C, D = (w[k] for k in ("B", "H", "Hkv", "T", "C", "D"))
+    shapes = dict(q=(B, H, N, D), u=(1, Hkv, 1, D), v=(1, Hkv, 1, D), z=(1, Hkv, 1, D), k=(B, Hkv, N, D),
+                  rt=(1, Hkv, T, D), rc=(1, Hkv, C, D), val=(B, Hkv, N, D))
+    host = {n: torch.randn(*s, generator=g).to(torch.bfloat16) for n, s in shapes.items()}
+    if pinned:
+        host = {n: x.pin_memory() for n, x in host.items()}
+    return host, {n: x.to(dev) for n, x in host.items()}
+
+
+def time_kernel(torch, attentions, t, w, steps, warmup, flush):
+    call = lambda: attentions.flashmvpa(t["q"], t["u"], t["v"], t["z"], t["k"], t["rt"], t["rc"], t["val"],
+                                        causal=True, sm_scale=w["D"] ** -0.5, window_size=w["window"])
+    for _ in range(warmup):
+        call()
+    torch.cuda.synchronize()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for a, b in ev:
+        flush.add_(1)          # writes 256 MiB: evicts the 126 MB L2 between timed launches
+        a.record()
+        call()
+        b.record()
+    torch.cuda.synchronize()
+    return [a.elapsed_time(b) for a, b in ev]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-extra", action="store_true", help="skip the extra reported points")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+    import attentions
+    import mvpa_native
+
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = mvpa_native.lib()
+    w = WORKLOAD
+    host, t = make_inputs(torch, dev, w, seed=1 + rank, pinned=True)
+    flush = torch.zeros(64 * 1024 * 1024, dtype=torch.float32, device=dev)
+    f = flops(**w)
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident throughput ----
+    sync_all()
+    n0 = lib.mvpa_launch_count()
+    with ClockSampler(local) as clk:
+        sync_all()
+        ms = time_kernel(torch, attentions, t, w, args.steps, args.warmup, flush)
+        sync_all()
+    launches = lib.mvpa_launch_count() - n0 - args.warmup
+    total_ms = torch.tensor([sum(ms)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
+    total_ms = float(total_ms.item())
+    value = world * f["f_alg"] * args.steps / (total_ms * 1e-3) / 1e12
+
+    # ---- end to end: pinned host inputs -> device -> flashmvpa -> host ----
+    big = ("q", "k", "val")
+    o_host = torch.empty(host["q"].shape, dtype=torch.bfloat16).pin_memory()
+    h2d = sum(host[n].numel() * 2 for n in host)
+    d2h = o_host.numel() * 2
+
+    def e2e_step():
+        d = {n: host[n].to(dev, non_blocking=True) for n in host}
+        o = attentions.flashmvpa(d["q"], d["u"], d["v"], d["z"], d["k"], d["rt"], d["rc"], d["val"],
+                                 causal=True, sm_scale=w["D"] ** -0.5, window_size=w["window"])
+        o_host.copy_(o, non_blocking=True)
+
+    for _ in range(args.warmup):
+        e2e_step()
+    sync_all()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.steps):
+        e2e_step()
+    b.record()
+    sync_all()
+    e2e_ms = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    e2e_val = world * f["f_alg"] * args.steps / (float(e2e_ms.item()) * 1e-3) / 1e12
+
+    if rank == 0:
+        peak, peak_src = peaks()
+        kernel_ms = statistics.mean(ms)
+        achieved = f["f_alg"] / (kernel_ms * 1e-3) / 1e12
+        out = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": NAME, "per_gpu_batch": w["B"], "global_batch": w["B"] * world,
+                       "l2": "256 MiB buffer rewritten between timed launches", "parallelism": f"batch x{world}"},
+            "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": int(launches),
+            "clocks": clk.summary(),
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                         "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                         "kernel": "tc_fwd_kernel<64,64>", "flops_per_launch": f["f_alg"],
+                         "achieved_dense_convention": f["f_dense"] / (kernel_ms * 1e-3) / 1e12},
+        }
+        if not args.no_extra:
+            extra = {}
+            for name, ww in (("16k_tokens_D128_H16_Hkv8_B1", dict(B=1, H=16, Hkv=8, T=128, C=128, D=128, window=10)),
+                             ("cfg3_fwd_B8_T128_C32_D64", dict(B=8, H=16, Hkv=16, T=128, C=32, D=64, window=10))):
+                _, tt = make_inputs(torch, dev, ww, seed=7)
+                m2 = statistics.mean(time_kernel(torch, attentions, tt, ww, 10, 3, flush))
+                ff = flops(**ww)
+                extra[name] = {"ms": m2, "tflops_f_alg": ff["f_alg"] / m2 / 1e9, "tflops_f_dense": ff["f_dense"] / m2 / 1e9,
+                               "frac_of_peak_f_alg": ff["f_alg"] / m2 / 1e9 / peak}
+                del tt
+            out["extra"] = extra
+        if not args.no_cpu:
+            sample = dict(w, B=1)
+            sec, cores = cpu_port_time(sample)
+            out["cpu_baseline"] = {"value": flops(**sample)["f_alg"] / sec / 1e12, "unit": UNIT, "cores": cores,
+                                   "kind": "port", "sample": "1 of the 4 batch elements (16 heads, 4096 tokens), fp32, 1 pass",
+                                   "seconds": sec}
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
