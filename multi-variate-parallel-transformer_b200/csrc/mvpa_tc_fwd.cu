@@ -3,22 +3,26 @@
 // One CTA owns 128 query rows (= TPB whole time steps of CP channel slots, CP = channels padded
 // to a power of two) of one (batch, head) and walks the causal key tiles of the same shape.
 //
-//   warp 4   TMA producer (one lane): Q tile, relative keys, then the K/V ring
-//   warp 5   MMA issuer (one lane):   S = Q'K^T and O += P V on tcgen05, plus the two small
+//   warps 0-3, 4-7  two softmax warpgroups.  Thread (row, wg) owns TMEM lane `row` and the key
+//            columns [64 wg, 64 wg + 64) of every tile: it adds the temporal and channel
+//            relative scores, masks, runs the base-2 online softmax
+//            (`attentions/attn.py:309-315`) and writes P (bf16) back into TMEM for the PV
+//            product.  O is rescaled only when the running maximum moved by more than 2^8.
+//   warp 8   TMA producer (one lane): Q tile, relative keys, then the K/V ring
+//   warp 9   MMA issuer (one lane): S = Q'K^T and O += P V on tcgen05, plus the two small
 //            products that replace the reference's `_rel_bias` matrices
 //            (`attentions/attn.py:1305-1314`); allocates / frees TMEM
-//   warps 0-3 softmax: one thread per query row (= one TMEM lane): adds the temporal and channel
-//            relative scores, masks, online softmax in base 2 (`attentions/attn.py:309-315`),
-//            writes P (bf16) back into TMEM for the PV product, rescales O only when the
-//            running maximum moved by more than 2^8, epilogue O / l and L = m + log2 l.
 //
-// TMEM columns: [0,128) S0 / P0, [128,256) S1 / P1, [256,256+D) O, [384,512) temporal scores
-// TB[row][j] = c2 (q+vt).r_time[j].  The channel scores of a row are gathered once per CTA into
-// registers (fp16x2, relative to their maximum).
+// Key tiles are visited dense-first: the tiles that overlap the content window (and the
+// diagonal), then the "light" tiles that lie wholly outside it.  The reference zero-fills the
+// content term there (`attentions/attn.py:261-271`) but still computes it; here a light tile
+// loads no K, issues no QK^T and computes no exponential per pair: its probabilities are the
+// outer product  exp2(tb_i[t_k] - m) x exp2(cb_i[c_k])  of a per-time-step scalar and the row's
+// channel vector, formed with packed bf16 multiplies.
 //
-// Tiles whose every pair lies outside the content window skip the K load and the QK^T product
-// (the reference zero-fills the content term there, `attentions/attn.py:261-271`, but still
-// computes it); their scores are the two relative terms only.
+// TMEM columns: [0,128) S0 / P0, [128,256) S1 / P1, [256,256+D) O, [384,512) raw temporal
+// products TBraw[row][j] = q.r_time[j]  (the bias part vt.r_time[j] is a per-column constant
+// kept in shared memory).
 #include <cuda_fp16.h>
 
 #include "mvpa_common.cuh"
@@ -30,12 +34,21 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kThreads = 192;
+constexpr int kSoftmaxThreads = 256;
+constexpr int kThreads = 384;  // warps 10, 11 only donate their registers
 constexpr int kTmemCols = 512;
-constexpr uint32_t kColS = 0;      // + 128 * buf
+constexpr uint32_t kColS = 0;  // + 128 * buf
 constexpr uint32_t kColO = 256;
 constexpr uint32_t kColTB = 384;
 constexpr float kRescaleThreshold = 8.f;  // log2 units: P stays below 2^8
+
+// Optional in-kernel timeline (build with -DMVPA_TC_TRACE): 128 clock64 stamps per CTA, written
+// by one softmax thread and the MMA thread into the workspace after the status word.
+#ifdef MVPA_TC_TRACE
+#define TRACE(slot) do { if (trace_on) p.trace[(size_t)blockIdx.x * 128 + (slot)] = clock64(); } while (0)
+#else
+#define TRACE(slot) do { } while (0)
+#endif
 
 struct TcMaps {
   CUtensorMap q, k, v, rt, rc;
@@ -49,27 +62,33 @@ struct TcArgs {
   int B, H, Hkv, T, C, g, window, n_qt;
   float c2;
   int* status;
+  long long* trace;
 };
 
 enum BarrierIndex {
-  kBarProFull = 0, kBarProReady, kBarProMma, kBarProDone,
-  kBarSFull,                 // 2
-  kBarPFull = kBarSFull + 2, // 2
-  kBarPvDone = kBarPFull + 2,// 2
-  kBarKvFull = kBarPvDone + 2,  // ST, then kv_free ST
+  kBarProFull = 0, kBarProMma, kBarProDone, kBarXchg,
+  kBarSFull,                     // 2
+  kBarPFull = kBarSFull + 2,     // 2
+  kBarPlFull = kBarPFull + 2,    // 4: P of the light tiles (four buffers, 64 TMEM columns each)
+  kBarSlotFull = kBarPlFull + 4,  // NS, then slot_free NS
 };
 
 template <int D>
 struct Cfg {
-  static constexpr int NH = D / 64;              // 64-column (128-byte) halves of a row
-  static constexpr int HALF = 16384;             // 128 rows x 128 B
-  static constexpr int TILE = NH * HALF;         // one 128 x D bf16 tile
-  static constexpr int ST = D == 64 ? 4 : 2;     // K/V ring depth
-  static constexpr int STAGE = 2 * TILE;         // K then V
+  static constexpr int NH = D / 64;            // 64-column (128-byte) halves of a row
+  static constexpr int HALF = 16384;           // 128 rows x 128 B
+  static constexpr int TILE = NH * HALF;       // one 128 x D bf16 tile = one ring slot
+  // K/V ring of NS slots.  A dense tile takes two consecutive slots (K then V), a light tile one (V).
+  static constexpr int NS = D == 64 ? 10 : 5;
+  static constexpr int PRO_SLOTS = 65536 / TILE;  // slots the prologue borrows (64 KB: sR + sC, then the scratch)
+  static constexpr int EARLY = NS - PRO_SLOTS;    // loads that may start before the prologue ends
   static constexpr int SMEM_Q = 0;
   static constexpr int SMEM_RING = TILE;
-  static constexpr int SMEM_TAIL = SMEM_RING + ST * STAGE;
-  static constexpr int TAIL_BYTES = 3 * D * 4 + (kBarKvFull + 2 * ST) * 8 + 16;
+  static constexpr int SMEM_PRO = SMEM_RING + EARLY * TILE;
+  static constexpr int SMEM_TAIL = SMEM_RING + NS * TILE;
+  // tail: u/vt/z (3D f32), vR[128], zC[128], smax[2][2][128], lsum[2][128], barriers, tmem slot, abort
+  static constexpr int TAIL_FLOATS = 3 * D + 128 + 128 + 512 + 256;
+  static constexpr int TAIL_BYTES = TAIL_FLOATS * 4 + (kBarSlotFull + 2 * NS) * 8 + 16;
   static constexpr int SMEM_BYTES = SMEM_TAIL + TAIL_BYTES + 1024;  // + alignment slack
 };
 
@@ -78,68 +97,89 @@ __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, int* s
   return __all_sync(0xffffffffu, mbar_wait(bar, parity, status, code));
 }
 
-__device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// All 256 softmax threads.  Only ever called outside data-dependent control flow.
+__device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
-// True when no pair of (query tile I, key tile J) has a non-zero content term.
-__device__ __forceinline__ bool tile_is_light(int I, int J, int TPB, int window, int n_qt) {
-  if (window <= 0 || I == n_qt - 1) return false;  // last tile holds the row t = T-1 that sees all
-  const int min_dt = I * TPB - (J * TPB + TPB - 1);
-  return min_dt > window;
+__device__ __forceinline__ uint32_t hmul2_bf16(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+// Number of leading key tiles of query tile I that are "light": every pair outside the content
+// window, i.e.  I*TPB - (J*TPB + TPB - 1) > window.  Light-ness is monotone in J.
+__device__ __forceinline__ int light_tiles(int I, int TPB, int window, int n_qt) {
+  if (window <= 0 || I == n_qt - 1) return 0;  // the last tile holds the row t = T-1 that sees all
+  const int x = I * TPB - TPB - window;
+  return x < 0 ? 0 : x / TPB + 1;
 }
 
 template <int D, int CP>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
   using C_ = Cfg<D>;
-  constexpr int NH = C_::NH, HALF = C_::HALF, TILE = C_::TILE, ST = C_::ST;
-  constexpr int TPB = 128 / CP;   // time steps per tile
+  constexpr int NH = C_::NH, HALF = C_::HALF, TILE = C_::TILE, NS = C_::NS;
+  constexpr int TPB = 128 / CP;                // time steps per tile
+  constexpr int TPW = TPB >= 2 ? TPB / 2 : 1;  // time steps inside one warpgroup's 64 columns
+  constexpr int NCH = CP < 64 ? CP : 64;       // distinct channel slots inside those columns
   constexpr int KSTEPS = D / 16;
-  constexpr int LDC = CP + 1;     // scratch row stride (floats)
+  constexpr int DW = D / 2;                    // O columns each warpgroup rescales / stores
   static_assert(CP >= 32 && CP <= 128 && (CP & (CP - 1)) == 0, "CP in {32,64,128}");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem + C_::SMEM_Q;
   uint8_t* ring = smem + C_::SMEM_RING;
-  uint8_t* sQv = ring;                   // prologue-only buffers alias the K/V ring
-  uint8_t* sQz = ring + TILE;
-  uint8_t* sR = ring + 2 * TILE;         // r_time rows 0..127 (rows >= T are zero)
-  uint8_t* sC = ring + 3 * TILE;         // r_chan rows 0..CP-1
-  float* scratch = reinterpret_cast<float*>(ring);  // [128][LDC], after the prologue MMAs
-  float* s_bias = reinterpret_cast<float*>(smem + C_::SMEM_TAIL);  // u, vt, z as fp32, times 1
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_bias + 3 * D);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kBarKvFull + 2 * ST);
+  uint8_t* sR = smem + C_::SMEM_PRO;            // r_time rows 0..127 (rows >= T are zero)
+  uint8_t* sC = sR + TILE;                      // r_chan rows 0..CP-1
+  float* scratch = reinterpret_cast<float*>(smem + C_::SMEM_PRO);  // [128][CP], once sR / sC are dead
+  float* s_bias = reinterpret_cast<float*>(smem + C_::SMEM_TAIL);  // u, vt, z as fp32
+  float* s_vr = s_bias + 3 * D;                 // vt . r_time[j]
+  float* s_zc = s_vr + 128;                     // z  . r_chan[j]
+  float* s_max = s_zc + 128;                    // [2 slots][2 wg][128 rows]
+  float* s_lsum = s_max + 512;                  // [2 wg][128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_lsum + 256);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kBarSlotFull + 2 * NS);
   int* s_abort = reinterpret_cast<int*>(tmem_slot + 1);
-  uint64_t* kv_full = bars + kBarKvFull;
-  uint64_t* kv_free = kv_full + ST;
+  int* s_giveup = s_abort + 1;
+  uint64_t* slot_full = bars + kBarSlotFull;
+  uint64_t* slot_free = slot_full + NS;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int BH = p.B * p.H;
   const int I = p.n_qt - 1 - (int)(blockIdx.x / BH);  // latest (heaviest) query tiles first
   const int bh = blockIdx.x % BH, b = bh / p.H, h = bh % p.H, hk = h / p.g;
   const int n_tiles = I + 1;
+  const int n_light = light_tiles(I, TPB, p.window, p.n_qt);
+  const int n_dense = n_tiles - n_light;
+  // visit order: dense tiles n_light..I, then light tiles 0..n_light-1
+  auto tile_of = [&](int s) { return s < n_dense ? n_light + s : s - n_dense; };
+  // position of a tile's K / V in the load sequence; slot = q % NS, use count = q / NS
+  auto q_of_k = [&](int s) { return 2 * s; };
+  auto q_of_v = [&](int s) { return s < n_dense ? 2 * s + 1 : n_dense + s; };
   const int T = p.T, C = p.C;
 
   if (tid == 0) {
-    *s_abort = *p.status;  // a previous CTA already gave up: do nothing
+    *s_abort = *p.status;  // an earlier CTA already gave up: do nothing
+    *s_giveup = 0;
     mbar_init(&bars[kBarProFull], 1);
-    mbar_init(&bars[kBarProReady], 128);
     mbar_init(&bars[kBarProMma], 1);
-    mbar_init(&bars[kBarProDone], 128);
+    mbar_init(&bars[kBarProDone], kSoftmaxThreads);
+    mbar_init(&bars[kBarXchg], kSoftmaxThreads);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars[kBarSFull + i], 1);
-      mbar_init(&bars[kBarPFull + i], 128);
-      mbar_init(&bars[kBarPvDone + i], 1);
+      mbar_init(&bars[kBarPFull + i], kSoftmaxThreads);
     }
-    for (int i = 0; i < ST; ++i) {
-      mbar_init(&kv_full[i], 1);
-      mbar_init(&kv_free[i], 1);
+    for (int i = 0; i < 4; ++i) mbar_init(&bars[kBarPlFull + i], kSoftmaxThreads);
+    for (int i = 0; i < NS; ++i) {
+      mbar_init(&slot_full[i], 1);
+      mbar_init(&slot_free[i], 1);
     }
     mbar_fence_init();
   }
   __syncthreads();
   if (*s_abort != 0) return;
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
   }
@@ -147,10 +187,16 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-
-  if (warp == 4) {
+  // Register re-balancing between warpgroups: the producer / MMA warpgroup keeps 40 registers
+  // per thread, the two softmax warpgroups grow to 232.
+  if (warp >= 8) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+  if (warp == 8) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
+#ifdef MVPA_TC_TRACE
+      const bool trace_on = true;
+#endif
       prefetch_tensormap(&maps.q);
       prefetch_tensormap(&maps.k);
       prefetch_tensormap(&maps.v);
@@ -162,269 +208,485 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
         tma_load_3d(sR + hh * HALF, &maps.rt, &bars[kBarProFull], hh * 64, 0, hk);
         tma_load_3d(sC + hh * CP * 128, &maps.rc, &bars[kBarProFull], hh * 64, 0, hk);
       }
-      bool ok = mbar_wait(&bars[kBarProDone], 0, p.status, 10);
-      for (int j = 0; ok && j < n_tiles; ++j) {
-        const int s = j % ST;
-        if (j >= ST) ok = mbar_wait(&kv_free[s], ((j / ST) - 1) & 1, p.status, 11);
-        if (!ok) break;
-        const bool light = tile_is_light(I, j, TPB, p.window, p.n_qt);
-        uint8_t* sK = ring + s * C_::STAGE;
-        uint8_t* sV = sK + TILE;
-        mbar_arrive_expect_tx(&kv_full[s], (light ? 1 : 2) * TILE);
-        for (int hh = 0; hh < NH; ++hh) {
-          if (!light) tma_load_5d(sK + hh * HALF, &maps.k, &kv_full[s], hh * 64, 0, j * TPB, hk, b);
-          tma_load_5d(sV + hh * HALF, &maps.v, &kv_full[s], hh * 64, 0, j * TPB, hk, b);
-        }
+      bool ok = true;
+      auto load_slot = [&](const CUtensorMap* map, int q, int J) {
+        if (q == C_::EARLY) ok = mbar_wait(&bars[kBarProDone], 0, p.status, 10);  // borrowed slots are back
+        const int sl = q % NS;
+        if (ok && q >= NS) ok = mbar_wait(&slot_free[sl], ((q / NS) - 1) & 1, p.status, 11);
+        if (!ok) return;
+        if (q < 16) TRACE(96 + q);
+        uint8_t* dst = ring + sl * TILE;
+        mbar_arrive_expect_tx(&slot_full[sl], TILE);
+#pragma unroll
+        for (int hh = 0; hh < NH; ++hh) tma_load_5d(dst + hh * HALF, map, &slot_full[sl], hh * 64, 0, J * TPB, hk, b);
+      };
+      for (int s = 0; ok && s < n_tiles; ++s) {
+        const int J = tile_of(s);
+        if (s < n_dense) load_slot(&maps.k, q_of_k(s), J);
+        if (ok) load_slot(&maps.v, q_of_v(s), J);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ------------------------------- MMA issuer -------------------------------
     if (lane == 0) {
+#ifdef MVPA_TC_TRACE
+      const bool trace_on = true;
+#endif
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0);
       constexpr uint32_t idesc_c = make_idesc_bf16(128, CP, 0);
       constexpr uint32_t idesc_o = make_idesc_bf16(128, D, 1);
-      bool ok = mbar_wait(&bars[kBarProReady], 0, p.status, 20);
+      bool ok = mbar_wait(&bars[kBarProFull], 0, p.status, 20);
       if (ok) {
         tc_fence_after();
-        for (int kk = 0; kk < KSTEPS; ++kk) {  // temporal scores, all T columns at once
+        const DescHalves dq = make_desc_halves_sw128(smem_u32(sQ), 16, 1024);
+        const DescHalves dr = make_desc_halves_sw128(smem_u32(sR), 16, 1024);
+        const DescHalves dc = make_desc_halves_sw128(smem_u32(sC), 16, 1024);
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk) {  // raw temporal products, all 128 columns at once
           const uint32_t off = (kk / 4) * HALF + (kk % 4) * 32;
-          mma_ss(tmem + kColTB, make_desc_sw128(smem_u32(sQv) + off, 16, 1024),
-                 make_desc_sw128(smem_u32(sR) + off, 16, 1024), idesc_s, kk > 0);
+          mma_ss_h(tmem + kColTB, dq, off, dr, off, idesc_s, kk > 0);
         }
-        for (int kk = 0; kk < KSTEPS; ++kk) {  // channel scores -> S0 columns [0, CP)
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk) {  // raw channel products -> S0 columns [0, CP)
           const uint32_t offa = (kk / 4) * HALF + (kk % 4) * 32;
           const uint32_t offb = (kk / 4) * (CP * 128) + (kk % 4) * 32;
-          mma_ss(tmem + kColS, make_desc_sw128(smem_u32(sQz) + offa, 16, 1024),
-                 make_desc_sw128(smem_u32(sC) + offb, 16, 1024), idesc_c, kk > 0);
+          mma_ss_h(tmem + kColS, dq, offa, dc, offb, idesc_c, kk > 0);
         }
         mma_commit(&bars[kBarProMma]);
-        ok = mbar_wait(&bars[kBarProDone], 0, p.status, 21);
+        ok = mbar_wait(&bars[kBarProDone], 0, p.status, 21);  // Q rewritten as (q+u) c2; S0 free
       }
-      auto issue_qk = [&](int j) {
-        if (tile_is_light(I, j, TPB, p.window, p.n_qt)) return;
-        const int s = j % ST;
-        ok = mbar_wait(&kv_full[s], (j / ST) & 1, p.status, 22);
+      // From here on the thread keeps running counters instead of recomputing tile -> slot maps:
+      // its instruction stream is latency-bound, and everything that is not an MMA costs tensor time.
+      const DescHalves dq = make_desc_halves_sw128(smem_u32(sQ), 16, 1024);
+      const DescHalves dk0 = make_desc_halves_sw128(smem_u32(ring), 16, 1024);
+      const DescHalves dv0 = make_desc_halves_sw128(smem_u32(ring), HALF, 1024);
+      const uint32_t a_full = smem_u32(slot_full), a_free = smem_u32(slot_free);
+      const uint32_t a_sfull = smem_u32(&bars[kBarSFull]), a_pfull = smem_u32(&bars[kBarPFull]);
+      const uint32_t a_plfull = smem_u32(&bars[kBarPlFull]);
+      // ring cursor of the next slot to be consumed (K and V slots are consumed in load order)
+      uint32_t k_sl = 0, k_par = 0;  // slot / parity of the next K (dense tiles only)
+      auto advance = [&](uint32_t& sl, uint32_t& par, int by) {
+        sl += by;
+        if (sl >= (uint32_t)NS) { sl -= NS; par ^= 1; }
+      };
+      auto issue_qk = [&](int s) {  // S_s = Q' K_s^T ; K_s sits in slot (2s) % NS
+        ok = mbar_wait_a(a_full + 8 * k_sl, k_par, p.status, 22);
         if (!ok) return;
         tc_fence_after();
-        const uint32_t sK = smem_u32(ring + s * C_::STAGE);
+        const uint32_t d_s = tmem + kColS + 128 * (s & 1);
+        const uint32_t klo = dk0.lo + k_sl * (TILE >> 4);
+#pragma unroll
         for (int kk = 0; kk < KSTEPS; ++kk) {
-          const uint32_t off = (kk / 4) * HALF + (kk % 4) * 32;
-          mma_ss(tmem + kColS + 128 * (j & 1), make_desc_sw128(smem_u32(sQ) + off, 16, 1024),
-                 make_desc_sw128(sK + off, 16, 1024), idesc_s, kk > 0);
+          const uint32_t off = ((kk / 4) * HALF + (kk % 4) * 32) >> 4;
+          DescHalves da = dq, db = dk0;
+          da.lo = dq.lo + off;
+          db.lo = klo + off;
+          mma_ss_h(d_s, da, 0, db, 0, idesc_s, kk > 0);
         }
-        mma_commit(&bars[kBarSFull + (j & 1)]);
+        mma_commit_a(a_sfull + 8 * (s & 1));
+        mma_commit_a(a_free + 8 * k_sl);
+        advance(k_sl, k_par, 2);
       };
-      if (ok) issue_qk(0);
-      for (int j = 0; ok && j < n_tiles; ++j) {
-        if (j + 1 < n_tiles) issue_qk(j + 1);
-        if (!ok) break;
-        const int s = j % ST;
-        ok = mbar_wait(&bars[kBarPFull + (j & 1)], (j >> 1) & 1, p.status, 23);
-        if (ok) ok = mbar_wait(&kv_full[s], (j / ST) & 1, p.status, 24);
+      if (ok && n_dense > 0) issue_qk(0);
+      // The completion of PV_s is signalled on the free-barrier of the V slot it read: the producer
+      // waits there to refill the slot, the softmax warps to reuse P columns / rescale O / finish.
+      // Issue blocks once about three MMAs are queued, so the look-ahead for the next tile sits
+      // between the two halves of a tile's MMAs, where queued work hides its latency.
+      uint32_t v_sl = 1 % NS, v_par = 0;  // slot / parity of V_s (V_0 is load 1)
+      if (ok) ok = mbar_wait_a(a_full + 8 * v_sl, v_par, p.status, 24);
+      bool pre_p = false;  // P of the coming tile already seen complete
+      // ---- dense tiles ----
+      for (int s = 0; ok && s < n_dense; ++s) {
+        if (s + 1 < n_dense) issue_qk(s + 1);  // S of the next tile first: its softmax is the long pole
+        if (ok && !pre_p) ok = mbar_wait_a(a_pfull + 8 * (s & 1), (s >> 1) & 1, p.status, 23);
+        if (s < 16) TRACE(64 + 2 * s);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t sV = smem_u32(ring + s * C_::STAGE + TILE);
-        for (int kk = 0; kk < 8; ++kk) {  // 128 keys, 16 per step; P read from TMEM
-          mma_ts(tmem + kColO, tmem + kColS + 128 * (j & 1) + kk * 8,
-                 make_desc_sw128(sV + kk * 2048, HALF, 1024), idesc_o, (j > 0 || kk > 0));
+        // P_s: two 32-column halves at the start of each warpgroup's S columns (stride 64)
+        const uint32_t a0 = tmem + kColS + 128 * (s & 1);
+        const uint32_t b_lo = dv0.lo + v_sl * (TILE >> 4);
+        mma_ts_x4(tmem + kColO, a0, b_lo, dv0.hi, 2048 >> 4, idesc_o, (uint32_t)(s > 0));
+        const uint32_t done_bar = a_free + 8 * v_sl;
+        // next V: a dense successor's V is two loads on, a light successor's one load on
+        advance(v_sl, v_par, s + 1 < n_dense ? 2 : 1);
+        pre_p = false;
+        if (s + 1 < n_tiles) {
+          // A blocking wait for P_{s+1} here could deadlock against a rescale that waits for PV_s;
+          // a peek cannot.  V_{s+1} only depends on older tiles.
+          pre_p = s + 1 < n_dense ? mbar_test_wait_a(a_pfull + 8 * ((s + 1) & 1), ((s + 1) >> 1) & 1)
+                                  : mbar_test_wait_a(a_plfull, 0);
+          ok = mbar_wait_a(a_full + 8 * v_sl, v_par, p.status, 24);
         }
-        mma_commit(&kv_free[s]);
-        mma_commit(&bars[kBarPvDone + (j & 1)]);
+        if (s < 16) TRACE(65 + 2 * s);
+        if (!ok) break;
+        mma_ts_x4(tmem + kColO, a0 + 64, b_lo + 4 * (2048 >> 4), dv0.hi, 2048 >> 4, idesc_o, 1u);
+        mma_commit_a(done_bar);
+        if (s < 24) TRACE(36 + s);
+      }
+      // ---- light tiles: P in four contiguous 64-column buffers ----
+      uint32_t pb = 0, pb_par = 0;
+      for (int l = 0; ok && l < n_light; ++l) {
+        if (!pre_p) ok = mbar_wait_a(a_plfull + 8 * pb, pb_par, p.status, 23);
+        if (n_dense + l < 16) TRACE(64 + 2 * (n_dense + l));
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a0 = tmem + kColS + 64 * pb;
+        const uint32_t b_lo = dv0.lo + v_sl * (TILE >> 4);
+        mma_ts_x4(tmem + kColO, a0, b_lo, dv0.hi, 2048 >> 4, idesc_o, 1u);
+        const uint32_t done_bar = a_free + 8 * v_sl;
+        advance(v_sl, v_par, 1);
+        pb = (pb + 1) & 3;
+        if (pb == 0) pb_par ^= 1;
+        pre_p = false;
+        if (l + 1 < n_light) {
+          pre_p = mbar_test_wait_a(a_plfull + 8 * pb, pb_par);
+          ok = mbar_wait_a(a_full + 8 * v_sl, v_par, p.status, 24);
+        }
+        if (n_dense + l < 16) TRACE(65 + 2 * (n_dense + l));
+        if (!ok) break;
+        mma_ts_x4(tmem + kColO, a0 + 32, b_lo + 4 * (2048 >> 4), dv0.hi, 2048 >> 4, idesc_o, 1u);
+        mma_commit_a(done_bar);
+        if (n_dense + l < 24) TRACE(36 + n_dense + l);
       }
     }
+  }
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
     // ------------------------------ softmax warps ------------------------------
-    const int r = tid;                       // query row of the tile == TMEM lane
-    const int ti_loc = r / CP, c_i = r % CP;
+#ifdef MVPA_TC_TRACE
+    const bool trace_on = tid == 0;
+#endif
+    TRACE(0);
+    const int row = tid & 127;               // query row of the tile == TMEM lane
+    const int wg = tid >> 7;                 // column half this thread owns
+    const int ti_loc = row / CP, c_i = row % CP;
     const int ti_abs = I * TPB + ti_loc;
     const bool row_valid = c_i < C && ti_abs < T;
-    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
-    for (int d = r; d < 3 * D; d += 128) {
+    const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    const int tt_base = (64 * wg) / CP;      // first tile-local time step of this thread's columns
+    const int ck_base = CP == 128 ? 64 * wg : 0;  // first channel slot of this thread's columns
+    for (int d = tid; d < 3 * D; d += kSoftmaxThreads) {
       const __nv_bfloat16* src = d < D ? p.u : (d < 2 * D ? p.vt : p.z);
       s_bias[d] = __bfloat162float(src[hk * D + d % D]);
     }
     softmax_bar();
     bool ok = warp_wait(&bars[kBarProFull], 0, p.status, 30);
+    TRACE(1);
     if (ok) {
-      // Q' = (q+u) c2 in place, (q+vt) c2 and (q+z) c2 beside it (`attentions/attn.py:180-183`)
-      for (int hh = 0; hh < NH; ++hh) {
+      // per-column constants of the two relative products: vt.r_time[j] and z.r_chan[j]
+      const bool is_t = tid < 128;
+      const int j = tid & 127;
+      if (is_t || j < CP) {
+        const uint8_t* base = is_t ? sR : sC;
+        const int half_bytes = is_t ? HALF : CP * 128;
+        const float4* bias4 = reinterpret_cast<const float4*>(s_bias + (is_t ? D : 2 * D));
+        float acc = 0.f;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const uint32_t off = hh * HALF + r * 128 + ((c ^ (r & 7)) << 4);
-          const uint4 raw = *reinterpret_cast<const uint4*>(sQ + off);
-          const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-          uint32_t ou[4], ov[4], oz[4];
+        for (int hh = 0; hh < NH; ++hh) {
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int d = hh * 64 + c * 8 + 2 * e;
-            const float x0 = __uint_as_float(w[e] << 16), x1 = __uint_as_float(w[e] & 0xffff0000u);
-            ou[e] = pack_bf16((x0 + s_bias[d]) * p.c2, (x1 + s_bias[d + 1]) * p.c2);
-            ov[e] = pack_bf16((x0 + s_bias[D + d]) * p.c2, (x1 + s_bias[D + d + 1]) * p.c2);
-            oz[e] = pack_bf16((x0 + s_bias[2 * D + d]) * p.c2, (x1 + s_bias[2 * D + d + 1]) * p.c2);
+          for (int c = 0; c < 8; ++c) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(base + hh * half_bytes + j * 128 + ((c ^ (j & 7)) << 4));
+            const float4 b0 = bias4[hh * 16 + c * 2], b1 = bias4[hh * 16 + c * 2 + 1];
+            acc += __uint_as_float(raw.x << 16) * b0.x + __uint_as_float(raw.x & 0xffff0000u) * b0.y +
+                   __uint_as_float(raw.y << 16) * b0.z + __uint_as_float(raw.y & 0xffff0000u) * b0.w +
+                   __uint_as_float(raw.z << 16) * b1.x + __uint_as_float(raw.z & 0xffff0000u) * b1.y +
+                   __uint_as_float(raw.w << 16) * b1.z + __uint_as_float(raw.w & 0xffff0000u) * b1.w;
           }
-          *reinterpret_cast<uint4*>(sQ + off) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
-          *reinterpret_cast<uint4*>(sQv + off) = make_uint4(ov[0], ov[1], ov[2], ov[3]);
-          *reinterpret_cast<uint4*>(sQz + off) = make_uint4(oz[0], oz[1], oz[2], oz[3]);
         }
+        (is_t ? s_vr : s_zc)[j] = acc;
       }
-      fence_proxy_async_smem();
-      mbar_arrive(&bars[kBarProReady]);
       ok = warp_wait(&bars[kBarProMma], 0, p.status, 31);
     }
-    // Channel scores of this row, gathered by |c_i - c_k|, relative to their maximum, as fp16x2.
-    __half2 cbl[CP / 2];
-    float mc = 0.f;
+    TRACE(2);
+    softmax_bar();  // every thread is done reading sR / sC; the scratch may overwrite them
+    // Channel scores of the row, c2 (q.r_chan[j] + z.r_chan[j]), parked in shared memory in
+    // 32-column chunks (split between the warpgroups) for the per-row gather below.
     if (ok) {
       tc_fence_after();
 #pragma unroll
-      for (int c0 = 0; c0 < CP; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld32(lane_base + kColS + c0, v);
-        tmem_ld_wait();
+      for (int ci = 0; ci < CP / 32; ++ci) {
+        if ((ci & 1) == wg) {
+          uint32_t v[32];
+          tmem_ld32(lane_base + kColS + ci * 32, v);
+          tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) scratch[r * LDC + c0 + j] = __uint_as_float(v[j]);
+          for (int j4 = 0; j4 < 8; ++j4) {
+            const float4 zc = reinterpret_cast<const float4*>(s_zc)[ci * 8 + j4];
+            const float zz[4] = {zc.x, zc.y, zc.z, zc.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int jj = j4 * 4 + e;
+              scratch[row * CP + ((ci * 32 + jj + 2 * row) & (CP - 1))] = p.c2 * (__uint_as_float(v[jj]) + zz[e]);
+            }
+          }
+        }
       }
       tc_fence_before();
+    }
+    softmax_bar();  // scratch complete; the MMAs no longer need the raw Q tile
+    TRACE(3);
+    // Gathered by |c_i - c_k| for this thread's columns:
+    //   cbl = cb - max (fp16x2, log2 domain) for dense tiles,  bc = exp2(cbl) (bf16x2) for light tiles.
+    __half2 cbl[NCH / 2];
+    uint32_t bc[NCH / 2];
+    float mc = 0.f, sum_bc = 0.f;
+    {
+      float g[NCH];
       float mx = -INFINITY;
-      if (c_i < C)
-        for (int ck = 0; ck < C; ++ck) mx = fmaxf(mx, scratch[r * LDC + (C - 1 - abs(c_i - ck))]);
-      mc = (mx == -INFINITY) ? 0.f : mx;
+      if (ok) {
 #pragma unroll
-      for (int k2 = 0; k2 < CP / 2; ++k2) {
-        float x[2];
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int ck = 2 * k2 + e;
-          x[e] = (c_i < C && ck < C) ? scratch[r * LDC + (C - 1 - abs(c_i - ck))] - mc : -INFINITY;
+        for (int k = 0; k < NCH; ++k) {
+          const int ck = ck_base + k;
+          const int jc = min(max(C - 1 - abs(c_i - ck), 0), CP - 1);
+          const float val = scratch[row * CP + ((jc + 2 * row) & (CP - 1))];  // rows rotated: no bank conflicts on the (anti)diagonal
+          g[k] = (c_i < C && ck < C) ? val : -INFINITY;
+          mx = fmaxf(mx, g[k]);
         }
-        cbl[k2] = __floats2half2_rn(x[0], x[1]);
+      }
+      // the row maximum spans both warpgroups' columns when CP = 128
+      s_max[wg * 128 + row] = mx;
+      softmax_bar();
+      mx = fmaxf(mx, s_max[(wg ^ 1) * 128 + row]);
+      mc = (mx == -INFINITY) ? 0.f : mx;
+      if (ok) {
+#pragma unroll
+        for (int k2 = 0; k2 < NCH / 2; ++k2) {
+          const float x0 = g[2 * k2] - mc, x1 = g[2 * k2 + 1] - mc;
+          cbl[k2] = __floats2half2_rn(x0, x1);
+          bc[k2] = pack_bf16(ex2(x0), ex2(x1));
+          sum_bc += __uint_as_float(bc[k2] << 16) + __uint_as_float(bc[k2] & 0xffff0000u);
+        }
+        // Q' = (q+u) c2 in place (`attentions/attn.py:180-183`); each warpgroup converts half of the chunks
+        const float4* u4 = reinterpret_cast<const float4*>(s_bias);
+#pragma unroll
+        for (int cc = 0; cc < D / 16; ++cc) {
+          const int chunk = wg * (D / 16) + cc, hh = chunk / 8, c = chunk % 8;
+          const uint32_t off = hh * HALF + row * 128 + ((c ^ (row & 7)) << 4);
+          const uint4 raw = *reinterpret_cast<const uint4*>(sQ + off);
+          const float4 b0 = u4[chunk * 2], b1 = u4[chunk * 2 + 1];
+          uint4 out;
+          out.x = pack_bf16((__uint_as_float(raw.x << 16) + b0.x) * p.c2, (__uint_as_float(raw.x & 0xffff0000u) + b0.y) * p.c2);
+          out.y = pack_bf16((__uint_as_float(raw.y << 16) + b0.z) * p.c2, (__uint_as_float(raw.y & 0xffff0000u) + b0.w) * p.c2);
+          out.z = pack_bf16((__uint_as_float(raw.z << 16) + b1.x) * p.c2, (__uint_as_float(raw.z & 0xffff0000u) + b1.y) * p.c2);
+          out.w = pack_bf16((__uint_as_float(raw.w << 16) + b1.z) * p.c2, (__uint_as_float(raw.w & 0xffff0000u) + b1.w) * p.c2);
+          *reinterpret_cast<uint4*>(sQ + off) = out;
+        }
+        fence_proxy_async_smem();
       }
     }
-    mbar_arrive(&bars[kBarProDone]);  // ring and S0 may be overwritten from here on
+    mbar_arrive(&bars[kBarProDone]);  // borrowed ring stages, S0 and the rewritten Q are ready
+    TRACE(4);
 
     float m_used = -INFINITY, l_sum = 0.f;
-    int dense_seen[2] = {0, 0};
-    for (int j = 0; ok && j < n_tiles; ++j) {
-      const int buf = j & 1;
-      const bool light = tile_is_light(I, j, TPB, p.window, p.n_qt);
-      const uint32_t s_addr = lane_base + kColS + 128 * buf;
-      // per key time step of the tile: temporal score, validity, content on/off
-      float tbv[TPB], wmul[TPB];
-      bool valid[TPB];
-      {
-        uint32_t raw[TPB];
+
+    // O and l follow the running maximum only when it moved by more than 2^8.  Needs every PV
+    // product issued so far (tiles < s) to be complete; they execute in order, so the last one is
+    // enough.  Returns false if the wait ran out.
+    auto maybe_rescale = [&](int s, float m_tile) -> bool {
+      const bool need = m_tile > m_used + kRescaleThreshold;
+      if (!__any_sync(0xffffffffu, need)) return true;
+      const int qp = q_of_v(s - 1);
+      if (!warp_wait(&slot_free[qp % NS], (qp / NS) & 1, p.status, 33)) return false;
+      tc_fence_after();
+      const float alpha = need ? ex2(m_used - m_tile) : 1.f;
 #pragma unroll
-        for (int tt = 0; tt < TPB; ++tt) {
-          const int tk_abs = j * TPB + tt, dt = ti_abs - tk_abs;
-          valid[tt] = dt >= 0 && tk_abs < T;
-          wmul[tt] = (p.window > 0 && dt > p.window && ti_abs != T - 1) ? 0.f : 1.f;
-          const int dtc = min(max(dt, 0), T - 1);
-          tmem_ld1(lane_base + kColTB + (T - 1 - dtc), raw[tt]);
-        }
+      for (int c0 = 0; c0 < DW; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld32(lane_base + kColO + wg * DW + c0, v);
         tmem_ld_wait();
 #pragma unroll
-        for (int tt = 0; tt < TPB; ++tt) tbv[tt] = __uint_as_float(raw[tt]) + mc;
+        for (int jj = 0; jj < 32; ++jj) v[jj] = __float_as_uint(__uint_as_float(v[jj]) * alpha);
+        tmem_st32(lane_base + kColO + wg * DW + c0, v);
       }
-      float gmax[TPB];
-      if (!light) {
-        ok = warp_wait(&bars[kBarSFull + buf], dense_seen[buf] & 1, p.status, 32);
-        if (!ok) break;
-        ++dense_seen[buf];
+      tmem_st_wait();
+      l_sum *= alpha;
+      if (need) m_used = m_tile;
+      return true;
+    };
+    // temporal scores of the TPB key time steps of tile J, in log2 units, plus the channel maximum
+    auto load_tb = [&](int J, float (&tb_all)[TPB], bool (&valid_all)[TPB]) {
+      uint32_t raw[TPB];
+      int colj[TPB];
+#pragma unroll
+      for (int tt = 0; tt < TPB; ++tt) {
+        const int tk_abs = J * TPB + tt, dt = ti_abs - tk_abs;
+        valid_all[tt] = dt >= 0 && tk_abs < T;
+        colj[tt] = T - 1 - min(max(dt, 0), T - 1);
+        tmem_ld1(lane_base + kColTB + colj[tt], raw[tt]);
+      }
+      tmem_ld_wait();
+#pragma unroll
+      for (int tt = 0; tt < TPB; ++tt) tb_all[tt] = p.c2 * (__uint_as_float(raw[tt]) + s_vr[colj[tt]]) + mc;
+    };
+
+    // ------------------------------ dense tiles ------------------------------
+    // Abort protocol: this loop contains a named barrier, which must never lose a participant.
+    // A warp whose bounded wait runs out raises s_giveup, stops touching TMEM, and keeps walking
+    // to the next named barrier; there every warp sees the flag and all leave together.
+    for (int s = 0; s < n_dense; ++s) {
+      const int buf = s & 1;
+      const int J = tile_of(s);
+      const uint32_t s_addr = lane_base + kColS + 128 * buf + 64 * wg;
+      float tb_all[TPB];
+      bool valid_all[TPB];
+#pragma unroll
+      for (int tt = 0; tt < TPB; ++tt) { tb_all[tt] = 0.f; valid_all[tt] = false; }
+      if (ok) load_tb(J, tb_all, valid_all);
+      float tbv[TPW], wmul[TPW];
+      bool valid[TPW];
+#pragma unroll
+      for (int tl = 0; tl < TPW; ++tl) {
+        const int tt = tt_base + tl;
+        float tsel = 0.f;
+        bool vsel = false;
+#pragma unroll
+        for (int q = 0; q < TPB; ++q)  // compile-time indices keep tb_all in registers
+          if (q == tt) { tsel = tb_all[q]; vsel = valid_all[q]; }
+        tbv[tl] = tsel;
+        valid[tl] = vsel;
+        const int dt = ti_abs - (J * TPB + tt);
+        wmul[tl] = (p.window > 0 && dt > p.window && ti_abs != T - 1) ? 0.f : 1.f;
+      }
+      float sreg[64];
+      if (ok && !warp_wait(&bars[kBarSFull + buf], (s >> 1) & 1, p.status, 32)) ok = false;
+      float m_part = -INFINITY;
+      if (ok) {
         tc_fence_after();
+        uint32_t v0[32], v1[32];
+        tmem_ld32(s_addr, v0);
+        tmem_ld32(s_addr + 32, v1);
+        tmem_ld_wait();
 #pragma unroll
-        for (int tt = 0; tt < TPB; ++tt) gmax[tt] = -INFINITY;
-#pragma unroll
-        for (int c0 = 0; c0 < 128; c0 += 32) {
-          uint32_t v[32];
-          tmem_ld32(s_addr + c0, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int jj = 0; jj < 32; jj += 2) {
-            const int col = c0 + jj, tt = col / CP, ck = col % CP;
-            const float2 cb = __half22float2(cbl[ck / 2]);
-            gmax[tt] = fmaxf(gmax[tt], fmaf(__uint_as_float(v[jj]), wmul[tt], cb.x));
-            gmax[tt] = fmaxf(gmax[tt], fmaf(__uint_as_float(v[jj + 1]), wmul[tt], cb.y));
-          }
+        for (int jj = 0; jj < 32; ++jj) {
+          sreg[jj] = __uint_as_float(v0[jj]);
+          sreg[32 + jj] = __uint_as_float(v1[jj]);
         }
-      } else {
+        float gmax[TPW];
 #pragma unroll
-        for (int tt = 0; tt < TPB; ++tt) gmax[tt] = 0.f;  // max of (cb - mc) over the row's channels
+        for (int tl = 0; tl < TPW; ++tl) gmax[tl] = -INFINITY;
+#pragma unroll
+        for (int lc = 0; lc < 64; lc += 2) {
+          const int tl = lc / CP, k2 = (lc % NCH) / 2;
+          const float2 cb = __half22float2(cbl[k2]);
+          sreg[lc] = fmaf(sreg[lc], wmul[tl], cb.x);
+          sreg[lc + 1] = fmaf(sreg[lc + 1], wmul[tl], cb.y);
+          gmax[tl] = fmaxf(gmax[tl], fmaxf(sreg[lc], sreg[lc + 1]));
+        }
+#pragma unroll
+        for (int tl = 0; tl < TPW; ++tl)
+          if (valid[tl]) m_part = fmaxf(m_part, gmax[tl] + tbv[tl]);
       }
-      float m_tile = -INFINITY;
-#pragma unroll
-      for (int tt = 0; tt < TPB; ++tt)
-        if (valid[tt]) m_tile = fmaxf(m_tile, gmax[tt] + tbv[tt]);
-      if (j == 0) {
+      // the two column halves of a row must agree on the tile maximum
+      s_max[(buf * 2 + wg) * 128 + row] = m_part;
+      if (!ok) *s_giveup = 1;
+      softmax_bar();
+      if (*s_giveup != 0) { ok = false; break; }  // some warp's wait ran out: everyone leaves together
+      const float m_tile = fmaxf(m_part, s_max[(buf * 2 + (wg ^ 1)) * 128 + row]);
+      if (s == 0) {
         m_used = (m_tile == -INFINITY) ? 0.f : m_tile;
-      } else {
-        const bool need = m_tile > m_used + kRescaleThreshold;
-        if (__any_sync(0xffffffffu, need)) {
-          // O and l follow the maximum only when it moved by more than 2^8
-          ok = warp_wait(&bars[kBarPvDone + ((j - 1) & 1)], ((j - 1) >> 1) & 1, p.status, 33);
-          if (!ok) break;
-          tc_fence_after();
-          const float alpha = need ? ex2(m_used - m_tile) : 1.f;
-#pragma unroll
-          for (int c0 = 0; c0 < D; c0 += 32) {
-            uint32_t v[32];
-            tmem_ld32(lane_base + kColO + c0, v);
-            tmem_ld_wait();
-#pragma unroll
-            for (int jj = 0; jj < 32; ++jj) v[jj] = __float_as_uint(__uint_as_float(v[jj]) * alpha);
-            tmem_st32(lane_base + kColO + c0, v);
-          }
-          tmem_st_wait();
-          l_sum *= alpha;
-          if (need) m_used = m_tile;
-        }
+      } else if (!maybe_rescale(s, m_tile)) {
+        ok = false;
+        continue;
       }
-      if (j >= 2) {
-        // P_j reuses the columns of P_{j-2}: the PV product that reads those must have finished.
-        // (For a dense tile S_full already implies it; a light tile has no other wait.)
-        ok = warp_wait(&bars[kBarPvDone + buf], ((j - 2) >> 1) & 1, p.status, 35);
-        if (!ok) break;
-        tc_fence_after();
-      }
-      float negmu[TPB];
+      // (P_s reuses the columns of S_s / P_{s-2}; S_full of this tile already implies PV_{s-2} is done)
+      float negmu[TPW];
 #pragma unroll
-      for (int tt = 0; tt < TPB; ++tt) negmu[tt] = valid[tt] ? tbv[tt] - m_used : -INFINITY;
+      for (int tl = 0; tl < TPW; ++tl) negmu[tl] = valid[tl] ? tbv[tl] - m_used : -INFINITY;
       float psum = 0.f;
+      uint32_t lo[16], hi[16];
 #pragma unroll
-      for (int c0 = 0; c0 < 128; c0 += 32) {
-        uint32_t v[32];
-        if (!light) {
-          tmem_ld32(s_addr + c0, v);
-          tmem_ld_wait();
-        }
-        uint32_t pk[16];
-#pragma unroll
-        for (int jj = 0; jj < 32; jj += 2) {
-          const int col = c0 + jj, tt = col / CP, ck = col % CP;
-          const float2 cb = __half22float2(cbl[ck / 2]);
-          const float s0 = light ? cb.x : fmaf(__uint_as_float(v[jj]), wmul[tt], cb.x);
-          const float s1 = light ? cb.y : fmaf(__uint_as_float(v[jj + 1]), wmul[tt], cb.y);
-          const float p0 = ex2(s0 + negmu[tt]), p1 = ex2(s1 + negmu[tt]);
-          psum += p0 + p1;
-          pk[jj / 2] = pack_bf16(p0, p1);
-        }
-        tmem_st16(s_addr + c0 / 2, pk);  // P (bf16) overwrites the S columns already consumed
+      for (int lc = 0; lc < 64; lc += 2) {
+        const int tl = lc / CP;
+        const float p0 = ex2(sreg[lc] + negmu[tl]), p1 = ex2(sreg[lc + 1] + negmu[tl]);
+        psum += p0 + p1;
+        if (lc < 32) lo[lc / 2] = pack_bf16(p0, p1);
+        else hi[lc / 2 - 16] = pack_bf16(p0, p1);
       }
       l_sum += psum;
+      tmem_st16(s_addr, lo);  // P (bf16) over this thread's own, already consumed S columns
+      tmem_st16(s_addr + 16, hi);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bars[kBarPFull + buf]);
+      if (s < 24) TRACE(8 + s);
+    }
+
+    // ------------------------------ light tiles ------------------------------
+    // P[i,k] = a_i[t_k] * bc_i[c_k]: one exponential per (row, key time step), packed bf16
+    // multiplies for the rest.  Four P buffers of 64 TMEM columns (the idle S columns) let these
+    // warps run ahead of the PV products.
+    if (ok && n_light > 0) {
+      // the buffers overlap S0 / S1: the last dense PV products must be done with them
+      const int q1 = q_of_v(n_dense - 1);
+      ok = warp_wait(&slot_free[q1 % NS], (q1 / NS) & 1, p.status, 37);
+      tc_fence_after();
+    }
+    for (int l = 0; ok && l < n_light; ++l) {
+      const int s = n_dense + l;
+      float tb_all[TPB];
+      bool valid_all[TPB];
+      load_tb(l, tb_all, valid_all);
+      if (s >= 12 && s < 16) TRACE(112 + 4 * (s - 12));
+      float m_tile = -INFINITY;
+#pragma unroll
+      for (int tt = 0; tt < TPB; ++tt)
+        if (valid_all[tt]) m_tile = fmaxf(m_tile, tb_all[tt]);  // max over channels of (cb - mc) is 0
+      if (!maybe_rescale(s, m_tile)) { ok = false; break; }
+      if (l >= 4) {
+        // this buffer last held P of light tile l-4: its PV product frees the V slot it read
+        const int q = q_of_v(s - 4);
+        ok = warp_wait(&slot_free[q % NS], (q / NS) & 1, p.status, 35);
+        if (!ok) break;
+        tc_fence_after();
+      }
+      if (s >= 12 && s < 16) TRACE(113 + 4 * (s - 12));
+      uint32_t lo[16], hi[16];
+#pragma unroll
+      for (int tl = 0; tl < TPW; ++tl) {
+        const int tt = tt_base + tl;
+        float tsel = 0.f;
+        bool vsel = false;
+#pragma unroll
+        for (int q = 0; q < TPB; ++q)
+          if (q == tt) { tsel = tb_all[q]; vsel = valid_all[q]; }
+        const float a = vsel ? ex2(tsel - m_used) : 0.f;
+        const uint32_t a2 = pack_bf16(a, a);
+        l_sum += __uint_as_float(a2 << 16) * sum_bc;
+#pragma unroll
+        for (int k2 = 0; k2 < NCH / 2; ++k2) {
+          const int idx = tl * (NCH / 2) + k2;
+          if (idx < 16) lo[idx] = hmul2_bf16(a2, bc[k2]);
+          else hi[idx - 16] = hmul2_bf16(a2, bc[k2]);
+        }
+      }
+      const uint32_t p_addr = lane_base + kColS + 64 * (l & 3) + 32 * wg;
+      tmem_st16(p_addr, lo);
+      tmem_st16(p_addr + 16, hi);
+      if (s >= 12 && s < 16) TRACE(114 + 4 * (s - 12));
+      tmem_st_wait();
+      if (s >= 12 && s < 16) TRACE(115 + 4 * (s - 12));
+      tc_fence_before();
+      mbar_arrive(&bars[kBarPlFull + (l & 3)]);
+      if (s < 24) TRACE(8 + s);
     }
     // ------------------------------- epilogue ---------------------------------
-    if (ok) ok = warp_wait(&bars[kBarPvDone + ((n_tiles - 1) & 1)], ((n_tiles - 1) >> 1) & 1, p.status, 34);
+    if (ok) {
+      const int ql = q_of_v(n_tiles - 1);
+      ok = warp_wait(&slot_free[ql % NS], (ql / NS) & 1, p.status, 34);
+    }
+    TRACE(5);
+    s_lsum[wg * 128 + row] = l_sum;
+    softmax_bar();
+    l_sum = s_lsum[row] + s_lsum[128 + row];
     if (ok) {
       tc_fence_after();
       const float inv = 1.f / l_sum;
       const int64_t n = (int64_t)ti_abs * C + c_i;
-      __nv_bfloat16* orow = p.o + b * p.o_sb + h * p.o_sh + n * p.o_sn;
+      __nv_bfloat16* orow = p.o + b * p.o_sb + h * p.o_sh + n * p.o_sn + wg * DW;
 #pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 32) {
+      for (int c0 = 0; c0 < DW; c0 += 32) {
         uint32_t v[32];
-        tmem_ld32(lane_base + kColO + c0, v);
+        tmem_ld32(lane_base + kColO + wg * DW + c0, v);
         tmem_ld_wait();
         if (row_valid) {
 #pragma unroll
@@ -437,12 +699,13 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
           }
         }
       }
-      if (row_valid && p.lse != nullptr) p.lse[(int64_t)bh * T * C + n] = m_used + log2f(l_sum);
+      if (wg == 0 && row_valid && p.lse != nullptr) p.lse[(int64_t)bh * T * C + n] = m_used + log2f(l_sum);
     }
+    TRACE(6);
     tc_fence_before();
   }
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem, kTmemCols);
   }
@@ -500,8 +763,10 @@ int launch(const Args& a, int* status, cudaStream_t s) {
   t.n_qt = (a.T + TPB - 1) / TPB;
   t.c2 = a.c2;
   t.status = status;
+  t.trace = reinterpret_cast<long long*>(status) + 32;  // workspace + 256 bytes (MVPA_TC_TRACE builds only)
   constexpr int smem = Cfg<D>::SMEM_BYTES;
   static_assert(smem <= 232448, "shared memory budget");
+  static_assert(Cfg<D>::EARLY >= 2, "the first tile's K and V load while the prologue runs");
   MVPA_CUDA_CHECK(cudaFuncSetAttribute(tc_fwd_kernel<D, CP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   MVPA_CUDA_CHECK(cudaMemsetAsync(status, 0, sizeof(int), s));
   const unsigned grid = (unsigned)t.n_qt * a.B * a.H;
@@ -519,7 +784,11 @@ bool tc_fwd_supported(const Args& a) {
 
 size_t tc_fwd_workspace_bytes(const mvpa_problem* p) {
   const bool tc = (p->D == 64 || p->D == 128) && p->C <= 128 && p->T <= 128;
+#ifdef MVPA_TC_TRACE
+  return tc ? 256 + (size_t)p->T * p->B * p->H * 1024 : 0;
+#else
   return tc ? 256 : 0;  // the kernel status word (bounded waits report here)
+#endif
 }
 
 int tc_fwd(const Args& a, void* workspace, size_t workspace_bytes, cudaStream_t s) {

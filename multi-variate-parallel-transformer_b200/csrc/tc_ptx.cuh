@@ -44,13 +44,59 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait.  On time-out stores `code` to *status (first writer wins) and returns false.
+// A phase that has already completed is caught by the non-suspending test first.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+  if (mbar_test_wait(bar, parity)) return true;
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
   }
   if (status != nullptr) atomicCAS(status, 0, code);
   return false;
+}
+
+// Variants on a shared-space address (the MMA-issuing thread keeps barrier addresses as integers
+// so that no generic-to-shared conversion sits in its instruction stream).
+__device__ __forceinline__ bool mbar_test_wait_a(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_a(uint32_t bar, uint32_t parity, int* status, int code) {
+  if (mbar_test_wait_a(bar, parity)) return true;
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  if (status != nullptr) atomicCAS(status, 0, code);
+  return false;
+}
+__device__ __forceinline__ void mma_commit_a(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
 // --------------------------------- TMA --------------------------------------
@@ -191,6 +237,64 @@ __device__ __forceinline__ uint64_t make_desc_sw128(uint32_t smem_addr, uint32_t
   d |= (uint64_t)1 << 46;
   d |= (uint64_t)2 << 61;
   return d;
+}
+
+// The same descriptor split into 32-bit halves: the low word carries the start address (and LBO),
+// so stepping through a tile is one 32-bit add per MMA instead of rebuilding 64 bits.
+struct DescHalves {
+  uint32_t lo, hi;
+};
+__device__ __forceinline__ DescHalves make_desc_halves_sw128(uint32_t smem_addr, uint32_t lbo_bytes,
+                                                             uint32_t sbo_bytes) {
+  DescHalves d;
+  d.lo = ((smem_addr >> 4) & 0x3FFF) | (((lbo_bytes >> 4) & 0x3FFF) << 16);
+  d.hi = ((sbo_bytes >> 4) & 0x3FFF) | (1u << 14) | (2u << 29);
+  return d;
+}
+__device__ __forceinline__ void mma_ss_h(uint32_t d_tmem, DescHalves a, uint32_t a_off_bytes, DescHalves b,
+                                         uint32_t b_off_bytes, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}" ::"r"(d_tmem),
+      "r"(a.lo + (a_off_bytes >> 4)), "r"(a.hi), "r"(b.lo + (b_off_bytes >> 4)), "r"(b.hi), "r"(idesc),
+      "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_ts_h(uint32_t d_tmem, uint32_t a_tmem, DescHalves b, uint32_t b_off_bytes,
+                                         uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "r"(b.lo + (b_off_bytes >> 4)), "r"(b.hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Four consecutive K-steps of  D[tmem] (+)= A[tmem] * B[smem]  in one instruction block: the
+// issuing thread is latency-bound, so everything but the MMAs themselves is kept out of its way.
+// A: 16 keys = 8 packed bf16x2 columns per step.  B: MN-major, `b_step16` descriptor units
+// (16-byte units) per step, starting at descriptor low word `b_lo`.
+__device__ __forceinline__ void mma_ts_x4(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
+                                          uint32_t b_step16, uint32_t idesc, uint32_t accumulate_first) {
+  asm volatile(
+      "{\n\t.reg .pred p0, p1;\n\t.reg .b64 db;\n\t.reg .b32 lo;\n\t"
+      "setp.ne.b32 p0, %6, 0;\n\t"
+      "setp.eq.b32 p1, 0, 0;\n\t"
+      "mov.b32 lo, %2;\n\t"
+      "mov.b64 db, {lo, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %5, p0;\n\t"
+      "add.u32 lo, lo, %4;\n\t mov.b64 db, {lo, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1 + 8], db, %5, p1;\n\t"
+      "add.u32 lo, lo, %4;\n\t mov.b64 db, {lo, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1 + 16], db, %5, p1;\n\t"
+      "add.u32 lo, lo, %4;\n\t mov.b64 db, {lo, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1 + 24], db, %5, p1;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(b_step16), "r"(idesc), "r"(accumulate_first)
+      : "memory");
 }
 
 // Instruction descriptor for kind::f16 with bf16 A/B and fp32 accumulation.

@@ -17,7 +17,9 @@ import threading
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _CSRC = os.path.join(_HERE, "csrc")
 _INCLUDE = os.path.join(os.path.dirname(_HERE), "include")
-LIB_PATH = os.path.join(_HERE, "libmvpa_b200.so")
+# MVPA_B200_LIB: load a library built elsewhere (e.g. an instrumented build) instead of the in-tree one.
+_OVERRIDE = os.environ.get("MVPA_B200_LIB")
+LIB_PATH = _OVERRIDE or os.path.join(_HERE, "libmvpa_b200.so")
 HASH_PATH = LIB_PATH + ".srchash"
 
 NVCC_FLAGS = [
@@ -47,6 +49,8 @@ def _source_hash() -> str:
 
 
 def _stale() -> bool:
+    if _OVERRIDE:
+        return False
     if not (os.path.exists(LIB_PATH) and os.path.exists(HASH_PATH)):
         return True
     with open(HASH_PATH) as f:
