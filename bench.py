@@ -61,39 +61,67 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clocks and throttle reasons through NVML while the timed region runs (a thread
+    in this process, every 2 ms); falls back to one `nvidia-smi` query if NVML is missing."""
 
     def __init__(self, index):
-        self.rows, self.proc, self.index = [], None, index
+        self.index, self.rows, self.stop, self.thread, self.max_mhz = index, [], False, None, None
 
     def __enter__(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self._physical_index())
+            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            masks = {"hw_slowdown": nv.nvmlClocksEventReasonHwSlowdown,
+                     "hw_thermal_slowdown": nv.nvmlClocksEventReasonHwThermalSlowdown,
+                     "sw_thermal_slowdown": nv.nvmlClocksEventReasonSwThermalSlowdown,
+                     "sw_power_cap": nv.nvmlClocksEventReasonSwPowerCap}
+
+            def loop():
+                while not self.stop:
+                    try:
+                        mhz = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+                        try:
+                            r = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+                        except Exception:
+                            r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                        self.rows.append((float(mhz), [n for n, m in masks.items() if r & m]))
+                    except Exception:
+                        pass
+                    time.sleep(0.002)
+
+            self.thread = threading.Thread(target=loop, daemon=True)
             self.thread.start()
-        except OSError:
-            self.proc = None
+        except Exception:
+            self.thread = None
         return self
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([x.strip() for x in line.split(",")])
+    def _physical_index(self):
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [x for x in vis.split(",") if x.strip() != ""]
+            if self.index < len(ids) and ids[self.index].strip().isdigit():
+                return int(ids[self.index])
+        return self.index
 
     def __exit__(self, *a):
-        if self.proc is not None:
-            self.proc.terminate()
+        self.stop = True
+        if self.thread is not None:
             self.thread.join(timeout=2)
 
     def summary(self):
-        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
-        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = sorted({n for r in self.rows if len(r) >= 6 for n, v in zip(names, r[2:6]) if v == "Active"})
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+        if not self.rows:
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=clocks.sm,clocks.max.sm",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True).stdout
+                a, b = (float(x) for x in out.strip().split(","))
+                return {"sm_mhz": a, "sm_max_mhz": b, "reasons": [], "samples": 0, "note": "idle nvidia-smi query"}
+            except Exception:
+                return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        sm = [r[0] for r in self.rows]
+        reasons = sorted({n for r in self.rows for n in r[1]})
+        return {"sm_mhz": statistics.median(sm), "sm_min_mhz": min(sm), "sm_max_mhz": self.max_mhz,
                 "reasons": reasons, "samples": len(sm)}
 
 
@@ -176,7 +204,7 @@ def time_kernel(torch, attentions, t, w, steps, warmup, flush):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS),
@@ -215,11 +243,13 @@ def main():
     # ---- device-resident throughput ----
     sync_all()
     n0 = lib.mvpa_launch_count()
-    with ClockSampler(local) as clk:
-        sync_all()
-        ms = time_kernel(torch, attentions, t, w, args.steps, args.warmup, flush)
-        sync_all()
-    launches = lib.mvpa_launch_count() - n0 - args.warmup
+    clk = ClockSampler(local)
+    clk.__enter__()
+    sync_all()
+    ms = time_kernel(torch, attentions, t, w, args.steps, args.warmup, flush)
+    sync_all()
+    per_call = (lib.mvpa_launch_count() - n0) // (args.steps + args.warmup)  # kernels of the library per call
+    launches = per_call * args.steps
     total_ms = torch.tensor([sum(ms)], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
@@ -247,6 +277,7 @@ def main():
         e2e_step()
     b.record()
     sync_all()
+    clk.__exit__()
     e2e_ms = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)

@@ -62,6 +62,7 @@ struct TcArgs {
   int B, H, Hkv, T, C, g, window, n_qt;
   float c2;
   int* status;
+  const float* relc;  // (Hkv, 256): vt.r_time[j] at [0,128), z.r_chan[j] at [128,256)
   long long* trace;
 };
 
@@ -112,6 +113,30 @@ __device__ __forceinline__ int light_tiles(int I, int TPB, int window, int n_qt)
   if (window <= 0 || I == n_qt - 1) return 0;  // the last tile holds the row t = T-1 that sees all
   const int x = I * TPB - TPB - window;
   return x < 0 ? 0 : x / TPB + 1;
+}
+
+// Per-column constants of the two relative products, once per kv head instead of once per CTA:
+//   relc[hk][j] = vt[hk] . r_time[hk][j]  (j < T),   relc[hk][128 + j] = z[hk] . r_chan[hk][j]  (j < C)
+// (the bias halves of `_rel_bias`, `attentions/attn.py:1308-1313`).
+__global__ void __launch_bounds__(256) rel_const_kernel(const __nv_bfloat16* __restrict__ vt,
+                                                        const __nv_bfloat16* __restrict__ z,
+                                                        const __nv_bfloat16* __restrict__ rt,
+                                                        const __nv_bfloat16* __restrict__ rc, float* __restrict__ relc,
+                                                        int T, int C, int D) {
+  const int hk = blockIdx.x, j = threadIdx.x & 127;
+  const bool is_t = threadIdx.x < 128;
+  const int rows = is_t ? T : C;
+  float acc = 0.f;
+  if (j < rows) {
+    const __nv_bfloat16* key = (is_t ? rt : rc) + ((size_t)hk * rows + j) * D;
+    const __nv_bfloat16* bias = (is_t ? vt : z) + (size_t)hk * D;
+    for (int d = 0; d < D; d += 2) {
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(key + d));
+      const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(bias + d));
+      acc += a.x * b.x + a.y * b.y;
+    }
+  }
+  relc[hk * 256 + threadIdx.x] = acc;
 }
 
 template <int D, int CP>
@@ -292,8 +317,13 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
       // waits there to refill the slot, the softmax warps to reuse P columns / rescale O / finish.
       // Issue blocks once about three MMAs are queued, so the look-ahead for the next tile sits
       // between the two halves of a tile's MMAs, where queued work hides its latency.
-      uint32_t v_sl = 1 % NS, v_par = 0;  // slot / parity of V_s (V_0 is load 1)
-      if (ok) ok = mbar_wait_a(a_full + 8 * v_sl, v_par, p.status, 24);
+      // (The softmax warps wait for V_s to land before they report P_s, so P-ready implies V-ready
+      // and this thread has a single barrier per tile.)
+      uint32_t v_sl = 1 % NS;  // slot of V_s (V_0 is load 1)
+      auto advance_v = [&](int by) {
+        v_sl += by;
+        if (v_sl >= (uint32_t)NS) v_sl -= NS;
+      };
       bool pre_p = false;  // P of the coming tile already seen complete
       // ---- dense tiles ----
       for (int s = 0; ok && s < n_dense; ++s) {
@@ -305,22 +335,15 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
         // P_s: two 32-column halves at the start of each warpgroup's S columns (stride 64)
         const uint32_t a0 = tmem + kColS + 128 * (s & 1);
         const uint32_t b_lo = dv0.lo + v_sl * (TILE >> 4);
-        mma_ts_x4(tmem + kColO, a0, b_lo, dv0.hi, 2048 >> 4, idesc_o, (uint32_t)(s > 0));
-        const uint32_t done_bar = a_free + 8 * v_sl;
-        // next V: a dense successor's V is two loads on, a light successor's one load on
-        advance(v_sl, v_par, s + 1 < n_dense ? 2 : 1);
-        pre_p = false;
-        if (s + 1 < n_tiles) {
-          // A blocking wait for P_{s+1} here could deadlock against a rescale that waits for PV_s;
-          // a peek cannot.  V_{s+1} only depends on older tiles.
-          pre_p = s + 1 < n_dense ? mbar_test_wait_a(a_pfull + 8 * ((s + 1) & 1), ((s + 1) >> 1) & 1)
-                                  : mbar_test_wait_a(a_plfull, 0);
-          ok = mbar_wait_a(a_full + 8 * v_sl, v_par, p.status, 24);
-        }
-        if (s < 16) TRACE(65 + 2 * s);
-        if (!ok) break;
+        // A blocking wait for P_{s+1} here could deadlock against a rescale that waits for PV_s;
+        // a peek cannot.
+        const bool dn = s + 1 < n_dense;
+        pre_p = mma_ts_x4_peek(tmem + kColO, a0, b_lo, dv0.hi, 2048 >> 4, idesc_o, (uint32_t)(s > 0),
+                               dn ? a_pfull + 8 * ((s + 1) & 1) : a_plfull, dn ? ((s + 1) >> 1) & 1 : 0);
+        if (s + 1 >= n_tiles) pre_p = false;
         mma_ts_x4(tmem + kColO, a0 + 64, b_lo + 4 * (2048 >> 4), dv0.hi, 2048 >> 4, idesc_o, 1u);
-        mma_commit_a(done_bar);
+        mma_commit_a(a_free + 8 * v_sl);
+        advance_v(dn ? 2 : 1);  // a dense successor's V is two loads on, a light successor's one
         if (s < 24) TRACE(36 + s);
       }
       // ---- light tiles: P in four contiguous 64-column buffers ----
@@ -332,20 +355,13 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
         tc_fence_after();
         const uint32_t a0 = tmem + kColS + 64 * pb;
         const uint32_t b_lo = dv0.lo + v_sl * (TILE >> 4);
-        mma_ts_x4(tmem + kColO, a0, b_lo, dv0.hi, 2048 >> 4, idesc_o, 1u);
-        const uint32_t done_bar = a_free + 8 * v_sl;
-        advance(v_sl, v_par, 1);
         pb = (pb + 1) & 3;
         if (pb == 0) pb_par ^= 1;
-        pre_p = false;
-        if (l + 1 < n_light) {
-          pre_p = mbar_test_wait_a(a_plfull + 8 * pb, pb_par);
-          ok = mbar_wait_a(a_full + 8 * v_sl, v_par, p.status, 24);
-        }
-        if (n_dense + l < 16) TRACE(65 + 2 * (n_dense + l));
-        if (!ok) break;
+        pre_p = mma_ts_x4_peek(tmem + kColO, a0, b_lo, dv0.hi, 2048 >> 4, idesc_o, 1u, a_plfull + 8 * pb, pb_par);
+        if (l + 1 >= n_light) pre_p = false;
         mma_ts_x4(tmem + kColO, a0 + 32, b_lo + 4 * (2048 >> 4), dv0.hi, 2048 >> 4, idesc_o, 1u);
-        mma_commit_a(done_bar);
+        mma_commit_a(a_free + 8 * v_sl);
+        advance_v(1);
         if (n_dense + l < 24) TRACE(36 + n_dense + l);
       }
     }
@@ -365,40 +381,14 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const int tt_base = (64 * wg) / CP;      // first tile-local time step of this thread's columns
     const int ck_base = CP == 128 ? 64 * wg : 0;  // first channel slot of this thread's columns
-    for (int d = tid; d < 3 * D; d += kSoftmaxThreads) {
-      const __nv_bfloat16* src = d < D ? p.u : (d < 2 * D ? p.vt : p.z);
-      s_bias[d] = __bfloat162float(src[hk * D + d % D]);
-    }
+    for (int d = tid; d < D; d += kSoftmaxThreads) s_bias[d] = __bfloat162float(p.u[hk * D + d]);
+    s_vr[tid] = p.relc[hk * 256 + tid];  // s_vr and s_zc are adjacent: 256 floats
     softmax_bar();
     bool ok = warp_wait(&bars[kBarProFull], 0, p.status, 30);
     TRACE(1);
-    if (ok) {
-      // per-column constants of the two relative products: vt.r_time[j] and z.r_chan[j]
-      const bool is_t = tid < 128;
-      const int j = tid & 127;
-      if (is_t || j < CP) {
-        const uint8_t* base = is_t ? sR : sC;
-        const int half_bytes = is_t ? HALF : CP * 128;
-        const float4* bias4 = reinterpret_cast<const float4*>(s_bias + (is_t ? D : 2 * D));
-        float acc = 0.f;
-#pragma unroll
-        for (int hh = 0; hh < NH; ++hh) {
-#pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(base + hh * half_bytes + j * 128 + ((c ^ (j & 7)) << 4));
-            const float4 b0 = bias4[hh * 16 + c * 2], b1 = bias4[hh * 16 + c * 2 + 1];
-            acc += __uint_as_float(raw.x << 16) * b0.x + __uint_as_float(raw.x & 0xffff0000u) * b0.y +
-                   __uint_as_float(raw.y << 16) * b0.z + __uint_as_float(raw.y & 0xffff0000u) * b0.w +
-                   __uint_as_float(raw.z << 16) * b1.x + __uint_as_float(raw.z & 0xffff0000u) * b1.y +
-                   __uint_as_float(raw.w << 16) * b1.z + __uint_as_float(raw.w & 0xffff0000u) * b1.w;
-          }
-        }
-        (is_t ? s_vr : s_zc)[j] = acc;
-      }
-      ok = warp_wait(&bars[kBarProMma], 0, p.status, 31);
-    }
+    if (ok) ok = warp_wait(&bars[kBarProMma], 0, p.status, 31);
     TRACE(2);
-    softmax_bar();  // every thread is done reading sR / sC; the scratch may overwrite them
+    // (the relative-key tiles sR / sC were only read by the two MMAs: the scratch may overwrite them)
     // Channel scores of the row, c2 (q.r_chan[j] + z.r_chan[j]), parked in shared memory in
     // 32-column chunks (split between the warpgroups) for the per-row gather below.
     if (ok) {
@@ -503,10 +493,10 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
       if (need) m_used = m_tile;
       return true;
     };
-    // temporal scores of the TPB key time steps of tile J, in log2 units, plus the channel maximum
-    auto load_tb = [&](int J, float (&tb_all)[TPB], bool (&valid_all)[TPB]) {
-      uint32_t raw[TPB];
-      int colj[TPB];
+    // temporal scores of the TPB key time steps of tile J, in log2 units, plus the channel maximum.
+    // Issue and use are split so that the TMEM round trip overlaps the barrier waits in between;
+    // the values are valid after the next tmem_ld_wait().
+    auto tb_issue = [&](int J, uint32_t (&raw)[TPB], int (&colj)[TPB], bool (&valid_all)[TPB]) {
 #pragma unroll
       for (int tt = 0; tt < TPB; ++tt) {
         const int tk_abs = J * TPB + tt, dt = ti_abs - tk_abs;
@@ -514,9 +504,16 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
         colj[tt] = T - 1 - min(max(dt, 0), T - 1);
         tmem_ld1(lane_base + kColTB + colj[tt], raw[tt]);
       }
-      tmem_ld_wait();
+    };
+    auto tb_finish = [&](const uint32_t (&raw)[TPB], const int (&colj)[TPB], float (&tb_all)[TPB]) {
 #pragma unroll
       for (int tt = 0; tt < TPB; ++tt) tb_all[tt] = p.c2 * (__uint_as_float(raw[tt]) + s_vr[colj[tt]]) + mc;
+    };
+    // V_s has landed?  (These warps vouch for it when they report P_s, so the MMA issuer has a
+    // single barrier per tile.)
+    auto wait_v = [&](int s) -> bool {
+      const int qv = q_of_v(s);
+      return warp_wait(&slot_full[qv % NS], (qv / NS) & 1, p.status, 38);
     };
 
     // ------------------------------ dense tiles ------------------------------
@@ -529,11 +526,30 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
       const uint32_t s_addr = lane_base + kColS + 128 * buf + 64 * wg;
       float tb_all[TPB];
       bool valid_all[TPB];
+      uint32_t tb_raw[TPB];
+      int tb_col[TPB];
 #pragma unroll
-      for (int tt = 0; tt < TPB; ++tt) { tb_all[tt] = 0.f; valid_all[tt] = false; }
-      if (ok) load_tb(J, tb_all, valid_all);
+      for (int tt = 0; tt < TPB; ++tt) { tb_all[tt] = 0.f; valid_all[tt] = false; tb_raw[tt] = 0; tb_col[tt] = 0; }
+      if (ok) tb_issue(J, tb_raw, tb_col, valid_all);
       float tbv[TPW], wmul[TPW];
       bool valid[TPW];
+      float sreg[64];
+      if (ok && !warp_wait(&bars[kBarSFull + buf], (s >> 1) & 1, p.status, 32)) ok = false;
+      float m_part = -INFINITY;
+      if (ok) {
+        tc_fence_after();
+        uint32_t v0[32], v1[32];
+        tmem_ld32(s_addr, v0);
+        tmem_ld32(s_addr + 32, v1);
+        if (!wait_v(s)) ok = false;  // overlaps the TMEM round trips
+        tmem_ld_wait();
+        tb_finish(tb_raw, tb_col, tb_all);
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) {
+          sreg[jj] = __uint_as_float(v0[jj]);
+          sreg[32 + jj] = __uint_as_float(v1[jj]);
+        }
+      }
 #pragma unroll
       for (int tl = 0; tl < TPW; ++tl) {
         const int tt = tt_base + tl;
@@ -547,20 +563,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
         const int dt = ti_abs - (J * TPB + tt);
         wmul[tl] = (p.window > 0 && dt > p.window && ti_abs != T - 1) ? 0.f : 1.f;
       }
-      float sreg[64];
-      if (ok && !warp_wait(&bars[kBarSFull + buf], (s >> 1) & 1, p.status, 32)) ok = false;
-      float m_part = -INFINITY;
       if (ok) {
-        tc_fence_after();
-        uint32_t v0[32], v1[32];
-        tmem_ld32(s_addr, v0);
-        tmem_ld32(s_addr + 32, v1);
-        tmem_ld_wait();
-#pragma unroll
-        for (int jj = 0; jj < 32; ++jj) {
-          sreg[jj] = __uint_as_float(v0[jj]);
-          sreg[32 + jj] = __uint_as_float(v1[jj]);
-        }
         float gmax[TPW];
 #pragma unroll
         for (int tl = 0; tl < TPW; ++tl) gmax[tl] = -INFINITY;
@@ -625,7 +628,15 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
       const int s = n_dense + l;
       float tb_all[TPB];
       bool valid_all[TPB];
-      load_tb(l, tb_all, valid_all);
+      {
+        uint32_t tb_raw[TPB];
+        int tb_col[TPB];
+        tb_issue(l, tb_raw, tb_col, valid_all);
+        ok = wait_v(s);  // overlaps the TMEM round trip
+        tmem_ld_wait();
+        if (!ok) break;
+        tb_finish(tb_raw, tb_col, tb_all);
+      }
       if (s >= 12 && s < 16) TRACE(112 + 4 * (s - 12));
       float m_tile = -INFINITY;
 #pragma unroll
@@ -763,12 +774,17 @@ int launch(const Args& a, int* status, cudaStream_t s) {
   t.n_qt = (a.T + TPB - 1) / TPB;
   t.c2 = a.c2;
   t.status = status;
-  t.trace = reinterpret_cast<long long*>(status) + 32;  // workspace + 256 bytes (MVPA_TC_TRACE builds only)
+  float* relc = reinterpret_cast<float*>(status) + 64;  // workspace + 256 bytes
+  t.relc = relc;
+  t.trace = reinterpret_cast<long long*>(relc + (size_t)a.Hkv * 256);  // MVPA_TC_TRACE builds only
   constexpr int smem = Cfg<D>::SMEM_BYTES;
   static_assert(smem <= 232448, "shared memory budget");
   static_assert(Cfg<D>::EARLY >= 2, "the first tile's K and V load while the prologue runs");
   MVPA_CUDA_CHECK(cudaFuncSetAttribute(tc_fwd_kernel<D, CP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   MVPA_CUDA_CHECK(cudaMemsetAsync(status, 0, sizeof(int), s));
+  rel_const_kernel<<<a.Hkv, 256, 0, s>>>(t.vt, t.z, (const __nv_bfloat16*)a.rt, (const __nv_bfloat16*)a.rc, relc, a.T,
+                                        a.C, D);
+  count_launch();
   const unsigned grid = (unsigned)t.n_qt * a.B * a.H;
   tc_fwd_kernel<D, CP><<<grid, kThreads, smem, s>>>(maps, t);
   count_launch();
@@ -784,16 +800,17 @@ bool tc_fwd_supported(const Args& a) {
 
 size_t tc_fwd_workspace_bytes(const mvpa_problem* p) {
   const bool tc = (p->D == 64 || p->D == 128) && p->C <= 128 && p->T <= 128;
+  // status word (bounded waits report here) + per-kv-head constants of the relative products
+  size_t bytes = 256 + (size_t)p->Hkv * 1024;
 #ifdef MVPA_TC_TRACE
-  return tc ? 256 + (size_t)p->T * p->B * p->H * 1024 : 0;
-#else
-  return tc ? 256 : 0;  // the kernel status word (bounded waits report here)
+  bytes += (size_t)p->T * p->B * p->H * 1024;
 #endif
+  return tc ? bytes : 0;
 }
 
 int tc_fwd(const Args& a, void* workspace, size_t workspace_bytes, cudaStream_t s) {
-  if (workspace == nullptr || workspace_bytes < 256) {
-    set_error("tensor-core forward needs a 256-byte workspace");
+  if (workspace == nullptr || workspace_bytes < 256 + (size_t)a.Hkv * 1024 || ((uintptr_t)workspace & 15) != 0) {
+    set_error("tensor-core forward needs a 16-byte aligned workspace of mvpa_fwd_workspace_bytes() bytes");
     return MVPA_ERR_WORKSPACE;
   }
   int* status = reinterpret_cast<int*>(workspace);

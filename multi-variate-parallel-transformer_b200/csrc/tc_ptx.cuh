@@ -297,6 +297,35 @@ __device__ __forceinline__ void mma_ts_x4(uint32_t d_tmem, uint32_t a_tmem, uint
       : "memory");
 }
 
+// Same, with a non-blocking peek at an mbarrier phase folded in: the test is issued before the four
+// MMAs and its predicate is only read after them, so its ~150-cycle latency is hidden behind MMA
+// issue instead of stalling the (in-order) issuing thread.  Returns whether the phase had completed.
+__device__ __forceinline__ bool mma_ts_x4_peek(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
+                                               uint32_t b_step16, uint32_t idesc, uint32_t accumulate_first,
+                                               uint32_t peek_bar, uint32_t peek_parity) {
+  uint32_t ready;
+  asm volatile(
+      "{\n\t.reg .pred p0, p1, pr;\n\t.reg .b64 db;\n\t.reg .b32 lo;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 pr, [%8], %9;\n\t"
+      "setp.ne.b32 p0, %7, 0;\n\t"
+      "setp.eq.b32 p1, 0, 0;\n\t"
+      "mov.b32 lo, %3;\n\t"
+      "mov.b64 db, {lo, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [%2], db, %6, p0;\n\t"
+      "add.u32 lo, lo, %5;\n\t mov.b64 db, {lo, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [%2 + 8], db, %6, p1;\n\t"
+      "add.u32 lo, lo, %5;\n\t mov.b64 db, {lo, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [%2 + 16], db, %6, p1;\n\t"
+      "add.u32 lo, lo, %5;\n\t mov.b64 db, {lo, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [%2 + 24], db, %6, p1;\n\t"
+      "selp.u32 %0, 1, 0, pr;\n\t}"
+      : "=r"(ready)
+      : "r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(b_step16), "r"(idesc), "r"(accumulate_first),
+        "r"(peek_bar), "r"(peek_parity)
+      : "memory");
+  return ready != 0;
+}
+
 // Instruction descriptor for kind::f16 with bf16 A/B and fp32 accumulation.
 //   [4,6) D fmt = 1 (f32)  [7,10) A fmt = 1 (bf16)  [10,13) B fmt = 1 (bf16)
 //   [15] A major (0 = K)   [16] B major (0 = K, 1 = MN)   [17,23) N >> 3   [24,29) M >> 4
