@@ -100,6 +100,32 @@ int mvpa_bwd(const mvpa_problem* p, const mvpa_tensor* q, const mvpa_tensor* k,
              const mvpa_tensor* dv, float* du, float* dvt, float* dz, float* dr_time,
              float* dr_chan, void* workspace, size_t workspace_bytes, void* cuda_stream);
 
+/*
+ * Forward for callers that must not allocate.  (No counterpart in the reference, which allocates
+ * freely through torch.)  Some hosts of this library cannot call cudaMalloc on the path that runs
+ * attention: a serving process that handed all device memory to its own pool at start-up, a
+ * plugin whose host forbids allocator calls inside its execute hook, code running between
+ * cudaStreamBeginCapture and cudaStreamEndCapture.  mvpa_fwd leaves the scratch to the caller;
+ * this variant of the bf16 tensor-core forward keeps its scratch (status word + per-kv-head
+ * constants, 65 792 bytes) in a fixed array that is part of the library's device image, so each
+ * GPU that loads the library holds those bytes until the process ends.
+ *
+ *   - Same arguments and results as mvpa_fwd, minus the workspace.  bf16 only, and only the
+ *     shapes the tensor-core forward takes (D 64 or 128, C <= 128, T <= 128); at most 64 kv
+ *     heads.  Anything else returns MVPA_ERR_UNSUPPORTED / MVPA_ERR_WORKSPACE with a message.
+ *   - The first call on a device looks up the array's device address (once per device, with
+ *     that device current).  Make that first call outside any stream capture.
+ *   - Calls no cudaMalloc / cudaFree and no allocating library routine.
+ *   - All calls on a device share the one array; whatever must start from zero is cleared on
+ *     the stream at the start of each call.  Two calls whose kernels overlap on the GPU (two
+ *     streams, two host threads) race on it: serialise them, or use mvpa_fwd with one
+ *     workspace per stream.
+ */
+int mvpa_fwd_noalloc(const mvpa_problem* p, const mvpa_tensor* q, const mvpa_tensor* k,
+                     const mvpa_tensor* v, const void* u, const void* vt, const void* z,
+                     const void* r_time, const void* r_chan, const mvpa_tensor* o, float* lse,
+                     void* cuda_stream);
+
 /* Reads back the status word the kernels of the last mvpa_fwd call left at the start of
  * `workspace` (every device-side wait is bounded; one that runs out records a code there and
  * the kernel returns instead of hanging).  Synchronises `cuda_stream`.  Returns MVPA_OK, or

@@ -185,6 +185,20 @@ int mvpa_bwd(const mvpa_problem* p, const mvpa_tensor* q, const mvpa_tensor* k, 
   return simt_bwd(b, p->dtype, (cudaStream_t)cuda_stream);
 }
 
+int mvpa_fwd_noalloc(const mvpa_problem* p, const mvpa_tensor* q, const mvpa_tensor* k, const mvpa_tensor* v,
+                     const void* u, const void* vt, const void* z, const void* r_time, const void* r_chan,
+                     const mvpa_tensor* o, float* lse, void* cuda_stream) {
+  Args a;
+  int rc = fill_args(a, p, q, k, v, u, vt, z, r_time, r_chan, o, lse);
+  if (rc) return rc;
+  if (!use_tc(a, p->dtype)) {
+    set_error("mvpa_fwd_noalloc covers the bf16 tensor-core forward only (D 64/128, C <= 128, T <= 128); "
+              "other problems need no scratch at all: call mvpa_fwd");
+    return MVPA_ERR_UNSUPPORTED;
+  }
+  return tc_fwd_static(a, (cudaStream_t)cuda_stream);
+}
+
 int mvpa_workspace_status(const void* workspace, size_t workspace_bytes, void* cuda_stream) {
   if (workspace == nullptr || workspace_bytes < sizeof(int)) return MVPA_OK;  // nothing was recorded
   int code = 0;

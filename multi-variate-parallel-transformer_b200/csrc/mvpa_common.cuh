@@ -55,6 +55,7 @@ void simt_bwd_carve(BwdArgs& b, float* ws);
 bool tc_fwd_supported(const Args& a);
 size_t tc_fwd_workspace_bytes(const mvpa_problem* p);
 int tc_fwd(const Args& a, void* workspace, size_t workspace_bytes, cudaStream_t s);
+int tc_fwd_static(const Args& a, cudaStream_t s);  // same, scratch in a built-in device array
 
 template <typename T>
 __device__ __forceinline__ float to_f32(T x);

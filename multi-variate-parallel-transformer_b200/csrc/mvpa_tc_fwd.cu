@@ -25,6 +25,8 @@
 // kept in shared memory).
 #include <cuda_fp16.h>
 
+#include <mutex>
+
 #include "mvpa_common.cuh"
 #include "tc_ptx.cuh"
 #include "tc_tma_host.cuh"
@@ -806,6 +808,49 @@ size_t tc_fwd_workspace_bytes(const mvpa_problem* p) {
   bytes += (size_t)p->T * p->B * p->H * 1024;
 #endif
   return tc ? bytes : 0;
+}
+
+// ---- forward without caller scratch --------------------------------------------------------
+// Scratch of the forward kernels (status word + per-kv-head constants of the relative products)
+// for callers that cannot hand over a workspace: a fixed array in device memory, part of the
+// library image, so every GPU that loads the library carries these 65 KB until the process exits.
+constexpr int kStaticMaxKvHeads = 64;
+constexpr size_t kStaticScratchBytes = 256 + (size_t)kStaticMaxKvHeads * 1024;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+int tc_fwd_static(const Args& a, cudaStream_t s) {
+#ifdef MVPA_TC_TRACE
+  set_error("the instrumented build writes its timeline to the caller's workspace: use mvpa_fwd");
+  return MVPA_ERR_UNSUPPORTED;
+#else
+  if (a.Hkv > kStaticMaxKvHeads) {
+    set_error("mvpa_fwd_noalloc: %d kv heads exceed the built-in scratch (at most %d); use mvpa_fwd with a workspace",
+              a.Hkv, kStaticMaxKvHeads);
+    return MVPA_ERR_WORKSPACE;
+  }
+  // In host code `g_static_scratch` only names the symbol; its device address has to be asked for,
+  // once per device, while that device is current.
+  constexpr int kMaxDevices = 64;
+  static void* addr[kMaxDevices] = {};
+  static std::mutex mu;
+  int dev = -1;
+  MVPA_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) {
+    set_error("mvpa_fwd_noalloc: device ordinal %d out of range", dev);
+    return MVPA_ERR_CUDA;
+  }
+  void* ptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (addr[dev] == nullptr) {
+      void* got = nullptr;
+      MVPA_CUDA_CHECK(cudaGetSymbolAddress(&got, g_static_scratch));
+      addr[dev] = got;
+    }
+    ptr = addr[dev];
+  }
+  return tc_fwd(a, ptr, kStaticScratchBytes, s);
+#endif
 }
 
 int tc_fwd(const Args& a, void* workspace, size_t workspace_bytes, cudaStream_t s) {

@@ -93,7 +93,7 @@ class Tensor(ctypes.Structure):
 
 EXPORTS = ("mvpa_fwd", "mvpa_bwd", "mvpa_fwd_workspace_bytes", "mvpa_bwd_workspace_bytes",
            "mvpa_last_error_string", "mvpa_launch_count", "mvpa_abi_version",
-           "mvpa_workspace_status")
+           "mvpa_workspace_status", "mvpa_fwd_noalloc")
 
 
 def lib() -> ctypes.CDLL:
@@ -122,6 +122,8 @@ def lib() -> ctypes.CDLL:
         L.mvpa_bwd.restype = ctypes.c_int
         L.mvpa_bwd.argtypes = [P, Tn, Tn, Tn, vp, vp, vp, vp, vp, Tn, vp, Tn, Tn, Tn, Tn,
                                vp, vp, vp, vp, vp, vp, ctypes.c_size_t, vp]
+        L.mvpa_fwd_noalloc.restype = ctypes.c_int
+        L.mvpa_fwd_noalloc.argtypes = [P, Tn, Tn, Tn, vp, vp, vp, vp, vp, Tn, vp, vp]
         L.mvpa_workspace_status.restype = ctypes.c_int
         L.mvpa_workspace_status.argtypes = [vp, ctypes.c_size_t, vp]
         L.mvpa_last_error_string.restype = ctypes.c_char_p
