@@ -40,6 +40,9 @@ WORKLOADS = {
             "16k tokens: bf16 fwd, B1 x 16 heads / 8 kv heads x 16384 tokens (128 ch x 128 seg), head_dim 128"),
 }
 WORKLOAD, NAME = WORKLOADS["cfg2"]
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the forward kernel, from the ncu
+# captures summarised under profiles/ (bytes)
+NCU_DRAM_BYTES = {"cfg2": 135.7e6, "16k": 208.2e6}
 METRIC = "flash_mvpa_fwd_tflops"
 UNIT = "TFLOP/s (F_alg)"
 
@@ -297,7 +300,7 @@ def main():
             "gpu_launches": int(launches),
             "clocks": clk.summary(),
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                         "frac": achieved / peak, "traffic": NCU_DRAM_BYTES.get(args.workload), "peak_source": peak_src,
                          "kernel": "tc_fwd_kernel<%d,%d>" % (w["D"], 32 if w["C"] <= 32 else 64 if w["C"] <= 64 else 128),
                          "flops_per_launch": f["f_alg"],
                          "achieved_dense_convention": f["f_dense"] / (kernel_ms * 1e-3) / 1e12},
@@ -313,7 +316,7 @@ def main():
                                "frac_of_peak_f_alg": ff["f_alg"] / m2 / 1e9 / peak}
                 del tt
             out["extra"] = extra
-        if not args.no_cpu:
+        if not args.no_cpu and world == 1:  # the CPU leg belongs to the single-GPU run (torchrun pins OMP threads to 1)
             sample = dict(w, B=1)
             sec, cores = cpu_port_time(sample)
             out["cpu_baseline"] = {"value": flops(**sample)["f_alg"] / sec / 1e12, "unit": UNIT, "cores": cores,

@@ -59,6 +59,14 @@ typedef struct mvpa_problem {
   int32_t dtype;  /* MVPA_F32 or MVPA_BF16                                        */
   float sm_scale; /* applied to the sum of the three score terms                  */
   int32_t flags;  /* reserved, must be 0                                          */
+  /* Query time range (forward only).  q, o and lse then hold the tokens of time steps
+   * [q_time_begin, q_time_begin + q_time_count) only, N_q = q_time_count*C rows, while k, v,
+   * r_time, T describe the whole sequence: the time-block sharding of one long sample across
+   * GPUs (each rank all-gathers K/V and computes its own query rows).  q_time_count == 0 means
+   * the whole sequence.  The tensor-core forward needs q_time_begin to be a multiple of its
+   * time steps per tile (128 / next_pow2(max(C,32))).  No counterpart in the reference. */
+  int32_t q_time_begin;
+  int32_t q_time_count;
 } mvpa_problem;
 
 /* A (batch, head, token, D) tensor with D contiguous; strides in elements.
@@ -76,9 +84,10 @@ size_t mvpa_bwd_workspace_bytes(const mvpa_problem* p);
 /*
  * Forward.  Replaces `_rel_bias` + `FlashMVPA.forward` + `_fwd_kernel`
  * (`attentions/attn.py:1305-1314, 1013-1138, 38-347`).
- *   q (B,H,N,D); k, v (B,Hkv,N,D); u, vt, z (Hkv,D) contiguous;
- *   r_time (Hkv,T,D), r_chan (Hkv,C,D) contiguous; o (B,H,N,D);
- *   lse (B*H, N) fp32, may be NULL when no backward will follow.
+ *   q (B,H,N_q,D); k, v (B,Hkv,N,D); u, vt, z (Hkv,D) contiguous;
+ *   r_time (Hkv,T,D), r_chan (Hkv,C,D) contiguous; o (B,H,N_q,D);
+ *   lse (B*H, N_q) fp32, may be NULL when no backward will follow.  N_q = N unless the problem
+ *   names a query time range.
  */
 int mvpa_fwd(const mvpa_problem* p, const mvpa_tensor* q, const mvpa_tensor* k,
              const mvpa_tensor* v, const void* u, const void* vt, const void* z,

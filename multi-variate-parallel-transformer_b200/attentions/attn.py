@@ -46,10 +46,10 @@ def _stream() -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def _problem(q, k, r_time, r_chan, sm_scale, window) -> _nat.Problem:
+def _problem(q, k, r_time, r_chan, sm_scale, window, q_time=(0, 0)) -> _nat.Problem:
     B, H, N, D = q.shape
     return _nat.Problem(B, H, k.shape[1], r_time.shape[-2], r_chan.shape[-2], D, int(window),
-                        _dtype_code(q), float(sm_scale), 0)
+                        _dtype_code(q), float(sm_scale), 0, int(q_time[0]), int(q_time[1]))
 
 
 class FlashMVPA(torch.autograd.Function):
@@ -58,13 +58,13 @@ class FlashMVPA(torch.autograd.Function):
     pre-multiplied score matrices."""
 
     @staticmethod
-    def forward(ctx, q, u, vt, z, k, r_time, r_chan, v, sm_scale, window):
+    def forward(ctx, q, u, vt, z, k, r_time, r_chan, v, sm_scale, window, q_time=(0, 0)):
         if not q.is_cuda:
             raise RuntimeError("flash_mvpa: tensors must be on a CUDA device (no CPU path)")
         lib = _nat.lib()
         q, k, v = _rows(q), _rows(k), _rows(v)
         u, vt, z, r_time, r_chan = (x.contiguous() for x in (u, vt, z, r_time, r_chan))
-        prob = _problem(q, k, r_time, r_chan, sm_scale, window)
+        prob = _problem(q, k, r_time, r_chan, sm_scale, window, q_time)
         o = torch.empty_like(q)
         lse = torch.empty((q.shape[0] * q.shape[1], q.shape[2]), device=q.device, dtype=torch.float32)
         nbytes = lib.mvpa_fwd_workspace_bytes(ctypes.byref(prob))
@@ -79,12 +79,14 @@ class FlashMVPA(torch.autograd.Function):
         if _CHECK_STATUS and nbytes:  # debugging aid: synchronises the stream
             _nat.check(lib.mvpa_workspace_status(ws.data_ptr(), nbytes, _stream()), "mvpa_fwd kernels")
         ctx.save_for_backward(q, u, vt, z, k, r_time, r_chan, v, o, lse)
-        ctx.sm_scale, ctx.window = sm_scale, window
+        ctx.sm_scale, ctx.window, ctx.q_time = sm_scale, window, q_time
         return o
 
     @staticmethod
     def backward(ctx, do):
         q, u, vt, z, k, r_time, r_chan, v, o, lse = ctx.saved_tensors
+        if ctx.q_time[1]:
+            raise NotImplementedError("flash_mvpa: backward through a query time range is not implemented")
         lib = _nat.lib()
         do = _rows(do)
         prob = _problem(q, k, r_time, r_chan, ctx.sm_scale, ctx.window)
@@ -103,12 +105,12 @@ class FlashMVPA(torch.autograd.Function):
                               drt.data_ptr(), drc.data_ptr(), ws.data_ptr(), nbytes, _stream())
         _nat.check(st, "mvpa_bwd")
         dt = q.dtype
-        return (dq, du.to(dt), dvt.to(dt), dz.to(dt), dk, drt.to(dt), drc.to(dt), dv, None, None)
+        return (dq, du.to(dt), dvt.to(dt), dz.to(dt), dk, drt.to(dt), drc.to(dt), dv, None, None, None)
 
 
 def flash_mvpa(q, q_bias, q_btime, q_bchan, k_glob, k_time, k_chan, v, causal, sm_scale,
                window_size=0, p_drop=0.0, sequence_parallel=False, rel_bias_time=True,
-               rel_bias_chan=True, generator=None):
+               rel_bias_chan=True, generator=None, q_time_range=None):
     """Fused multi-variate parallel attention.
 
     q (B,H,N,D); q_bias/q_btime/q_bchan (1,Hkv,1,D) = u/v/z; k_glob, v (B,Hkv,N,D);
@@ -119,6 +121,10 @@ def flash_mvpa(q, q_bias, q_btime, q_bchan, k_glob, k_time, k_chan, v, causal, s
     (`:1339, 1344`).  `sequence_parallel` only chose a launch geometry in the
     reference (`:1165-1172`) and is accepted and ignored.  Structured attention dropout
     (`:1052-1062`) and runs without the relative terms are not implemented: they raise.
+
+    `q_time_range=(t0, n)` (an extension, forward only): `q` holds only the tokens of time steps
+    [t0, t0+n) while the keys, values and relative keys describe the whole sequence — what one
+    rank computes when a long sample is sharded by query time blocks (`mvpa_shard`).
     """
     if not (rel_bias_time and rel_bias_chan):
         raise NotImplementedError("flash_mvpa: both relative terms are required (as the layer uses it)")
@@ -126,11 +132,17 @@ def flash_mvpa(q, q_bias, q_btime, q_bchan, k_glob, k_time, k_chan, v, causal, s
         raise NotImplementedError("flash_mvpa: attention dropout is not implemented; use p_drop=0")
     q_heads, kv_heads = q.shape[1], v.shape[1]
     assert q_heads % kv_heads == 0, "Q heads must be divisible by KV heads."
-    n_ctx, time_ctx, chan_ctx = q.shape[2], k_time.shape[2], k_chan.shape[2]
+    n_ctx, time_ctx, chan_ctx = k_glob.shape[2], k_time.shape[2], k_chan.shape[2]
     assert n_ctx == time_ctx * chan_ctx
+    q_time = (0, 0)
+    if q_time_range is not None:
+        q_time = (int(q_time_range[0]), int(q_time_range[1]))
+        assert q_time[1] > 0 and q.shape[2] == q_time[1] * chan_ctx
+    else:
+        assert q.shape[2] == n_ctx
     assert q.shape[-1] == k_glob.shape[-1] == v.shape[-1]
     assert q.shape[-1] in {16, 32, 64, 128}
     D = q.shape[-1]
     u, vt, z = (x.reshape(kv_heads, D) for x in (q_bias, q_btime, q_bchan))
     return FlashMVPA.apply(q, u, vt, z, k_glob, k_time.reshape(kv_heads, time_ctx, D),
-                           k_chan.reshape(kv_heads, chan_ctx, D), v, sm_scale, window_size)
+                           k_chan.reshape(kv_heads, chan_ctx, D), v, sm_scale, window_size, q_time)

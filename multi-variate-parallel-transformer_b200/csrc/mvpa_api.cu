@@ -55,6 +55,12 @@ int check_problem(const mvpa_problem* p) {
     set_error("flags must be 0");
     return MVPA_ERR_SHAPE;
   }
+  if (p->q_time_begin < 0 || p->q_time_count < 0 || p->q_time_begin + p->q_time_count > p->T ||
+      (p->q_time_count == 0 && p->q_time_begin != 0)) {
+    set_error("query time range [%d, %d) is not inside [0, T = %d)", p->q_time_begin,
+              p->q_time_begin + p->q_time_count, p->T);
+    return MVPA_ERR_SHAPE;
+  }
   return MVPA_OK;
 }
 
@@ -107,6 +113,8 @@ int fill_args(Args& a, const mvpa_problem* p, const mvpa_tensor* q, const mvpa_t
   a.B = p->B; a.H = p->H; a.Hkv = p->Hkv; a.T = p->T; a.C = p->C; a.D = p->D;
   a.N = p->T * p->C; a.g = p->H / p->Hkv; a.window = p->window;
   a.sm_scale = p->sm_scale; a.c2 = p->sm_scale * kLog2e;
+  a.q_t0 = p->q_time_count > 0 ? p->q_time_begin : 0;
+  a.q_tn = p->q_time_count > 0 ? p->q_time_count : p->T;
   return MVPA_OK;
 }
 
@@ -160,6 +168,10 @@ int mvpa_bwd(const mvpa_problem* p, const mvpa_tensor* q, const mvpa_tensor* k, 
   if (lse == nullptr) {
     set_error("mvpa_bwd: lse is NULL (run mvpa_fwd with an lse buffer first)");
     return MVPA_ERR_SHAPE;
+  }
+  if (b.a.q_tn != b.a.T) {
+    set_error("mvpa_bwd: a query time range is a forward-only feature");
+    return MVPA_ERR_UNSUPPORTED;
   }
   if ((rc = check_tensor("d_o", d_o, p->dtype))) return rc;
   if ((rc = check_tensor("dq", dq, p->dtype))) return rc;
@@ -216,6 +228,6 @@ const char* mvpa_last_error_string(void) { return g_error; }
 
 uint64_t mvpa_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
-int mvpa_abi_version(void) { return 1; }
+int mvpa_abi_version(void) { return 2; }
 
 }  // extern "C"

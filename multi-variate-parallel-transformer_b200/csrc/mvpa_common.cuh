@@ -22,6 +22,7 @@ struct Args {
   int64_t v_sb, v_sh, v_sn;
   int64_t o_sb, o_sh, o_sn;
   int B, H, Hkv, T, C, D, N, g, window;
+  int q_t0, q_tn;  // query rows cover time steps [q_t0, q_t0 + q_tn); N_q = q_tn * C
   float sm_scale;  // natural-log domain scale of the score sum
   float c2;        // sm_scale * log2(e): scores are kept in base 2
 };

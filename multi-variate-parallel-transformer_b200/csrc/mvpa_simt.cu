@@ -137,14 +137,16 @@ __global__ void __launch_bounds__(kThreads) simt_fwd_kernel(Args p) {
   const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
   const int qt = gridDim.x - 1 - blockIdx.x;  // heaviest (latest) query tiles first
   const int bh = blockIdx.y, b = bh / p.H, h = bh % p.H, hk = h / p.g;
-  const int m0 = qt * kBM;
+  const int m0 = qt * kBM;               // first row of the tile inside this call's q / o / lse
   const int N = p.N, T = p.T, C = p.C;
+  const int Nq = p.q_tn * C;             // rows of this call (a query time range, or all of N)
+  const int row0 = p.q_t0 * C;           // token index of row 0
   const Tin* q = (const Tin*)p.q + b * p.q_sb + h * p.q_sh;
   const Tin* k = (const Tin*)p.k + b * p.k_sb + hk * p.k_sh;
   const Tin* v = (const Tin*)p.v + b * p.v_sb + hk * p.v_sh;
-  const int valid = min(kBM, N - m0);
+  const int valid = min(kBM, Nq - m0);
 
-  load_tile<Tin, D>(Qs, q, p.q_sn, m0, N, kBM, nullptr, 1.f);
+  load_tile<Tin, D>(Qs, q, p.q_sn, m0, Nq, kBM, nullptr, 1.f);
   if (tid < kBM) { ms[tid] = -INFINITY; ls[tid] = 0.f; }
   __syncthreads();
   rel_scores<Tin, D>(Qs, kBM, (const Tin*)p.vt + hk * D, (const Tin*)p.z + hk * D,
@@ -161,7 +163,7 @@ __global__ void __launch_bounds__(kThreads) simt_fwd_kernel(Args p) {
   int ti[2], ci[2];
 #pragma unroll
   for (int a = 0; a < 2; ++a) {
-    const int i = min(m0 + 2 * ty + a, N - 1);
+    const int i = row0 + min(m0 + 2 * ty + a, Nq - 1);  // token index in the whole sequence
     ti[a] = i / C;
     ci[a] = i % C;
   }
@@ -171,7 +173,7 @@ __global__ void __launch_bounds__(kThreads) simt_fwd_kernel(Args p) {
 #pragma unroll
     for (int e = 0; e < DV; ++e) oacc[a][e] = 0.f;
 
-  const int t_last = (m0 + valid - 1) / C;
+  const int t_last = (row0 + m0 + valid - 1) / C;
   const int hi = min(N, (t_last + 1) * C);  // causal bound (`attentions/attn.py:102-104,125-127`)
   for (int n0 = 0; n0 < hi; n0 += kBN) {
     __syncthreads();
@@ -240,7 +242,7 @@ __global__ void __launch_bounds__(kThreads) simt_fwd_kernel(Args p) {
       const float inv = 1.f / ls[r];
 #pragma unroll
       for (int e = 0; e < DV; ++e) o[(int64_t)i * p.o_sn + tx + 16 * e] = from_f32<Tin>(oacc[a][e] * inv);
-      if (tx == 0 && p.lse != nullptr) p.lse[(int64_t)bh * N + i] = ms[r] + log2f(ls[r]);
+      if (tx == 0 && p.lse != nullptr) p.lse[(int64_t)bh * Nq + i] = ms[r] + log2f(ls[r]);
     }
   }
 }
@@ -640,7 +642,7 @@ int launch_fwd(const Args& a, cudaStream_t s) {
   }
   int rc = set_smem(simt_fwd_kernel<Tin, D>, smem);
   if (rc) return rc;
-  dim3 grid((a.N + kBM - 1) / kBM, a.B * a.H);
+  dim3 grid((a.q_tn * a.C + kBM - 1) / kBM, a.B * a.H);
   simt_fwd_kernel<Tin, D><<<grid, kThreads, smem, s>>>(a);
   count_launch();
   MVPA_CUDA_CHECK(cudaGetLastError());

@@ -62,6 +62,7 @@ struct TcArgs {
   float* lse;
   int64_t o_sb, o_sh, o_sn;
   int B, H, Hkv, T, C, g, window, n_qt;
+  int q_t0, q_tn, q_tiles;  // query time range of this call and its number of query tiles
   float c2;
   int* status;
   const float* relc;  // (Hkv, 256): vt.r_time[j] at [0,128), z.r_chan[j] at [128,256)
@@ -174,7 +175,8 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int BH = p.B * p.H;
-  const int I = p.n_qt - 1 - (int)(blockIdx.x / BH);  // latest (heaviest) query tiles first
+  const int I_loc = p.q_tiles - 1 - (int)(blockIdx.x / BH);  // latest (heaviest) query tiles first
+  const int I = p.q_t0 / TPB + I_loc;                         // tile index in the whole sequence
   const int bh = blockIdx.x % BH, b = bh / p.H, h = bh % p.H, hk = h / p.g;
   const int n_tiles = I + 1;
   const int n_light = light_tiles(I, TPB, p.window, p.n_qt);
@@ -231,7 +233,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
       prefetch_tensormap(&maps.rc);
       mbar_arrive_expect_tx(&bars[kBarProFull], 2 * TILE + NH * CP * 128);
       for (int hh = 0; hh < NH; ++hh) {
-        tma_load_5d(sQ + hh * HALF, &maps.q, &bars[kBarProFull], hh * 64, 0, I * TPB, h, b);
+        tma_load_5d(sQ + hh * HALF, &maps.q, &bars[kBarProFull], hh * 64, 0, I_loc * TPB, h, b);
         tma_load_3d(sR + hh * HALF, &maps.rt, &bars[kBarProFull], hh * 64, 0, hk);
         tma_load_3d(sC + hh * CP * 128, &maps.rc, &bars[kBarProFull], hh * 64, 0, hk);
       }
@@ -379,7 +381,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
     const int wg = tid >> 7;                 // column half this thread owns
     const int ti_loc = row / CP, c_i = row % CP;
     const int ti_abs = I * TPB + ti_loc;
-    const bool row_valid = c_i < C && ti_abs < T;
+    const bool row_valid = c_i < C && ti_abs < p.q_t0 + p.q_tn;
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const int tt_base = (64 * wg) / CP;      // first tile-local time step of this thread's columns
     const int ck_base = CP == 128 ? 64 * wg : 0;  // first channel slot of this thread's columns
@@ -694,7 +696,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
     if (ok) {
       tc_fence_after();
       const float inv = 1.f / l_sum;
-      const int64_t n = (int64_t)ti_abs * C + c_i;
+      const int64_t n = (int64_t)(ti_abs - p.q_t0) * C + c_i;  // row inside this call's q / o / lse
       __nv_bfloat16* orow = p.o + b * p.o_sb + h * p.o_sh + n * p.o_sn + wg * DW;
 #pragma unroll
       for (int c0 = 0; c0 < DW; c0 += 32) {
@@ -712,7 +714,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
           }
         }
       }
-      if (wg == 0 && row_valid && p.lse != nullptr) p.lse[(int64_t)bh * T * C + n] = m_used + log2f(l_sum);
+      if (wg == 0 && row_valid && p.lse != nullptr) p.lse[(int64_t)bh * p.q_tn * C + n] = m_used + log2f(l_sum);
     }
     TRACE(6);
     tc_fence_before();
@@ -729,7 +731,7 @@ int make_maps(TcMaps& m, const Args& a, int CP) {
   const uint64_t es = 2;
   int rc;
   {
-    const uint64_t dims[5] = {(uint64_t)a.D, (uint64_t)a.C, (uint64_t)a.T, (uint64_t)a.H, (uint64_t)a.B};
+    const uint64_t dims[5] = {(uint64_t)a.D, (uint64_t)a.C, (uint64_t)a.q_tn, (uint64_t)a.H, (uint64_t)a.B};
     const uint64_t str[4] = {(uint64_t)a.q_sn * es, (uint64_t)a.q_sn * a.C * es, (uint64_t)a.q_sh * es,
                              (uint64_t)a.q_sb * es};
     const uint32_t box[5] = {64, (uint32_t)CP, (uint32_t)TPB, 1, 1};
@@ -774,6 +776,12 @@ int launch(const Args& a, int* status, cudaStream_t s) {
   t.B = a.B; t.H = a.H; t.Hkv = a.Hkv; t.T = a.T; t.C = a.C; t.g = a.g; t.window = a.window;
   constexpr int TPB = 128 / CP;
   t.n_qt = (a.T + TPB - 1) / TPB;
+  t.q_t0 = a.q_t0; t.q_tn = a.q_tn;
+  t.q_tiles = (a.q_tn + TPB - 1) / TPB;
+  if (a.q_t0 % TPB != 0) {
+    set_error("query time range must start on a tile boundary: q_time_begin %d is not a multiple of %d", a.q_t0, TPB);
+    return MVPA_ERR_ALIGNMENT;
+  }
   t.c2 = a.c2;
   t.status = status;
   float* relc = reinterpret_cast<float*>(status) + 64;  // workspace + 256 bytes
@@ -787,7 +795,7 @@ int launch(const Args& a, int* status, cudaStream_t s) {
   rel_const_kernel<<<a.Hkv, 256, 0, s>>>(t.vt, t.z, (const __nv_bfloat16*)a.rt, (const __nv_bfloat16*)a.rc, relc, a.T,
                                         a.C, D);
   count_launch();
-  const unsigned grid = (unsigned)t.n_qt * a.B * a.H;
+  const unsigned grid = (unsigned)t.q_tiles * a.B * a.H;
   tc_fwd_kernel<D, CP><<<grid, kThreads, smem, s>>>(maps, t);
   count_launch();
   MVPA_CUDA_CHECK(cudaGetLastError());

@@ -83,7 +83,8 @@ class Problem(ctypes.Structure):
     _fields_ = [("B", ctypes.c_int32), ("H", ctypes.c_int32), ("Hkv", ctypes.c_int32),
                 ("T", ctypes.c_int32), ("C", ctypes.c_int32), ("D", ctypes.c_int32),
                 ("window", ctypes.c_int32), ("dtype", ctypes.c_int32),
-                ("sm_scale", ctypes.c_float), ("flags", ctypes.c_int32)]
+                ("sm_scale", ctypes.c_float), ("flags", ctypes.c_int32),
+                ("q_time_begin", ctypes.c_int32), ("q_time_count", ctypes.c_int32)]
 
 
 class Tensor(ctypes.Structure):

@@ -26,7 +26,8 @@ def test_library_exports_every_declared_symbol():
 
 
 def _prob(**kw):
-    d = dict(B=1, H=4, Hkv=2, T=4, C=4, D=64, window=10, dtype=nat.MVPA_F32, sm_scale=0.125, flags=0)
+    d = dict(B=1, H=4, Hkv=2, T=4, C=4, D=64, window=10, dtype=nat.MVPA_F32, sm_scale=0.125, flags=0,
+             q_time_begin=0, q_time_count=0)
     d.update(kw)
     return nat.Problem(*[d[f[0]] for f in nat.Problem._fields_])
 
@@ -46,6 +47,7 @@ def test_argument_errors_are_reported_without_a_device():
     assert _call_fwd(_prob(), ptr=260) == -3 and "16" in nat.last_error()
     assert _call_fwd(_prob(), stride_n=63) == -3
     assert _call_fwd(_prob(flags=1)) == -1
+    assert _call_fwd(_prob(q_time_begin=3, q_time_count=2)) == -1 and "time range" in nat.last_error()
 
 
 def test_workspace_queries():

@@ -1,0 +1,139 @@
+"""Partitioning for multi-GPU runs.  CPU part: the zig-zag plan and, with two `gloo` ranks, the
+K/V all-gather + per-rank query ranges reassemble exactly the single-process result (the oracle's
+torch port stands in for the CUDA operator).  GPU part: a query time range through the C ABI
+equals the matching rows of the full call."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import mvpa_shard as ms
+from conftest import PKG, ROOT
+
+
+@pytest.mark.parametrize("T,C,world", [(128, 128, 8), (128, 128, 2), (64, 64, 4), (25, 22, 2), (110, 100, 8), (3, 16, 4)])
+def test_zigzag_plan_covers_time_once_and_balances(T, C, world):
+    plan = ms.zigzag_chunks(T, C, world)
+    step = ms.tile_time_steps(C)
+    owned = np.zeros(T, int)
+    for chunks in plan:
+        assert len(chunks) == 2
+        for t0, n in chunks:
+            assert t0 % step == 0 or n == 0
+            owned[t0:t0 + n] += 1
+    assert (owned == 1).all()
+    work = [ms.causal_work(T, c) for c in plan]
+    assert sum(work) == T * (T + 1) // 2
+    if T // step >= 4 * world:                      # enough tiles to balance
+        assert max(work) <= 1.15 * (sum(work) / world)
+    assert ms.batch_slice(10, 4, 0) == slice(0, 3) and ms.batch_slice(10, 4, 3) == slice(8, 10)
+
+
+def _cpu_op(q, u, vt, z, k, rt, rc, v, causal, sm_scale, window_size, q_time_range=None):
+    import mvpa_port_torch as port
+    Hkv, D = k.shape[1], q.shape[-1]
+    t0, n = q_time_range
+    C = rc.shape[-2]
+    N = k.shape[2]
+    qf = torch.zeros(q.shape[0], q.shape[1], N, D)
+    qf[:, :, t0 * C:(t0 + n) * C] = q
+    o = port.rel_attn(qf, u.reshape(Hkv, D), vt.reshape(Hkv, D), z.reshape(Hkv, D), k, rt.reshape(Hkv, -1, D),
+                      rc.reshape(Hkv, -1, D), v, sm_scale, window_size)
+    return o[:, :, t0 * C:(t0 + n) * C]
+
+
+def _worker(rank, world, port, out_dir):
+    for p in (PKG, os.path.join(ROOT, "oracle")):
+        sys.path.insert(0, p)
+    import mvpa_port_torch as portmod
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        B, H, Hkv, T, C, D = 1, 4, 2, 13, 5, 16
+        g = torch.Generator().manual_seed(5)
+        r = lambda *s: torch.randn(*s, generator=g)
+        q, k, v = r(B, T * C, H, D), r(B, T * C, Hkv, D), r(B, T * C, Hkv, D)     # projection layout
+        u, vt, z, rt, rc = r(1, Hkv, 1, D), r(1, Hkv, 1, D), r(1, Hkv, 1, D), r(1, Hkv, T, D), r(1, Hkv, C, D)
+        plan = ms.zigzag_chunks(T, C, world)
+        cut = lambda x: [x[:, t0 * C:(t0 + n) * C].contiguous() if n else None for t0, n in plan[rank]]
+        outs = ms.time_sharded_attention(_cpu_op, cut(q), u, vt, z, cut(k), rt, rc, cut(v), T, C, D ** -0.5, 10)
+        ref = portmod.rel_attn(q.permute(0, 2, 1, 3), u.reshape(Hkv, D), vt.reshape(Hkv, D), z.reshape(Hkv, D),
+                               k.permute(0, 2, 1, 3), rt.reshape(Hkv, T, D), rc.reshape(Hkv, C, D),
+                               v.permute(0, 2, 1, 3), D ** -0.5, 10).permute(0, 2, 1, 3)
+        err = 0.0
+        for (t0, n), o in zip(plan[rank], outs):
+            if n:
+                err = max(err, (o - ref[:, t0 * C:(t0 + n) * C]).abs().max().item())
+        np.save(os.path.join(out_dir, f"err{rank}.npy"), np.array([err]))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_time_sharding_with_two_gloo_ranks(tmp_path):
+    port = 29500 + (os.getpid() % 2000)
+    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    errs = [float(np.load(tmp_path / f"err{r}.npy")[0]) for r in range(2)]
+    assert max(errs) < 1e-5, errs
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("cfg", [(1, 4, 2, 24, 128, 64, torch.bfloat16), (2, 2, 2, 20, 64, 128, torch.bfloat16),
+                                 (1, 2, 1, 12, 22, 64, torch.bfloat16), (1, 2, 2, 9, 8, 32, torch.float32)])
+def test_query_time_range_equals_rows_of_full_call(cuda, cfg):
+    import attentions
+    B, H, Hkv, T, C, D, dtype = cfg
+    g = torch.Generator().manual_seed(11)
+    r = lambda *s: torch.randn(*s, generator=g).to(dtype).to(cuda)
+    N = T * C
+    q, k, v = r(B, H, N, D), r(B, Hkv, N, D), r(B, Hkv, N, D)
+    u, vt, z, rt, rc = r(1, Hkv, 1, D), r(1, Hkv, 1, D), r(1, Hkv, 1, D), r(1, Hkv, T, D), r(1, Hkv, C, D)
+    kw = dict(causal=True, sm_scale=D ** -0.5, window_size=10)
+    full = attentions.flashmvpa(q, u, vt, z, k, rt, rc, v, **kw)
+    step = ms.tile_time_steps(C) if dtype == torch.bfloat16 and D >= 64 else 1
+    for t0, n in ((0, step), (step * 2, T - step * 2), (T - step, step)):
+        part = attentions.flashmvpa(q[:, :, t0 * C:(t0 + n) * C].contiguous(), u, vt, z, k, rt, rc, v,
+                                    q_time_range=(t0, n), **kw)
+        assert torch.equal(part, full[:, :, t0 * C:(t0 + n) * C]), (t0, n)
+
+
+def _gpu_worker(rank, world, port, out_dir):
+    for p in (PKG, os.path.join(ROOT, "oracle")):
+        sys.path.insert(0, p)
+    import attentions
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        B, H, Hkv, T, C, D = 1, 4, 2, 32, 128, 128
+        g = torch.Generator().manual_seed(6)
+        r = lambda *s: torch.randn(*s, generator=g).to(torch.bfloat16).to(dev)
+        q, k, v = r(B, T * C, H, D), r(B, T * C, Hkv, D), r(B, T * C, Hkv, D)
+        u, vt, z, rt, rc = r(1, Hkv, 1, D), r(1, Hkv, 1, D), r(1, Hkv, 1, D), r(1, Hkv, T, D), r(1, Hkv, C, D)
+        plan = ms.zigzag_chunks(T, C, world)
+        cut = lambda x: [x[:, t0 * C:(t0 + n) * C].contiguous() if n else None for t0, n in plan[rank]]
+        outs = ms.time_sharded_attention(attentions.flashmvpa, cut(q), u, vt, z, cut(k), rt, rc, cut(v), T, C,
+                                         D ** -0.5, 10)
+        full = attentions.flashmvpa(q.permute(0, 2, 1, 3), u, vt, z, k.permute(0, 2, 1, 3), rt, rc,
+                                    v.permute(0, 2, 1, 3), causal=True, sm_scale=D ** -0.5,
+                                    window_size=10).permute(0, 2, 1, 3)
+        same = all(torch.equal(o, full[:, t0 * C:(t0 + n) * C]) for (t0, n), o in zip(plan[rank], outs) if n)
+        torch.cuda.synchronize()
+        np.save(os.path.join(out_dir, f"same{rank}.npy"), np.array([int(same)]))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+def test_time_sharding_two_gpus_nccl_bit_equal_to_single_gpu(tmp_path):
+    """K/V all-gather over NCCL + per-rank query ranges: every rank's rows are bit-identical to the
+    single-GPU result (the kernels are deterministic and see the same K/V bytes)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    port = 29500 + (os.getpid() % 2000) + 7
+    mp.spawn(_gpu_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    assert all(int(np.load(tmp_path / f"same{r}.npy")[0]) == 1 for r in range(2))
