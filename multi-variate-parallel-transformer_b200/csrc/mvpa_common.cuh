@@ -41,6 +41,7 @@ struct BwdArgs {
   float *dtbg, *dcbg;  // gradients w.r.t. the unscaled relative scores
   float* delta;        // (B*H, N)
   float* partial;      // (B*H*nQT, 3, D) per-tile column sums for du/dvt/dz
+  float* tc_extra;     // workspace of the tensor-core query-side kernel (bf16 problems it supports)
 };
 
 void set_error(const char* fmt, ...);
@@ -57,6 +58,12 @@ bool tc_fwd_supported(const Args& a);
 size_t tc_fwd_workspace_bytes(const mvpa_problem* p);
 int tc_fwd(const Args& a, void* workspace, size_t workspace_bytes, cudaStream_t s);
 int tc_fwd_static(const Args& a, cudaStream_t s);  // same, scratch in a built-in device array
+
+// tcgen05 query side of the backward for bf16 (mvpa_tc_bwd.cu): content part of dq (fp32) and the
+// gradients of the two relative score matrices, into the workspace of the CUDA-core backward.
+bool tc_bwd_q_supported(const Args& a);
+size_t tc_bwd_q_workspace_floats(const mvpa_problem* p);
+int tc_bwd_q(const BwdArgs& b, float* extra_workspace, cudaStream_t s);
 
 template <typename T>
 __device__ __forceinline__ float to_f32(T x);

@@ -1,0 +1,568 @@
+// Flash-MVPA backward for bf16 on sm_100a, query side: dQ (content part) and the gradients of the
+// two relative score matrices, on tcgen05 tensor cores with TMEM accumulators and TMA-staged tiles.
+//
+// Replaces, for the query side, `_bwd_kernel_one_col_block` (`attentions/attn.py:561-751`):
+//   P  = exp2(S2 - L)                      S2 as in the forward, L = m + log2 l saved by it
+//   dP = dO V^T                            (`:677`)
+//   dS = P o (dP - delta) * sm_scale       (`:680`)
+//   dQ += (dS o win) K                     (`:708-730`)
+//   dTB[i, T-1-(t_i-t_k)] += sum_{c_k} dS[i,k],  dCB[i, C-1-|c_i-c_k|] += sum_{t_k} dS[i,k]   (`:681-707`)
+// The reference builds the two relative-score gradients with 0/1 "csm" matmuls and atomics; here a
+// thread owns a query row, so they are plain register sums (per key time step / per channel slot).
+//
+// Same CTA shape as the forward (mvpa_tc_fwd.cu): 128 query rows of one (b,h); two softmax
+// warpgroups (thread = TMEM lane = query row, 64 key columns each), one TMA producer lane, one MMA
+// issuer lane; dense tiles (inside the content window) first, then light tiles.  Per dense tile
+// three products: S = Q'K^T, dP = dO V^T, dQ += dS_w K (dS_w as bf16 in TMEM, K as MN-major
+// operand); a light tile needs dP only: its content term is zero-filled, so it contributes to the
+// relative-score gradients but not to dQ's content part, and P is the outer product of the forward.
+//
+// TMEM columns: [0,128) S / dS, [128,256) dP, [256,256+D) dQ, [384,512) raw temporal products.
+// S / dP are single-buffered: MMA and softmax work alternate within a CTA.
+#include <cuda_fp16.h>
+
+#include "mvpa_common.cuh"
+#include "tc_ptx.cuh"
+#include "tc_tma_host.cuh"
+
+namespace mvpa {
+namespace {
+
+using namespace ptx;
+
+constexpr int kSoftmaxThreads = 256;
+constexpr int kThreads = 384;  // warps 10, 11 only donate their registers
+constexpr int kTmemCols = 512;
+constexpr uint32_t kColS = 0;
+constexpr uint32_t kColDP = 128;
+constexpr uint32_t kColDQ = 256;
+constexpr uint32_t kColTB = 384;
+
+struct BqMaps {
+  CUtensorMap q, k, v, dout, rt, rc;
+};
+
+struct BqArgs {
+  const __nv_bfloat16* u;
+  const float* relc;   // (Hkv, 256): vt.r_time[j] at [0,128), z.r_chan[j] at [128,256)
+  const float* lse;    // (B*H, N) base-2 log-sum-exp of the forward
+  const float* delta;  // (B*H, N) sum_d dO*O
+  float* dqc;          // (B*H, N, D) content part of dq
+  float* dtb;          // (B*H, N, T) zero-initialised; column T-1-(t_i-t_k)
+  float* dcb;          // (B*H, N, C) column C-1-|c_i-c_k|
+  int B, H, Hkv, T, C, g, window, n_qt;
+  float c2, sm_scale;
+  int* status;
+};
+
+enum BarrierIndex {
+  kBarProFull = 0, kBarProMma, kBarProDone, kBarSdpFull, kBarDsFull, kBarAllDone,
+  kBarSlotFull,  // NS, then slot_free NS
+};
+
+template <int D>
+struct Cfg {
+  static constexpr int NH = D / 64;
+  static constexpr int HALF = 16384;
+  static constexpr int TILE = NH * HALF;
+  static constexpr int NS = D == 64 ? 8 : 4;       // K/V ring slots (dense tile: K and V; light: V)
+  static constexpr int PRO_SLOTS = 65536 / TILE;   // borrowed by the prologue (sR + sC, then scratch)
+  static constexpr int EARLY = NS - PRO_SLOTS;
+  static constexpr int SMEM_Q = 0;
+  static constexpr int SMEM_DO = TILE;
+  static constexpr int SMEM_RING = 2 * TILE;
+  static constexpr int SMEM_PRO = SMEM_RING + EARLY * TILE;
+  static constexpr int SMEM_TAIL = SMEM_RING + NS * TILE;
+  // tail: u (D f32), vR[128], zC[128], smax[2][128], barriers, tmem slot, abort
+  static constexpr int TAIL_FLOATS = D + 128 + 128 + 256;
+  static constexpr int TAIL_BYTES = TAIL_FLOATS * 4 + (kBarSlotFull + 2 * NS) * 8 + 16;
+  static constexpr int SMEM_BYTES = SMEM_TAIL + TAIL_BYTES + 1024;
+};
+
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, status, code));
+}
+// All 256 softmax threads; only called outside data-dependent control flow.
+__device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+__device__ __forceinline__ int light_tiles(int I, int TPB, int window, int n_qt) {
+  if (window <= 0 || I == n_qt - 1) return 0;
+  const int x = I * TPB - TPB - window;
+  return x < 0 ? 0 : x / TPB + 1;
+}
+
+__global__ void __launch_bounds__(256) rel_const_kernel(const __nv_bfloat16* __restrict__ vt,
+                                                        const __nv_bfloat16* __restrict__ z,
+                                                        const __nv_bfloat16* __restrict__ rt,
+                                                        const __nv_bfloat16* __restrict__ rc, float* __restrict__ relc,
+                                                        int T, int C, int D) {
+  const int hk = blockIdx.x, j = threadIdx.x & 127;
+  const bool is_t = threadIdx.x < 128;
+  const int rows = is_t ? T : C;
+  float acc = 0.f;
+  if (j < rows) {
+    const __nv_bfloat16* key = (is_t ? rt : rc) + ((size_t)hk * rows + j) * D;
+    const __nv_bfloat16* bias = (is_t ? vt : z) + (size_t)hk * D;
+    for (int d = 0; d < D; d += 2) {
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(key + d));
+      const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(bias + d));
+      acc += a.x * b.x + a.y * b.y;
+    }
+  }
+  relc[hk * 256 + threadIdx.x] = acc;
+}
+
+template <int D, int CP>
+__global__ void __launch_bounds__(kThreads, 1)
+tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
+  using C_ = Cfg<D>;
+  constexpr int NH = C_::NH, HALF = C_::HALF, TILE = C_::TILE, NS = C_::NS;
+  constexpr int TPB = 128 / CP;
+  constexpr int TPW = TPB >= 2 ? TPB / 2 : 1;
+  constexpr int NCH = CP < 64 ? CP : 64;
+  constexpr int KSTEPS = D / 16;
+  constexpr int DW = D / 2;
+  static_assert(CP >= 32 && CP <= 128 && (CP & (CP - 1)) == 0, "CP in {32,64,128}");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem + C_::SMEM_Q;
+  uint8_t* sDO = smem + C_::SMEM_DO;
+  uint8_t* ring = smem + C_::SMEM_RING;
+  uint8_t* sR = smem + C_::SMEM_PRO;
+  uint8_t* sC = sR + TILE;
+  float* scratch = reinterpret_cast<float*>(smem + C_::SMEM_PRO);  // [128][CP]
+  float* s_bias = reinterpret_cast<float*>(smem + C_::SMEM_TAIL);  // u as fp32
+  float* s_vr = s_bias + D;
+  float* s_zc = s_vr + 128;
+  float* s_max = s_zc + 128;  // [2 wg][128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_max + 256);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kBarSlotFull + 2 * NS);
+  int* s_abort = reinterpret_cast<int*>(tmem_slot + 1);
+  uint64_t* slot_full = bars + kBarSlotFull;
+  uint64_t* slot_free = slot_full + NS;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int BH = p.B * p.H;
+  const int I = p.n_qt - 1 - (int)(blockIdx.x / BH);
+  const int bh = blockIdx.x % BH, b = bh / p.H, h = bh % p.H, hk = h / p.g;
+  const int n_tiles = I + 1;
+  const int n_light = light_tiles(I, TPB, p.window, p.n_qt);
+  const int n_dense = n_tiles - n_light;
+  auto tile_of = [&](int s) { return s < n_dense ? n_light + s : s - n_dense; };
+  auto q_of_k = [&](int s) { return 2 * s; };
+  auto q_of_v = [&](int s) { return s < n_dense ? 2 * s + 1 : n_dense + s; };
+  const int T = p.T, C = p.C;
+
+  if (tid == 0) {
+    *s_abort = *p.status;
+    mbar_init(&bars[kBarProFull], 1);
+    mbar_init(&bars[kBarProMma], 1);
+    mbar_init(&bars[kBarProDone], kSoftmaxThreads);
+    mbar_init(&bars[kBarSdpFull], 1);
+    mbar_init(&bars[kBarDsFull], kSoftmaxThreads);
+    mbar_init(&bars[kBarAllDone], 1);
+    for (int i = 0; i < NS; ++i) {
+      mbar_init(&slot_full[i], 1);
+      mbar_init(&slot_free[i], 1);
+    }
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (*s_abort != 0) return;
+  if (warp == 9) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp >= 8) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+  if (warp == 8) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      prefetch_tensormap(&maps.q);
+      prefetch_tensormap(&maps.k);
+      prefetch_tensormap(&maps.v);
+      prefetch_tensormap(&maps.dout);
+      mbar_arrive_expect_tx(&bars[kBarProFull], 3 * TILE + NH * CP * 128);
+      for (int hh = 0; hh < NH; ++hh) {
+        tma_load_5d(sQ + hh * HALF, &maps.q, &bars[kBarProFull], hh * 64, 0, I * TPB, h, b);
+        tma_load_5d(sDO + hh * HALF, &maps.dout, &bars[kBarProFull], hh * 64, 0, I * TPB, h, b);
+        tma_load_3d(sR + hh * HALF, &maps.rt, &bars[kBarProFull], hh * 64, 0, hk);
+        tma_load_3d(sC + hh * CP * 128, &maps.rc, &bars[kBarProFull], hh * 64, 0, hk);
+      }
+      bool ok = true;
+      auto load_slot = [&](const CUtensorMap* map, int q, int J) {
+        if (q == C_::EARLY) ok = mbar_wait(&bars[kBarProDone], 0, p.status, 110);
+        const int sl = q % NS;
+        if (ok && q >= NS) ok = mbar_wait(&slot_free[sl], ((q / NS) - 1) & 1, p.status, 111);
+        if (!ok) return;
+        uint8_t* dst = ring + sl * TILE;
+        mbar_arrive_expect_tx(&slot_full[sl], TILE);
+#pragma unroll
+        for (int hh = 0; hh < NH; ++hh) tma_load_5d(dst + hh * HALF, map, &slot_full[sl], hh * 64, 0, J * TPB, hk, b);
+      };
+      for (int s = 0; ok && s < n_tiles; ++s) {
+        const int J = tile_of(s);
+        if (s < n_dense) load_slot(&maps.k, q_of_k(s), J);
+        if (ok) load_slot(&maps.v, q_of_v(s), J);
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------- MMA issuer -------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0);
+      constexpr uint32_t idesc_c = make_idesc_bf16(128, CP, 0);
+      constexpr uint32_t idesc_q = make_idesc_bf16(128, D, 1);
+      const DescHalves dq = make_desc_halves_sw128(smem_u32(sQ), 16, 1024);
+      const DescHalves ddo = make_desc_halves_sw128(smem_u32(sDO), 16, 1024);
+      const DescHalves dkm0 = make_desc_halves_sw128(smem_u32(ring), 16, 1024);    // K-major view of a slot
+      const DescHalves dmn0 = make_desc_halves_sw128(smem_u32(ring), HALF, 1024);  // MN-major view of a slot
+      bool ok = mbar_wait(&bars[kBarProFull], 0, p.status, 120);
+      if (ok) {
+        tc_fence_after();
+        const DescHalves dr = make_desc_halves_sw128(smem_u32(sR), 16, 1024);
+        const DescHalves dc = make_desc_halves_sw128(smem_u32(sC), 16, 1024);
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk) {
+          const uint32_t off = (kk / 4) * HALF + (kk % 4) * 32;
+          mma_ss_h(tmem + kColTB, dq, off, dr, off, idesc_s, kk > 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk) {
+          const uint32_t offa = (kk / 4) * HALF + (kk % 4) * 32;
+          const uint32_t offb = (kk / 4) * (CP * 128) + (kk % 4) * 32;
+          mma_ss_h(tmem + kColS, dq, offa, dc, offb, idesc_c, kk > 0);
+        }
+        mma_commit(&bars[kBarProMma]);
+        ok = mbar_wait(&bars[kBarProDone], 0, p.status, 121);
+      }
+      int prev_k_sl = -1;  // K slot of the previous tile if it was dense (its dQ product is still owed)
+      for (int s = 0; ok && s <= n_tiles; ++s) {
+        if (s > 0) {
+          // softmax warps are done with tile s-1: dS_w sits in the S columns, dP has been read
+          ok = mbar_wait(&bars[kBarDsFull], (s - 1) & 1, p.status, 122);
+          if (!ok) break;
+          tc_fence_after();
+          if (prev_k_sl >= 0) {  // dQ += dS_w K   (A from TMEM, K as MN-major operand)
+            const uint32_t b_lo = dmn0.lo + (uint32_t)prev_k_sl * (TILE >> 4);
+            mma_ts_x4(tmem + kColDQ, tmem + kColS, b_lo, dmn0.hi, 2048 >> 4, idesc_q, (uint32_t)(s - 1 > 0));
+            mma_ts_x4(tmem + kColDQ, tmem + kColS + 64, b_lo + 4 * (2048 >> 4), dmn0.hi, 2048 >> 4, idesc_q, 1u);
+            mma_commit(&slot_free[prev_k_sl]);
+          }
+        }
+        if (s == n_tiles) break;
+        const bool dense = s < n_dense;
+        const int qv = q_of_v(s), vsl = qv % NS;
+        if (dense) {
+          const int qk = q_of_k(s), ksl = qk % NS;
+          ok = mbar_wait(&slot_full[ksl], (qk / NS) & 1, p.status, 123);
+          if (!ok) break;
+          tc_fence_after();
+          DescHalves dk = dkm0;
+          dk.lo += (uint32_t)ksl * (TILE >> 4);
+#pragma unroll
+          for (int kk = 0; kk < KSTEPS; ++kk) {  // S = Q' K^T
+            const uint32_t off = (kk / 4) * HALF + (kk % 4) * 32;
+            mma_ss_h(tmem + kColS, dq, off, dk, off, idesc_s, kk > 0);
+          }
+          prev_k_sl = ksl;
+        } else {
+          prev_k_sl = -1;
+        }
+        ok = mbar_wait(&slot_full[vsl], (qv / NS) & 1, p.status, 124);
+        if (!ok) break;
+        tc_fence_after();
+        DescHalves dv = dkm0;
+        dv.lo += (uint32_t)vsl * (TILE >> 4);
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk) {  // dP = dO V^T  (V rows = keys, D contiguous: K-major operand)
+          const uint32_t off = (kk / 4) * HALF + (kk % 4) * 32;
+          mma_ss_h(tmem + kColDP, ddo, off, dv, off, idesc_s, kk > 0);
+        }
+        mma_commit(&bars[kBarSdpFull]);
+        mma_commit(&slot_free[vsl]);
+      }
+      mma_commit(&bars[kBarAllDone]);
+    }
+  }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+    // ------------------------------ softmax warps ------------------------------
+    const int row = tid & 127;
+    const int wg = tid >> 7;
+    const int ti_loc = row / CP, c_i = row % CP;
+    const int ti_abs = I * TPB + ti_loc;
+    const bool row_valid = c_i < C && ti_abs < T;
+    const int64_t n_row = (int64_t)bh * T * C + (int64_t)ti_abs * C + c_i;  // global row of this thread
+    const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    const int tt_base = (64 * wg) / CP;
+    const int ck_base = CP == 128 ? 64 * wg : 0;
+    for (int d = tid; d < D; d += kSoftmaxThreads) s_bias[d] = __bfloat162float(p.u[hk * D + d]);
+    s_vr[tid] = p.relc[hk * 256 + tid];  // s_vr and s_zc are adjacent: 256 floats
+    // L = +inf on rows that do not exist: their P is 0 everywhere
+    const float L_i = row_valid ? p.lse[n_row] : INFINITY;
+    const float delta_i = row_valid ? p.delta[n_row] : 0.f;
+    softmax_bar();
+    bool ok = warp_wait(&bars[kBarProMma], 0, p.status, 131);
+    if (ok) {
+      tc_fence_after();
+#pragma unroll
+      for (int ci = 0; ci < CP / 32; ++ci) {
+        if ((ci & 1) == wg) {
+          uint32_t v[32];
+          tmem_ld32(lane_base + kColS + ci * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j4 = 0; j4 < 8; ++j4) {
+            const float4 zc = reinterpret_cast<const float4*>(s_zc)[ci * 8 + j4];
+            const float zz[4] = {zc.x, zc.y, zc.z, zc.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int jj = j4 * 4 + e;
+              scratch[row * CP + ((ci * 32 + jj + 2 * row) & (CP - 1))] = p.c2 * (__uint_as_float(v[jj]) + zz[e]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+    }
+    softmax_bar();
+    __half2 cbl[NCH / 2];
+    float mc = 0.f;
+    {
+      float g[NCH];
+      float mx = -INFINITY;
+#pragma unroll
+      for (int k = 0; k < NCH; ++k) {
+        const int ck = ck_base + k;
+        const int jc = min(max(C - 1 - abs(c_i - ck), 0), CP - 1);
+        const float val = ok ? scratch[row * CP + ((jc + 2 * row) & (CP - 1))] : 0.f;
+        g[k] = (c_i < C && ck < C) ? val : -INFINITY;
+        mx = fmaxf(mx, g[k]);
+      }
+      s_max[wg * 128 + row] = mx;
+      softmax_bar();
+      mx = fmaxf(mx, s_max[(wg ^ 1) * 128 + row]);
+      mc = (mx == -INFINITY) ? 0.f : mx;
+#pragma unroll
+      for (int k2 = 0; k2 < NCH / 2; ++k2) cbl[k2] = __floats2half2_rn(g[2 * k2] - mc, g[2 * k2 + 1] - mc);
+      if (ok) {
+        const float4* u4 = reinterpret_cast<const float4*>(s_bias);
+#pragma unroll
+        for (int cc = 0; cc < D / 16; ++cc) {
+          const int chunk = wg * (D / 16) + cc, hh = chunk / 8, c = chunk % 8;
+          const uint32_t off = hh * HALF + row * 128 + ((c ^ (row & 7)) << 4);
+          const uint4 raw = *reinterpret_cast<const uint4*>(sQ + off);
+          const float4 b0 = u4[chunk * 2], b1 = u4[chunk * 2 + 1];
+          uint4 out;
+          out.x = pack_bf16((__uint_as_float(raw.x << 16) + b0.x) * p.c2, (__uint_as_float(raw.x & 0xffff0000u) + b0.y) * p.c2);
+          out.y = pack_bf16((__uint_as_float(raw.y << 16) + b0.z) * p.c2, (__uint_as_float(raw.y & 0xffff0000u) + b0.w) * p.c2);
+          out.z = pack_bf16((__uint_as_float(raw.z << 16) + b1.x) * p.c2, (__uint_as_float(raw.z & 0xffff0000u) + b1.y) * p.c2);
+          out.w = pack_bf16((__uint_as_float(raw.w << 16) + b1.z) * p.c2, (__uint_as_float(raw.w & 0xffff0000u) + b1.w) * p.c2);
+          *reinterpret_cast<uint4*>(sQ + off) = out;
+        }
+        fence_proxy_async_smem();
+      }
+    }
+    mbar_arrive(&bars[kBarProDone]);
+
+    // gradient of the channel scores, per channel slot of this thread's columns (summed over time)
+    float dcb_acc[NCH];
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) dcb_acc[k] = 0.f;
+    const float off_row = mc - L_i;  // every exponent carries +mc (cbl is relative to it) and -L
+
+    for (int s = 0; ok && s < n_tiles; ++s) {
+      const bool dense = s < n_dense;
+      const int J = tile_of(s);
+      ok = warp_wait(&bars[kBarSdpFull], s & 1, p.status, 132);
+      if (!ok) break;
+      tc_fence_after();
+      // temporal scores of this thread's key time steps
+      float offs[TPW], wmul[TPW], dtb_acc[TPW];
+      int slot[TPW];
+      bool valid[TPW];
+      {
+        uint32_t raw[TPW];
+#pragma unroll
+        for (int tl = 0; tl < TPW; ++tl) {
+          const int tk_abs = J * TPB + tt_base + tl, dt = ti_abs - tk_abs;
+          valid[tl] = dt >= 0 && tk_abs < T && row_valid;
+          slot[tl] = T - 1 - min(max(dt, 0), T - 1);
+          wmul[tl] = (p.window > 0 && dt > p.window && ti_abs != T - 1) ? 0.f : 1.f;
+          dtb_acc[tl] = 0.f;
+          tmem_ld1(lane_base + kColTB + slot[tl], raw[tl]);
+        }
+        tmem_ld_wait();
+#pragma unroll
+        for (int tl = 0; tl < TPW; ++tl)
+          offs[tl] = valid[tl] ? p.c2 * (__uint_as_float(raw[tl]) + s_vr[slot[tl]]) + off_row : -INFINITY;
+      }
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t sv[32], dp[32];
+        if (dense) tmem_ld32(lane_base + kColS + 64 * wg + 32 * half, sv);
+        tmem_ld32(lane_base + kColDP + 64 * wg + 32 * half, dp);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int jj = 0; jj < 32; jj += 2) {
+          const int lc = 32 * half + jj, tl = lc / CP, k = lc % NCH;
+          const float2 cb = __half22float2(cbl[k / 2]);
+          const float s0 = dense ? fmaf(__uint_as_float(sv[jj]), wmul[tl], cb.x) : cb.x;
+          const float s1 = dense ? fmaf(__uint_as_float(sv[jj + 1]), wmul[tl], cb.y) : cb.y;
+          const float p0 = ex2(s0 + offs[tl]), p1 = ex2(s1 + offs[tl]);
+          const float ds0 = p0 * (__uint_as_float(dp[jj]) - delta_i) * p.sm_scale;      // `attentions/attn.py:680`
+          const float ds1 = p1 * (__uint_as_float(dp[jj + 1]) - delta_i) * p.sm_scale;
+          dcb_acc[k] += ds0;
+          dcb_acc[k + 1] += ds1;
+          dtb_acc[tl] += ds0 + ds1;
+          pk[jj / 2] = pack_bf16(ds0 * wmul[tl], ds1 * wmul[tl]);  // content term only inside the window
+        }
+        if (dense) tmem_st16(lane_base + kColS + 64 * wg + 16 * half, pk);  // dS_w over consumed S columns
+      }
+      if (dense) tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&bars[kBarDsFull]);
+      // row sums per key time step; both warpgroups may own part of a time step (CP = 128)
+#pragma unroll
+      for (int tl = 0; tl < TPW; ++tl)
+        if (valid[tl]) atomicAdd(&p.dtb[n_row * T + slot[tl]], dtb_acc[tl]);
+    }
+    // ------------------------------- epilogue ---------------------------------
+    if (ok) ok = warp_wait(&bars[kBarAllDone], 0, p.status, 134);
+    // channel-score gradient: from key-channel slots to |c_i - c_k| slots, through shared memory
+    float* sc = reinterpret_cast<float*>(ring);  // [128][CP]; every TMA load has been consumed by now
+    if (CP == 128 || wg == 0) {
+#pragma unroll
+      for (int k = 0; k < NCH; ++k) sc[row * CP + ((ck_base + k + 2 * row) & (CP - 1))] = dcb_acc[k];
+    }
+    softmax_bar();
+    if (CP < 128 && wg == 1) {  // both warpgroups hold sums for the same channel slots (different time steps)
+#pragma unroll
+      for (int k = 0; k < NCH; ++k) sc[row * CP + ((k + 2 * row) & (CP - 1))] += dcb_acc[k];
+    }
+    softmax_bar();
+    if (ok && row_valid) {
+      for (int e = wg * (CP / 2); e < (wg + 1) * (CP / 2) && e < C; ++e) {
+        float val = 0.f;
+        if (c_i - e >= 0) val += sc[row * CP + ((c_i - e + 2 * row) & (CP - 1))];
+        if (e > 0 && c_i + e < C) val += sc[row * CP + ((c_i + e + 2 * row) & (CP - 1))];
+        p.dcb[n_row * C + (C - 1 - e)] = val;
+      }
+    }
+    if (ok) {
+      tc_fence_after();
+      float* out = p.dqc + n_row * D + wg * DW;
+#pragma unroll
+      for (int c0 = 0; c0 < DW; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld32(lane_base + kColDQ + wg * DW + c0, v);
+        tmem_ld_wait();
+        if (row_valid) {
+#pragma unroll
+          for (int q4 = 0; q4 < 8; ++q4)
+            *reinterpret_cast<uint4*>(out + c0 + q4 * 4) = make_uint4(v[q4 * 4], v[q4 * 4 + 1], v[q4 * 4 + 2], v[q4 * 4 + 3]);
+        }
+      }
+    }
+    tc_fence_before();
+  }
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+int make_maps(BqMaps& m, const BwdArgs& bw, int CP) {
+  const Args& a = bw.a;
+  const int TPB = 128 / CP;
+  const uint64_t es = 2;
+  const uint32_t box[5] = {64, (uint32_t)CP, (uint32_t)TPB, 1, 1};
+  int rc;
+  auto enc5 = [&](CUtensorMap* map, const void* ptr, int heads, int64_t sn, int64_t sh, int64_t sb) {
+    const uint64_t dims[5] = {(uint64_t)a.D, (uint64_t)a.C, (uint64_t)a.T, (uint64_t)heads, (uint64_t)a.B};
+    const uint64_t str[4] = {(uint64_t)sn * es, (uint64_t)sn * a.C * es, (uint64_t)sh * es, (uint64_t)sb * es};
+    return encode_bf16_sw128(map, ptr, 5, dims, str, box);
+  };
+  if ((rc = enc5(&m.q, a.q, a.H, a.q_sn, a.q_sh, a.q_sb))) return rc;
+  if ((rc = enc5(&m.dout, bw.d_o, a.H, bw.do_sn, bw.do_sh, bw.do_sb))) return rc;
+  if ((rc = enc5(&m.k, a.k, a.Hkv, a.k_sn, a.k_sh, a.k_sb))) return rc;
+  if ((rc = enc5(&m.v, a.v, a.Hkv, a.v_sn, a.v_sh, a.v_sb))) return rc;
+  {
+    const uint64_t dims[3] = {(uint64_t)a.D, (uint64_t)a.T, (uint64_t)a.Hkv};
+    const uint64_t str[2] = {(uint64_t)a.D * es, (uint64_t)a.T * a.D * es};
+    const uint32_t b3[3] = {64, 128, 1};
+    if ((rc = encode_bf16_sw128(&m.rt, a.rt, 3, dims, str, b3))) return rc;
+  }
+  {
+    const uint64_t dims[3] = {(uint64_t)a.D, (uint64_t)a.C, (uint64_t)a.Hkv};
+    const uint64_t str[2] = {(uint64_t)a.D * es, (uint64_t)a.C * a.D * es};
+    const uint32_t b3[3] = {64, (uint32_t)CP, 1};
+    if ((rc = encode_bf16_sw128(&m.rc, a.rc, 3, dims, str, b3))) return rc;
+  }
+  return MVPA_OK;
+}
+
+template <int D, int CP>
+int launch(const BwdArgs& bw, float* dqc, int* status, float* relc, cudaStream_t s) {
+  const Args& a = bw.a;
+  BqMaps maps;
+  int rc = make_maps(maps, bw, CP);
+  if (rc) return rc;
+  BqArgs t;
+  t.u = (const __nv_bfloat16*)a.u;
+  t.relc = relc; t.lse = a.lse; t.delta = bw.delta;
+  t.dqc = dqc; t.dtb = bw.dtbg; t.dcb = bw.dcbg;
+  t.B = a.B; t.H = a.H; t.Hkv = a.Hkv; t.T = a.T; t.C = a.C; t.g = a.g; t.window = a.window;
+  constexpr int TPB = 128 / CP;
+  t.n_qt = (a.T + TPB - 1) / TPB;
+  t.c2 = a.c2; t.sm_scale = a.sm_scale;
+  t.status = status;
+  constexpr int smem = Cfg<D>::SMEM_BYTES;
+  static_assert(smem <= 232448, "shared memory budget");
+  static_assert(Cfg<D>::EARLY >= 2, "the first tile's K and V load while the prologue runs");
+  MVPA_CUDA_CHECK(cudaFuncSetAttribute(tc_bwd_q_kernel<D, CP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  MVPA_CUDA_CHECK(cudaMemsetAsync(status, 0, 256, s));
+  MVPA_CUDA_CHECK(cudaMemsetAsync(bw.dtbg, 0, sizeof(float) * (size_t)a.B * a.H * a.N * a.T, s));
+  rel_const_kernel<<<a.Hkv, 256, 0, s>>>((const __nv_bfloat16*)a.vt, (const __nv_bfloat16*)a.z,
+                                        (const __nv_bfloat16*)a.rt, (const __nv_bfloat16*)a.rc, relc, a.T, a.C, D);
+  const unsigned grid = (unsigned)t.n_qt * a.B * a.H;
+  tc_bwd_q_kernel<D, CP><<<grid, kThreads, smem, s>>>(maps, t);
+  count_launch(2);
+  MVPA_CUDA_CHECK(cudaGetLastError());
+  return MVPA_OK;
+}
+
+}  // namespace
+
+bool tc_bwd_q_supported(const Args& a) { return (a.D == 64 || a.D == 128) && a.C <= 128 && a.T <= 128; }
+
+// extra fp32 workspace elements of the tensor-core query-side backward: dq content part, status, constants
+size_t tc_bwd_q_workspace_floats(const mvpa_problem* p) {
+  return (size_t)p->B * p->H * p->T * p->C * p->D + 64 + (size_t)p->Hkv * 256;
+}
+
+int tc_bwd_q(const BwdArgs& bw, float* extra, cudaStream_t s) {
+  const Args& a = bw.a;
+  float* dqc = extra;
+  int* status = reinterpret_cast<int*>(extra + (size_t)a.B * a.H * a.N * a.D);
+  float* relc = reinterpret_cast<float*>(status) + 64;
+  const int CP = a.C <= 32 ? 32 : (a.C <= 64 ? 64 : 128);
+  if (a.D == 64) {
+    if (CP == 32) return launch<64, 32>(bw, dqc, status, relc, s);
+    if (CP == 64) return launch<64, 64>(bw, dqc, status, relc, s);
+    return launch<64, 128>(bw, dqc, status, relc, s);
+  }
+  if (CP == 32) return launch<128, 32>(bw, dqc, status, relc, s);
+  if (CP == 64) return launch<128, 64>(bw, dqc, status, relc, s);
+  return launch<128, 128>(bw, dqc, status, relc, s);
+}
+
+}  // namespace mvpa
