@@ -731,7 +731,7 @@ int launch_bwd(const BwdArgs& b, cudaStream_t s) {
   constexpr int LD = D + 4;
   const int n_qt = (a.N + kBM - 1) / kBM;
   const dim3 grid_q(n_qt, a.B * a.H);
-  {
+  if (b.tc_extra == nullptr) {
     const size_t smem = sizeof(float) * kBM * LD;
     simt_rel_kernel<Tin, D><<<grid_q, kThreads, smem, s>>>(b);
     count_launch();
@@ -764,7 +764,7 @@ int launch_bwd(const BwdArgs& b, cudaStream_t s) {
     simt_dq_kernel<Tin, D><<<grid_q, kThreads, smem, s>>>(b);
     count_launch();
   }
-  {
+  if (b.tc_extra == nullptr) {  // (the tensor-core path has produced dK / dV already)
     const size_t smem = sizeof(float) * ((size_t)2 * kBM * LD + 2 * kBN * LD + 2 * kBM * kPLd + 2 * kBN);
     int rc = set_smem(simt_dkv_kernel<Tin, D>, smem);
     if (rc) return rc;

@@ -50,6 +50,11 @@ struct BqArgs {
   float* dqc;          // (B*H, N, D) content part of dq
   float* dtb;          // (B*H, N, T) zero-initialised; column T-1-(t_i-t_k)
   float* dcb;          // (B*H, N, C) column C-1-|c_i-c_k|
+  // per query row, kept for the key-side kernel (which visits every query tile many times):
+  __nv_bfloat16* qp;   // (B*H, N, D)  Q' = (q+u) c2
+  __half* cblw;        // (B*H, N, CP) channel scores gathered by key channel slot, relative to their max
+  float* offw;         // (B*H, N)     that max minus L
+  float* tbw;          // (B*H, N, T)  temporal scores, log2 units
   int B, H, Hkv, T, C, g, window, n_qt;
   float c2, sm_scale;
   int* status;
@@ -311,6 +316,20 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
     bool ok = warp_wait(&bars[kBarProMma], 0, p.status, 131);
     if (ok) {
       tc_fence_after();
+      // temporal scores of the row, for the key-side kernel (each warpgroup dumps half of the columns)
+#pragma unroll
+      for (int c0 = 0; c0 < 64; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld32(lane_base + kColTB + 64 * wg + c0, v);
+        tmem_ld_wait();
+        if (row_valid) {
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) {
+            const int j = 64 * wg + c0 + jj;
+            if (j < T) p.tbw[n_row * T + j] = p.c2 * (__uint_as_float(v[jj]) + s_vr[j]);
+          }
+        }
+      }
 #pragma unroll
       for (int ci = 0; ci < CP / 32; ++ci) {
         if ((ci & 1) == wg) {
@@ -351,6 +370,14 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
       mc = (mx == -INFINITY) ? 0.f : mx;
 #pragma unroll
       for (int k2 = 0; k2 < NCH / 2; ++k2) cbl[k2] = __floats2half2_rn(g[2 * k2] - mc, g[2 * k2 + 1] - mc);
+      if (ok && row_valid && (CP == 128 || wg == 0)) {
+        uint4* dst = reinterpret_cast<uint4*>(p.cblw + n_row * CP + ck_base);
+#pragma unroll
+        for (int m = 0; m < NCH / 8; ++m)
+          dst[m] = make_uint4(*reinterpret_cast<uint32_t*>(&cbl[4 * m]), *reinterpret_cast<uint32_t*>(&cbl[4 * m + 1]),
+                              *reinterpret_cast<uint32_t*>(&cbl[4 * m + 2]), *reinterpret_cast<uint32_t*>(&cbl[4 * m + 3]));
+        if (wg == 0) p.offw[n_row] = mc - L_i;
+      }
       if (ok) {
         const float4* u4 = reinterpret_cast<const float4*>(s_bias);
 #pragma unroll
@@ -365,6 +392,7 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
           out.z = pack_bf16((__uint_as_float(raw.z << 16) + b1.x) * p.c2, (__uint_as_float(raw.z & 0xffff0000u) + b1.y) * p.c2);
           out.w = pack_bf16((__uint_as_float(raw.w << 16) + b1.z) * p.c2, (__uint_as_float(raw.w & 0xffff0000u) + b1.w) * p.c2);
           *reinterpret_cast<uint4*>(sQ + off) = out;
+          if (row_valid) *reinterpret_cast<uint4*>(p.qp + n_row * D + hh * 64 + c * 8) = out;
         }
         fence_proxy_async_smem();
       }
@@ -480,6 +508,328 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Key side: dK, dV.  One CTA owns 128 keys (one key tile) of one (batch, kv head) and visits every
+// query tile that can see them, for each of the g query heads of the group; dK and dV stay in
+// TMEM for the whole CTA, so nothing is accumulated through global memory (the reference adds
+// dK / dV with atomics when g > 1, `attentions/attn.py:752-773`).
+//
+// Per (query tile, key tile) pair, with thread = query row as everywhere else:
+//   S = Q'K^T, dP = dO V^T on tcgen05;  P = exp2(S2 - L), dS = P o (dP - delta) sm_scale in registers;
+//   P and dS_w go to shared memory as bf16 in the MN-major operand layout (keys contiguous), and
+//   dV += P^T dO,  dK += dS_w^T Q'  (`attentions/attn.py:671-675, 718`) read them as the A operand.
+// The per-row quantities of the query tile (Q', gathered channel scores, temporal scores, offsets)
+// come from the workspace the query-side kernel filled.  Light pairs need neither S nor dK.
+// TMEM columns: [0,128) S, [128,256) dP, [256,256+D) dV, [384,384+D) dK.
+struct BkMaps {
+  CUtensorMap qp, dout, k, v;
+};
+struct BkArgs {
+  const __half* cblw;
+  const float *offw, *tbw, *delta;
+  __nv_bfloat16 *dk, *dv;
+  int64_t dk_sb, dk_sh, dk_sn, dv_sb, dv_sh, dv_sn;
+  int B, H, Hkv, T, C, g, window, n_qt;
+  float c2, sm_scale;
+  int* status;
+};
+enum BkBarrier { kKvFull = 0, kQdoFull, kBkSdpFull, kPdsFull, kPairDone, kBkAllDone, kBkBars };
+
+template <int D>
+struct BkCfg {
+  static constexpr int TILE = (D / 64) * 16384;
+  static constexpr int SMEM_K = 0, SMEM_V = TILE, SMEM_Q = 2 * TILE, SMEM_DO = 3 * TILE;
+  static constexpr int SMEM_P = 4 * TILE, SMEM_DS = 4 * TILE + 32768;
+  static constexpr int SMEM_TAIL = 4 * TILE + 65536;
+  static constexpr int SMEM_BYTES = SMEM_TAIL + kBkBars * 8 + 16 + 1024;
+};
+
+template <int D, int CP>
+__global__ void __launch_bounds__(kThreads, 1)
+tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
+  using C_ = BkCfg<D>;
+  constexpr int NH = D / 64, HALF = 16384, TILE = C_::TILE;
+  constexpr int TPB = 128 / CP;
+  constexpr int TPW = TPB >= 2 ? TPB / 2 : 1;
+  constexpr int NCH = CP < 64 ? CP : 64;
+  constexpr int KSTEPS = D / 16;
+  constexpr int DW = D / 2;
+  constexpr uint32_t kColDV = 256, kColDK = 384;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem + C_::SMEM_K;
+  uint8_t* sV = smem + C_::SMEM_V;
+  uint8_t* sQ = smem + C_::SMEM_Q;
+  uint8_t* sDO = smem + C_::SMEM_DO;
+  uint8_t* sP = smem + C_::SMEM_P;
+  uint8_t* sDS = smem + C_::SMEM_DS;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C_::SMEM_TAIL);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kBkBars);
+  int* s_abort = reinterpret_cast<int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int BK = p.B * p.Hkv;
+  const int J = (int)(blockIdx.x / BK);  // earliest key tiles (seen by the most query tiles) first
+  const int bk = blockIdx.x % BK, b = bk / p.Hkv, hk = bk % p.Hkv;
+  const int n_i = p.n_qt - J;            // query tiles J .. n_qt-1
+  const int n_pairs = p.g * n_i;
+  const int T = p.T, C = p.C;
+  auto pair_is_light = [&](int i) {
+    if (p.window <= 0 || i == p.n_qt - 1) return false;
+    return i * TPB - (J * TPB + TPB - 1) > p.window;
+  };
+
+  if (tid == 0) {
+    *s_abort = *p.status;
+    mbar_init(&bars[kKvFull], 1);
+    mbar_init(&bars[kQdoFull], 1);
+    mbar_init(&bars[kBkSdpFull], 1);
+    mbar_init(&bars[kPdsFull], kSoftmaxThreads);
+    mbar_init(&bars[kPairDone], 1);
+    mbar_init(&bars[kBkAllDone], 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (*s_abort != 0) return;
+  if (warp == 9) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp >= 8) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+  if (warp == 8) {
+    if (lane == 0) {  // ---- TMA producer ----
+      prefetch_tensormap(&maps.qp);
+      prefetch_tensormap(&maps.dout);
+      mbar_arrive_expect_tx(&bars[kKvFull], 2 * TILE);
+      for (int hh = 0; hh < NH; ++hh) {
+        tma_load_5d(sK + hh * HALF, &maps.k, &bars[kKvFull], hh * 64, 0, J * TPB, hk, b);
+        tma_load_5d(sV + hh * HALF, &maps.v, &bars[kKvFull], hh * 64, 0, J * TPB, hk, b);
+      }
+      bool ok = true;
+      for (int s = 0; ok && s < n_pairs; ++s) {
+        const int h = hk * p.g + s / n_i, i = J + s % n_i;
+        if (s > 0) ok = mbar_wait(&bars[kPairDone], (s - 1) & 1, p.status, 210);  // Q'/dO buffers are free
+        if (!ok) break;
+        mbar_arrive_expect_tx(&bars[kQdoFull], 2 * TILE);
+        for (int hh = 0; hh < NH; ++hh) {
+          tma_load_5d(sQ + hh * HALF, &maps.qp, &bars[kQdoFull], hh * 64, 0, i * TPB, h, b);
+          tma_load_5d(sDO + hh * HALF, &maps.dout, &bars[kQdoFull], hh * 64, 0, i * TPB, h, b);
+        }
+      }
+    }
+  } else if (warp == 9) {
+    if (lane == 0) {  // ---- MMA issuer ----
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0);
+      constexpr uint32_t idesc_g = make_idesc_bf16_ab(128, D, 1, 1);  // A = P^T / dS^T (MN-major), B MN-major
+      const DescHalves dqk = make_desc_halves_sw128(smem_u32(sQ), 16, 1024);
+      const DescHalves ddok = make_desc_halves_sw128(smem_u32(sDO), 16, 1024);
+      const DescHalves dk = make_desc_halves_sw128(smem_u32(sK), 16, 1024);
+      const DescHalves dv = make_desc_halves_sw128(smem_u32(sV), 16, 1024);
+      const DescHalves dqm = make_desc_halves_sw128(smem_u32(sQ), HALF, 1024);    // MN-major views
+      const DescHalves ddom = make_desc_halves_sw128(smem_u32(sDO), HALF, 1024);
+      const DescHalves dpm = make_desc_halves_sw128(smem_u32(sP), HALF, 1024);
+      const DescHalves ddsm = make_desc_halves_sw128(smem_u32(sDS), HALF, 1024);
+      bool ok = mbar_wait(&bars[kKvFull], 0, p.status, 220);
+      bool dk_started = false;
+      for (int s = 0; ok && s < n_pairs; ++s) {
+        const int i = J + s % n_i;
+        const bool light = pair_is_light(i);
+        ok = mbar_wait(&bars[kQdoFull], s & 1, p.status, 221);
+        if (!ok) break;
+        tc_fence_after();
+        if (!light) {
+#pragma unroll
+          for (int kk = 0; kk < KSTEPS; ++kk) {  // S = Q' K^T
+            const uint32_t off = (kk / 4) * HALF + (kk % 4) * 32;
+            mma_ss_h(tmem + kColS, dqk, off, dk, off, idesc_s, kk > 0);
+          }
+        }
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk) {  // dP = dO V^T
+          const uint32_t off = (kk / 4) * HALF + (kk % 4) * 32;
+          mma_ss_h(tmem + kColDP, ddok, off, dv, off, idesc_s, kk > 0);
+        }
+        mma_commit(&bars[kBkSdpFull]);
+        ok = mbar_wait(&bars[kPdsFull], s & 1, p.status, 222);  // P / dS_w are in shared memory
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)  // dV += P^T dO   (K = 128 query rows, 16 per step)
+          mma_ss_h(tmem + kColDV, dpm, kk * 2048, ddom, kk * 2048, idesc_g, (s > 0 || kk > 0));
+        if (!light) {
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)  // dK += dS_w^T Q'
+            mma_ss_h(tmem + kColDK, ddsm, kk * 2048, dqm, kk * 2048, idesc_g, (dk_started || kk > 0));
+          dk_started = true;
+        }
+        mma_commit(&bars[kPairDone]);
+      }
+      mma_commit(&bars[kBkAllDone]);
+      if (!dk_started) {}  // (a key tile always has its diagonal pair, which is dense)
+    }
+  }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+    const int row = tid & 127;
+    const int wg = tid >> 7;
+    const int ti_loc = row / CP, c_i = row % CP;
+    const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    const int tt_base = (64 * wg) / CP;
+    const int ck_base = CP == 128 ? 64 * wg : 0;
+    bool ok = true;
+    for (int s = 0; ok && s < n_pairs; ++s) {
+      const int h = hk * p.g + s / n_i, i = J + s % n_i;
+      const bool light = pair_is_light(i);
+      const int ti_abs = i * TPB + ti_loc;
+      const bool row_valid = c_i < C && ti_abs < T;
+      const int64_t n_row = ((int64_t)b * p.H + h) * T * C + (int64_t)ti_abs * C + c_i;
+      // per-row quantities of this query tile, from the query-side kernel's workspace
+      __half2 cbl[NCH / 2];
+      float off_row = -INFINITY, delta_i = 0.f;
+      if (row_valid) {
+        const uint4* src = reinterpret_cast<const uint4*>(p.cblw + n_row * CP + ck_base);
+#pragma unroll
+        for (int m = 0; m < NCH / 8; ++m) {
+          const uint4 w = src[m];
+          *reinterpret_cast<uint32_t*>(&cbl[4 * m]) = w.x;
+          *reinterpret_cast<uint32_t*>(&cbl[4 * m + 1]) = w.y;
+          *reinterpret_cast<uint32_t*>(&cbl[4 * m + 2]) = w.z;
+          *reinterpret_cast<uint32_t*>(&cbl[4 * m + 3]) = w.w;
+        }
+        off_row = p.offw[n_row];
+        delta_i = p.delta[n_row];
+      } else {
+#pragma unroll
+        for (int k2 = 0; k2 < NCH / 2; ++k2) cbl[k2] = __floats2half2_rn(0.f, 0.f);
+      }
+      float offs[TPW], wmul[TPW];
+#pragma unroll
+      for (int tl = 0; tl < TPW; ++tl) {
+        const int tk_abs = J * TPB + tt_base + tl, dt = ti_abs - tk_abs;
+        const bool valid = dt >= 0 && tk_abs < T && row_valid;
+        wmul[tl] = (p.window > 0 && dt > p.window && ti_abs != T - 1) ? 0.f : 1.f;
+        offs[tl] = valid ? p.tbw[n_row * T + (T - 1 - dt)] + off_row : -INFINITY;
+      }
+      ok = warp_wait(&bars[kBkSdpFull], s & 1, p.status, 232);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t sv[32], dp[32];
+        if (!light) tmem_ld32(lane_base + kColS + 64 * wg + 32 * half, sv);
+        tmem_ld32(lane_base + kColDP + 64 * wg + 32 * half, dp);
+        tmem_ld_wait();
+        uint32_t pp[16], pd[16];
+#pragma unroll
+        for (int jj = 0; jj < 32; jj += 2) {
+          const int lc = 32 * half + jj, tl = lc / CP, k = lc % NCH;
+          const float2 cb = __half22float2(cbl[k / 2]);
+          const float s0 = !light ? fmaf(__uint_as_float(sv[jj]), wmul[tl], cb.x) : cb.x;
+          const float s1 = !light ? fmaf(__uint_as_float(sv[jj + 1]), wmul[tl], cb.y) : cb.y;
+          const float p0 = ex2(s0 + offs[tl]), p1 = ex2(s1 + offs[tl]);
+          const float ds0 = p0 * (__uint_as_float(dp[jj]) - delta_i) * p.sm_scale * wmul[tl];
+          const float ds1 = p1 * (__uint_as_float(dp[jj + 1]) - delta_i) * p.sm_scale * wmul[tl];
+          pp[jj / 2] = pack_bf16(p0, p1);
+          pd[jj / 2] = pack_bf16(ds0, ds1);
+        }
+        // MN-major operand layout: 64-key block = this warpgroup, one 128-byte row per query row,
+        // 16-byte chunks swizzled by (row mod 8)
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) {
+          const int c = 4 * half + c4;
+          const uint32_t o = wg * HALF + row * 128 + ((c ^ (row & 7)) << 4);
+          *reinterpret_cast<uint4*>(sP + o) = make_uint4(pp[4 * c4], pp[4 * c4 + 1], pp[4 * c4 + 2], pp[4 * c4 + 3]);
+          if (!light)
+            *reinterpret_cast<uint4*>(sDS + o) = make_uint4(pd[4 * c4], pd[4 * c4 + 1], pd[4 * c4 + 2], pd[4 * c4 + 3]);
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(&bars[kPdsFull]);
+    }
+    // ---- epilogue: lane = key row now ----
+    if (ok) ok = warp_wait(&bars[kBkAllDone], 0, p.status, 234);
+    if (ok) {
+      tc_fence_after();
+      const int tk_abs = J * TPB + ti_loc;
+      const bool key_valid = c_i < C && tk_abs < T;
+      const int64_t n = (int64_t)tk_abs * C + c_i;
+      __nv_bfloat16* dvrow = p.dv + b * p.dv_sb + hk * p.dv_sh + n * p.dv_sn + wg * DW;
+      __nv_bfloat16* dkrow = p.dk + b * p.dk_sb + hk * p.dk_sh + n * p.dk_sn + wg * DW;
+      const float inv_c2 = 1.f / p.c2;  // Q' carries c2
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+#pragma unroll
+        for (int c0 = 0; c0 < DW; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld32(lane_base + (which == 0 ? kColDV : kColDK) + wg * DW + c0, v);
+          tmem_ld_wait();
+          if (key_valid) {
+            const float sc = which == 0 ? 1.f : inv_c2;
+            __nv_bfloat16* dst = (which == 0 ? dvrow : dkrow) + c0;
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint32_t w[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                w[e] = pack_bf16(__uint_as_float(v[q4 * 8 + 2 * e]) * sc, __uint_as_float(v[q4 * 8 + 2 * e + 1]) * sc);
+              *reinterpret_cast<uint4*>(dst + q4 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  }
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+template <int D, int CP>
+int launch_kv(const BwdArgs& bw, const BqArgs& q, cudaStream_t s) {
+  const Args& a = bw.a;
+  constexpr int TPB = 128 / CP;
+  const uint64_t es = 2;
+  const uint32_t box[5] = {64, (uint32_t)CP, (uint32_t)TPB, 1, 1};
+  BkMaps m;
+  int rc;
+  auto enc5 = [&](CUtensorMap* map, const void* ptr, int heads, int64_t sn, int64_t sh, int64_t sb) {
+    const uint64_t dims[5] = {(uint64_t)a.D, (uint64_t)a.C, (uint64_t)a.T, (uint64_t)heads, (uint64_t)a.B};
+    const uint64_t str[4] = {(uint64_t)sn * es, (uint64_t)sn * a.C * es, (uint64_t)sh * es, (uint64_t)sb * es};
+    return encode_bf16_sw128(map, ptr, 5, dims, str, box);
+  };
+  if ((rc = enc5(&m.qp, q.qp, a.H, a.D, (int64_t)a.N * a.D, (int64_t)a.H * a.N * a.D))) return rc;
+  if ((rc = enc5(&m.dout, bw.d_o, a.H, bw.do_sn, bw.do_sh, bw.do_sb))) return rc;
+  if ((rc = enc5(&m.k, a.k, a.Hkv, a.k_sn, a.k_sh, a.k_sb))) return rc;
+  if ((rc = enc5(&m.v, a.v, a.Hkv, a.v_sn, a.v_sh, a.v_sb))) return rc;
+  BkArgs t;
+  t.cblw = q.cblw; t.offw = q.offw; t.tbw = q.tbw; t.delta = bw.delta;
+  t.dk = (__nv_bfloat16*)bw.dk; t.dv = (__nv_bfloat16*)bw.dv;
+  t.dk_sb = bw.dk_sb; t.dk_sh = bw.dk_sh; t.dk_sn = bw.dk_sn;
+  t.dv_sb = bw.dv_sb; t.dv_sh = bw.dv_sh; t.dv_sn = bw.dv_sn;
+  t.B = a.B; t.H = a.H; t.Hkv = a.Hkv; t.T = a.T; t.C = a.C; t.g = a.g; t.window = a.window;
+  t.n_qt = q.n_qt; t.c2 = a.c2; t.sm_scale = a.sm_scale; t.status = q.status;
+  constexpr int smem = BkCfg<D>::SMEM_BYTES;
+  static_assert(smem <= 232448, "shared memory budget");
+  MVPA_CUDA_CHECK(cudaFuncSetAttribute(tc_bwd_kv_kernel<D, CP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  const unsigned grid = (unsigned)t.n_qt * a.B * a.Hkv;
+  tc_bwd_kv_kernel<D, CP><<<grid, kThreads, smem, s>>>(m, t);
+  count_launch();
+  MVPA_CUDA_CHECK(cudaGetLastError());
+  return MVPA_OK;
+}
+
 int make_maps(BqMaps& m, const BwdArgs& bw, int CP) {
   const Args& a = bw.a;
   const int TPB = 128 / CP;
@@ -511,7 +861,7 @@ int make_maps(BqMaps& m, const BwdArgs& bw, int CP) {
 }
 
 template <int D, int CP>
-int launch(const BwdArgs& bw, float* dqc, int* status, float* relc, cudaStream_t s) {
+int launch(const BwdArgs& bw, float* dqc, int* status, float* relc, float* rows_ws, cudaStream_t s) {
   const Args& a = bw.a;
   BqMaps maps;
   int rc = make_maps(maps, bw, CP);
@@ -520,6 +870,13 @@ int launch(const BwdArgs& bw, float* dqc, int* status, float* relc, cudaStream_t
   t.u = (const __nv_bfloat16*)a.u;
   t.relc = relc; t.lse = a.lse; t.delta = bw.delta;
   t.dqc = dqc; t.dtb = bw.dtbg; t.dcb = bw.dcbg;
+  {
+    const size_t rows = (size_t)a.B * a.H * a.N;
+    t.qp = reinterpret_cast<__nv_bfloat16*>(rows_ws);
+    t.cblw = reinterpret_cast<__half*>(rows_ws + rows * (D / 2));
+    t.offw = rows_ws + rows * (D / 2) + rows * 64;
+    t.tbw = t.offw + ((rows + 3) & ~(size_t)3);
+  }
   t.B = a.B; t.H = a.H; t.Hkv = a.Hkv; t.T = a.T; t.C = a.C; t.g = a.g; t.window = a.window;
   constexpr int TPB = 128 / CP;
   t.n_qt = (a.T + TPB - 1) / TPB;
@@ -537,7 +894,7 @@ int launch(const BwdArgs& bw, float* dqc, int* status, float* relc, cudaStream_t
   tc_bwd_q_kernel<D, CP><<<grid, kThreads, smem, s>>>(maps, t);
   count_launch(2);
   MVPA_CUDA_CHECK(cudaGetLastError());
-  return MVPA_OK;
+  return launch_kv<D, CP>(bw, t, s);
 }
 
 }  // namespace
@@ -546,7 +903,11 @@ bool tc_bwd_q_supported(const Args& a) { return (a.D == 64 || a.D == 128) && a.C
 
 // extra fp32 workspace elements of the tensor-core query-side backward: dq content part, status, constants
 size_t tc_bwd_q_workspace_floats(const mvpa_problem* p) {
-  return (size_t)p->B * p->H * p->T * p->C * p->D + 64 + (size_t)p->Hkv * 256;
+  const size_t rows = (size_t)p->B * p->H * p->T * p->C;
+  // dq content + status + constants + per-row data for the key side (Q' bf16, channel scores fp16
+  // padded to 128 slots, offset, temporal scores)
+  return rows * p->D + 64 + (size_t)p->Hkv * 256 + rows * (p->D / 2) + rows * 64 + ((rows + 3) & ~(size_t)3) +
+         rows * p->T + 64;
 }
 
 int tc_bwd_q(const BwdArgs& bw, float* extra, cudaStream_t s) {
@@ -554,15 +915,16 @@ int tc_bwd_q(const BwdArgs& bw, float* extra, cudaStream_t s) {
   float* dqc = extra;
   int* status = reinterpret_cast<int*>(extra + (size_t)a.B * a.H * a.N * a.D);
   float* relc = reinterpret_cast<float*>(status) + 64;
+  float* rows_ws = relc + (size_t)a.Hkv * 256;
   const int CP = a.C <= 32 ? 32 : (a.C <= 64 ? 64 : 128);
   if (a.D == 64) {
-    if (CP == 32) return launch<64, 32>(bw, dqc, status, relc, s);
-    if (CP == 64) return launch<64, 64>(bw, dqc, status, relc, s);
-    return launch<64, 128>(bw, dqc, status, relc, s);
+    if (CP == 32) return launch<64, 32>(bw, dqc, status, relc, rows_ws, s);
+    if (CP == 64) return launch<64, 64>(bw, dqc, status, relc, rows_ws, s);
+    return launch<64, 128>(bw, dqc, status, relc, rows_ws, s);
   }
-  if (CP == 32) return launch<128, 32>(bw, dqc, status, relc, s);
-  if (CP == 64) return launch<128, 64>(bw, dqc, status, relc, s);
-  return launch<128, 128>(bw, dqc, status, relc, s);
+  if (CP == 32) return launch<128, 32>(bw, dqc, status, relc, rows_ws, s);
+  if (CP == 64) return launch<128, 64>(bw, dqc, status, relc, rows_ws, s);
+  return launch<128, 128>(bw, dqc, status, relc, rows_ws, s);
 }
 
 }  // namespace mvpa

@@ -334,6 +334,11 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N, int b_mn_ma
          ((uint32_t)(M >> 4) << 24);
 }
 
+// Same with both operand majors selectable (bit 15: A is MN-major, bit 16: B is MN-major).
+__host__ __device__ constexpr uint32_t make_idesc_bf16_ab(int M, int N, int a_mn_major, int b_mn_major) {
+  return make_idesc_bf16(M, N, b_mn_major) | ((uint32_t)a_mn_major << 15);
+}
+
 // Byte offset of element (row, col) of a [rows x 64] bf16 tile stored with the 128-byte swizzle
 // TMA and tcgen05 agree on: 16-byte chunk index XOR (row mod 8).  Tile base must be 1024-aligned.
 __device__ __forceinline__ uint32_t sw128_offset(int row, int col) {
