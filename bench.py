@@ -54,6 +54,15 @@ def flops(B, H, T, C, D, window=10, **_):
     return dict(f_alg=B * H * (2 * D * (p_c + p_w) + 2 * D * N * (T + C)), f_dense=B * H * 4 * D * p_c)
 
 
+def flops_bwd(B, H, T, C, D, window=10, **_):
+    """Algorithmic backward count: dV, dP over causal pairs; recomputed S, dQ, dK over windowed pairs;
+    recomputed relative scores and their two gradient products each."""
+    N = T * C
+    p_c = C * C * T * (T + 1) // 2
+    p_w = C * C * (sum(min(t, window) + 1 for t in range(T - 1)) + T)
+    return B * H * (2 * D * (2 * p_c + 3 * p_w) + 6 * D * N * (T + C))
+
+
 def peaks():
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
@@ -315,6 +324,28 @@ def main():
                 extra[name] = {"ms": m2, "tflops_f_alg": ff["f_alg"] / m2 / 1e9, "tflops_f_dense": ff["f_dense"] / m2 / 1e9,
                                "frac_of_peak_f_alg": ff["f_alg"] / m2 / 1e9 / peak}
                 del tt
+            # training path (BASELINE config 3): forward + backward through autograd, dO ~ N(0,1)
+            ww = WORKLOADS["cfg3"][0]
+            _, tt = make_inputs(torch, dev, ww, seed=2)
+            leaves = {n: x.clone().requires_grad_(True) for n, x in tt.items()}
+            gout = torch.randn(tt["q"].shape, device=dev, dtype=torch.bfloat16)
+            times = []
+            for it in range(6):
+                flush.add_(1)
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                o = attentions.flashmvpa(leaves["q"], leaves["u"], leaves["v"], leaves["z"], leaves["k"], leaves["rt"],
+                                         leaves["rc"], leaves["val"], causal=True, sm_scale=ww["D"] ** -0.5,
+                                         window_size=ww["window"])
+                o.backward(gout)
+                b.record()
+                torch.cuda.synchronize()
+                if it >= 2:
+                    times.append(a.elapsed_time(b))
+            m3 = statistics.mean(times)
+            f3 = flops(**ww)["f_alg"] + flops_bwd(**ww)
+            extra["cfg3_fwd_bwd_B8_T128_C32_D64"] = {"ms": m3, "tflops_f_alg": f3 / m3 / 1e9,
+                                                     "frac_of_peak_f_alg": f3 / m3 / 1e9 / peak}
             out["extra"] = extra
         if not args.no_cpu and world == 1:  # the CPU leg belongs to the single-GPU run (torchrun pins OMP threads to 1)
             sample = dict(w, B=1)

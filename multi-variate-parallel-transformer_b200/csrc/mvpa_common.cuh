@@ -41,6 +41,7 @@ struct BwdArgs {
   float *dtbg, *dcbg;  // gradients w.r.t. the unscaled relative scores
   float* delta;        // (B*H, N)
   float* partial;      // (B*H*nQT, 3, D) per-tile column sums for du/dvt/dz
+  float* drel_part;    // (split, Hkv, T + C, D) split-K partials of dr_time / dr_chan
   float* tc_extra;     // workspace of the tensor-core query-side kernel (bf16 problems it supports)
 };
 

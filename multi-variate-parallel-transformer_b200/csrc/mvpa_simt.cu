@@ -22,6 +22,7 @@ constexpr int kThreads = 256;
 constexpr int kBM = 32;   // rows of the register-tiled products
 constexpr int kBN = 64;   // columns
 constexpr int kPLd = kBN + 1;
+constexpr int kDrelSplit = 32;  // split-K factor of the relative-key gradient reduction
 
 // ---- tile helpers (256 threads: ty = tid/16 owns rows 2ty,2ty+1; tx = tid%16) ----
 
@@ -645,14 +646,21 @@ __global__ void __launch_bounds__(kThreads) simt_drel_kernel(BwdArgs bw, int whi
   const int S = which == 0 ? p.T : p.C;
   const float* dx = which == 0 ? bw.dtbg : bw.dcbg;
   const Tin* bias = (const Tin*)(which == 0 ? p.vt : p.z) + blockIdx.y * D;
-  float* out = (which == 0 ? bw.drt : bw.drc) + (int64_t)blockIdx.y * S * D;
+  // split-K over the (batch, head of the group, 64-row chunk) range: gridDim.z partial sums
+  float* out = bw.drel_part + (((int64_t)blockIdx.z * p.Hkv + blockIdx.y) * (p.T + p.C) + (which == 0 ? 0 : p.T)) * D;
   const int hk = blockIdx.y, s0 = blockIdx.x * 32;
+  const int chunks_per_head = (p.N + kBN - 1) / kBN;
+  const int n_chunks = p.B * p.g * chunks_per_head;
+  const int per_z = (n_chunks + gridDim.z - 1) / gridDim.z;
+  const int c_begin = blockIdx.z * per_z, c_end = min(n_chunks, c_begin + per_z);
   float acc[2][DV] = {};
-  for (int b = 0; b < p.B; ++b)
-    for (int hh = 0; hh < p.g; ++hh) {
+  for (int ch = c_begin; ch < c_end; ++ch) {
+    {
+      const int b = ch / (p.g * chunks_per_head), hh = (ch / chunks_per_head) % p.g;
+      const int m0 = (ch % chunks_per_head) * kBN;
       const int h = hk * p.g + hh, bh = b * p.H + h;
       const Tin* q = (const Tin*)p.q + b * p.q_sb + h * p.q_sh;
-      for (int m0 = 0; m0 < p.N; m0 += kBN) {
+      {
         __syncthreads();
         load_tile<Tin, D>(Qs, q, p.q_sn, m0, p.N, kBN, bias, 1.f);
         for (int idx = tid; idx < kBN * 32; idx += kThreads) {
@@ -674,6 +682,7 @@ __global__ void __launch_bounds__(kThreads) simt_drel_kernel(BwdArgs bw, int whi
         }
       }
     }
+  }
 #pragma unroll
   for (int a = 0; a < 2; ++a) {
     const int s = s0 + 2 * ty + a;
@@ -681,6 +690,20 @@ __global__ void __launch_bounds__(kThreads) simt_drel_kernel(BwdArgs bw, int whi
 #pragma unroll
       for (int e = 0; e < DV; ++e) out[(int64_t)s * D + tx + 16 * e] = acc[a][e];
     }
+  }
+}
+
+// dr_time / dr_chan = sum of the split-K partials of simt_drel_kernel (fixed order: deterministic).
+__global__ void simt_drel_reduce_kernel(BwdArgs bw, int n_z) {
+  const Args& p = bw.a;
+  const int S = p.T + p.C;
+  const int64_t total = (int64_t)p.Hkv * S * p.D;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    float sum = 0.f;
+    for (int zz = 0; zz < n_z; ++zz) sum += bw.drel_part[(int64_t)zz * total + idx];
+    const int d = idx % p.D, sl = (idx / p.D) % S, hk = idx / ((int64_t)p.D * S);
+    if (sl < p.T) bw.drt[((int64_t)hk * p.T + sl) * p.D + d] = sum;
+    else bw.drc[((int64_t)hk * p.C + (sl - p.T)) * p.D + d] = sum;
   }
 }
 
@@ -776,9 +799,10 @@ int launch_bwd(const BwdArgs& b, cudaStream_t s) {
     const size_t smem = sizeof(float) * ((size_t)kBN * 33 + kBN * LD);
     int rc = set_smem(simt_drel_kernel<Tin, D>, smem);
     if (rc) return rc;
-    simt_drel_kernel<Tin, D><<<dim3((a.T + 31) / 32, a.Hkv), kThreads, smem, s>>>(b, 0);
-    simt_drel_kernel<Tin, D><<<dim3((a.C + 31) / 32, a.Hkv), kThreads, smem, s>>>(b, 1);
-    count_launch(2);
+    simt_drel_kernel<Tin, D><<<dim3((a.T + 31) / 32, a.Hkv, kDrelSplit), kThreads, smem, s>>>(b, 0);
+    simt_drel_kernel<Tin, D><<<dim3((a.C + 31) / 32, a.Hkv, kDrelSplit), kThreads, smem, s>>>(b, 1);
+    simt_drel_reduce_kernel<<<148, 256, 0, s>>>(b, kDrelSplit);
+    count_launch(3);
   }
   simt_dbias_kernel<<<dim3(a.Hkv, 3), 128, 0, s>>>(b, n_qt);
   count_launch();
@@ -821,7 +845,8 @@ int simt_bwd(const BwdArgs& b, int dtype, cudaStream_t s) {
 size_t simt_bwd_workspace_floats(const mvpa_problem* p) {
   const size_t BH = (size_t)p->B * p->H, N = (size_t)p->T * p->C;
   const size_t n_qt = (N + kBM - 1) / kBM;
-  size_t n = 2 * BH * N * (p->T + p->C) + BH * N + BH * n_qt * 3 * p->D;
+  size_t n = 2 * BH * N * (p->T + p->C) + BH * N + BH * n_qt * 3 * p->D +
+             (size_t)kDrelSplit * p->Hkv * (p->T + p->C) * p->D;
   n = (n + 63) & ~(size_t)63;  // keep what follows 256-byte aligned
   if (p->dtype == MVPA_BF16) n += tc_bwd_q_workspace_floats(p);
   return n;
@@ -837,7 +862,8 @@ void simt_bwd_carve(BwdArgs& b, float* ws) {
   b.dcbg = b.dtbg + BH * N * a.T;
   b.delta = b.dcbg + BH * N * a.C;
   b.partial = b.delta + BH * N;
-  size_t used = (size_t)(b.partial - ws) + BH * n_qt * 3 * a.D;
+  b.drel_part = b.partial + BH * n_qt * 3 * a.D;
+  size_t used = (size_t)(b.drel_part - ws) + (size_t)kDrelSplit * a.Hkv * (a.T + a.C) * a.D;
   used = (used + 63) & ~(size_t)63;
   b.tc_extra = ws + used;  // only meaningful for bf16 problems; the caller clears it otherwise
 }
