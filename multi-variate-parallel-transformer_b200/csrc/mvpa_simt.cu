@@ -456,82 +456,6 @@ __global__ void __launch_bounds__(kThreads) simt_dq_kernel(BwdArgs bw) {
   for (int idx = tid; idx < valid * C; idx += kThreads) dcbg[idx] = dCBs[idx];
 }
 
-// Finish of the tensor-core query-side backward: dq = dq_content + dTB r_time + dCB r_chan
-// (autograd through `_rel_bias`, `attentions/attn.py:1305-1314`) and the per-tile column sums that
-// become du / dvt / dz.  One CTA per 32 query rows; same partial layout as simt_dq_kernel.
-template <typename Tin, int D>
-__global__ void __launch_bounds__(kThreads) simt_dq_finish_kernel(BwdArgs bw, const float* __restrict__ dqc) {
-  constexpr int DV = D / 16;
-  const Args& p = bw.a;
-  extern __shared__ float smem[];
-  float* dTBs = smem;                 // 32 x T
-  float* dCBs = dTBs + kBM * p.T;     // 32 x C
-  float* red = dCBs + kBM * p.C;      // 16 x D
-  const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
-  const int qt = blockIdx.x, bh = blockIdx.y, b = bh / p.H, h = bh % p.H, hk = h / p.g;
-  const int m0 = qt * kBM, N = p.N, T = p.T, C = p.C;
-  const int valid = min(kBM, N - m0);
-  const float* dtbg = bw.dtbg + ((int64_t)bh * N + m0) * T;
-  const float* dcbg = bw.dcbg + ((int64_t)bh * N + m0) * C;
-  for (int idx = tid; idx < kBM * T; idx += kThreads) dTBs[idx] = idx < valid * T ? dtbg[idx] : 0.f;
-  for (int idx = tid; idx < kBM * C; idx += kThreads) dCBs[idx] = idx < valid * C ? dcbg[idx] : 0.f;
-  __syncthreads();
-  const Tin* rt = (const Tin*)p.rt + (int64_t)hk * T * D;
-  const Tin* rc = (const Tin*)p.rc + (int64_t)hk * C * D;
-  float qacc[2][DV], tacc[2][DV] = {}, cacc[2][DV] = {};
-#pragma unroll
-  for (int a = 0; a < 2; ++a) {
-    const int r = 2 * ty + a;
-#pragma unroll
-    for (int e = 0; e < DV; ++e)
-      qacc[a][e] = r < valid ? dqc[((int64_t)bh * N + m0 + r) * D + tx + 16 * e] : 0.f;
-  }
-  for (int s = 0; s < T; ++s) {
-    const float x0 = dTBs[(2 * ty) * T + s], x1 = dTBs[(2 * ty + 1) * T + s];
-#pragma unroll
-    for (int e = 0; e < DV; ++e) {
-      const float y = to_f32<Tin>(rt[(int64_t)s * D + tx + 16 * e]);
-      tacc[0][e] += x0 * y;
-      tacc[1][e] += x1 * y;
-    }
-  }
-  for (int s = 0; s < C; ++s) {
-    const float x0 = dCBs[(2 * ty) * C + s], x1 = dCBs[(2 * ty + 1) * C + s];
-#pragma unroll
-    for (int e = 0; e < DV; ++e) {
-      const float y = to_f32<Tin>(rc[(int64_t)s * D + tx + 16 * e]);
-      cacc[0][e] += x0 * y;
-      cacc[1][e] += x1 * y;
-    }
-  }
-  Tin* dq = (Tin*)bw.dq + b * bw.dq_sb + h * bw.dq_sh;
-#pragma unroll
-  for (int a = 0; a < 2; ++a) {
-    const int r = 2 * ty + a;
-    if (r < valid) {
-#pragma unroll
-      for (int e = 0; e < DV; ++e)
-        dq[(int64_t)(m0 + r) * bw.dq_sn + tx + 16 * e] = from_f32<Tin>(qacc[a][e] + tacc[a][e] + cacc[a][e]);
-    }
-  }
-  float* part = bw.partial + ((int64_t)bh * gridDim.x + qt) * 3 * D;
-  for (int which = 0; which < 3; ++which) {
-    __syncthreads();
-#pragma unroll
-    for (int e = 0; e < DV; ++e) {
-      const float x = which == 0 ? qacc[0][e] + qacc[1][e]
-                      : which == 1 ? tacc[0][e] + tacc[1][e] : cacc[0][e] + cacc[1][e];
-      red[ty * D + tx + 16 * e] = x;
-    }
-    __syncthreads();
-    for (int d = tid; d < D; d += kThreads) {
-      float sum = 0.f;
-      for (int y = 0; y < 16; ++y) sum += red[y * D + d];
-      part[which * D + d] = sum;
-    }
-  }
-}
-
 // dK / dV side: one CTA per (32 keys, b, kv head); loops over the g query heads of the group and
 // the causal query tiles (64 rows each).  Products are formed transposed (key rows x query cols).
 template <typename Tin, int D>
@@ -633,7 +557,9 @@ __global__ void __launch_bounds__(kThreads) simt_dkv_kernel(BwdArgs bw) {
 }
 
 // dr[hk][slot][d] = sum_{b, h in group, i} dX[b,h,i,slot] * (q[b,h,i,d] + bias[hk][d])
-// One CTA per (32 slots, kv head); streams every query row of the group in chunks of 64.
+// One CTA per (32 slots, kv head, split); streams its share of the group's query rows in chunks
+// of 64.  Also leaves the plain column sums sum_i dX[.,i,slot] per split (they become dvt / dz on
+// the tensor-core path).
 template <typename Tin, int D>
 __global__ void __launch_bounds__(kThreads) simt_drel_kernel(BwdArgs bw, int which) {
   constexpr int LD = D + 4;
@@ -654,6 +580,7 @@ __global__ void __launch_bounds__(kThreads) simt_drel_kernel(BwdArgs bw, int whi
   const int per_z = (n_chunks + gridDim.z - 1) / gridDim.z;
   const int c_begin = blockIdx.z * per_z, c_end = min(n_chunks, c_begin + per_z);
   float acc[2][DV] = {};
+  float colsum = 0.f;  // threads 0..31: one slot each
   for (int ch = c_begin; ch < c_end; ++ch) {
     {
       const int b = ch / (p.g * chunks_per_head), hh = (ch / chunks_per_head) % p.g;
@@ -670,6 +597,10 @@ __global__ void __launch_bounds__(kThreads) simt_drel_kernel(BwdArgs bw, int whi
         }
         __syncthreads();
         // rows >= N hold bias only in Qs but zero in Xs, so they add nothing
+        if (tid < 32) {
+#pragma unroll 8
+          for (int r = 0; r < kBN; ++r) colsum += Xs[r * 33 + tid];
+        }
 #pragma unroll 4
         for (int r = 0; r < kBN; ++r) {
           const float x0 = Xs[r * 33 + 2 * ty], x1 = Xs[r * 33 + 2 * ty + 1];
@@ -691,6 +622,8 @@ __global__ void __launch_bounds__(kThreads) simt_drel_kernel(BwdArgs bw, int whi
       for (int e = 0; e < DV; ++e) out[(int64_t)s * D + tx + 16 * e] = acc[a][e];
     }
   }
+  if (tid < 32 && s0 + tid < S)
+    bw.drel_cs[((int64_t)blockIdx.z * p.Hkv + hk) * (p.T + p.C) + (which == 0 ? 0 : p.T) + s0 + tid] = colsum;
 }
 
 // dr_time / dr_chan = sum of the split-K partials of simt_drel_kernel (fixed order: deterministic).
@@ -765,15 +698,10 @@ int launch_bwd(const BwdArgs& b, cudaStream_t s) {
     count_launch();
   }
   if (b.tc_extra != nullptr) {
-    // bf16 on the tensor cores: dq content part and the relative-score gradients, then the finish
+    // bf16 on the tensor cores: dq, dk, dv and the relative-score gradients
     if constexpr (D >= 64) {
       int rc = tc_bwd_q(b, b.tc_extra, s);
       if (rc) return rc;
-      const size_t smem = sizeof(float) * ((size_t)kBM * (a.T + a.C) + 16 * D);
-      rc = set_smem(simt_dq_finish_kernel<Tin, D>, smem);
-      if (rc) return rc;
-      simt_dq_finish_kernel<Tin, D><<<grid_q, kThreads, smem, s>>>(b, b.tc_extra);
-      count_launch();
     }
   } else {
     const size_t smem = sizeof(float) * ((size_t)2 * kBM * LD + 2 * kBN * LD + 2 * kBM * kPLd +
@@ -803,6 +731,10 @@ int launch_bwd(const BwdArgs& b, cudaStream_t s) {
     simt_drel_kernel<Tin, D><<<dim3((a.C + 31) / 32, a.Hkv, kDrelSplit), kThreads, smem, s>>>(b, 1);
     simt_drel_reduce_kernel<<<148, 256, 0, s>>>(b, kDrelSplit);
     count_launch(3);
+  }
+  if (b.tc_extra != nullptr) {
+    MVPA_CUDA_CHECK(cudaGetLastError());
+    return tc_bwd_bias(b, b.tc_extra, kDrelSplit, s);
   }
   simt_dbias_kernel<<<dim3(a.Hkv, 3), 128, 0, s>>>(b, n_qt);
   count_launch();
@@ -846,7 +778,7 @@ size_t simt_bwd_workspace_floats(const mvpa_problem* p) {
   const size_t BH = (size_t)p->B * p->H, N = (size_t)p->T * p->C;
   const size_t n_qt = (N + kBM - 1) / kBM;
   size_t n = 2 * BH * N * (p->T + p->C) + BH * N + BH * n_qt * 3 * p->D +
-             (size_t)kDrelSplit * p->Hkv * (p->T + p->C) * p->D;
+             (size_t)kDrelSplit * p->Hkv * (p->T + p->C) * (p->D + 1);
   n = (n + 63) & ~(size_t)63;  // keep what follows 256-byte aligned
   if (p->dtype == MVPA_BF16) n += tc_bwd_q_workspace_floats(p);
   return n;
@@ -863,7 +795,8 @@ void simt_bwd_carve(BwdArgs& b, float* ws) {
   b.delta = b.dcbg + BH * N * a.C;
   b.partial = b.delta + BH * N;
   b.drel_part = b.partial + BH * n_qt * 3 * a.D;
-  size_t used = (size_t)(b.drel_part - ws) + (size_t)kDrelSplit * a.Hkv * (a.T + a.C) * a.D;
+  b.drel_cs = b.drel_part + (size_t)kDrelSplit * a.Hkv * (a.T + a.C) * a.D;
+  size_t used = (size_t)(b.drel_cs - ws) + (size_t)kDrelSplit * a.Hkv * (a.T + a.C);
   used = (used + 63) & ~(size_t)63;
   b.tc_extra = ws + used;  // only meaningful for bf16 problems; the caller clears it otherwise
 }

@@ -1,5 +1,5 @@
-// Flash-MVPA backward for bf16 on sm_100a, query side: dQ (content part) and the gradients of the
-// two relative score matrices, on tcgen05 tensor cores with TMEM accumulators and TMA-staged tiles.
+// Flash-MVPA backward for bf16 on sm_100a, query side: dQ and the gradients of the two relative
+// score matrices, on tcgen05 tensor cores with TMEM accumulators and TMA-staged tiles.
 //
 // Replaces, for the query side, `_bwd_kernel_one_col_block` (`attentions/attn.py:561-751`):
 //   P  = exp2(S2 - L)                      S2 as in the forward, L = m + log2 l saved by it
@@ -16,6 +16,9 @@
 // three products: S = Q'K^T, dP = dO V^T, dQ += dS_w K (dS_w as bf16 in TMEM, K as MN-major
 // operand); a light tile needs dP only: its content term is zero-filled, so it contributes to the
 // relative-score gradients but not to dQ's content part, and P is the outer product of the forward.
+// After the last tile the relative-score gradients of the tile's rows go back through the tensor
+// cores: dQ += dTB r_time + dCB r_chan (autograd through `_rel_bias`, `attentions/attn.py:1305-1314`),
+// and dq leaves as bf16.
 //
 // TMEM columns: [0,128) S / dS, [128,256) dP, [256,256+D) dQ, [384,512) raw temporal products.
 // S / dP are single-buffered: MMA and softmax work alternate within a CTA.
@@ -47,7 +50,9 @@ struct BqArgs {
   const float* relc;   // (Hkv, 256): vt.r_time[j] at [0,128), z.r_chan[j] at [128,256)
   const float* lse;    // (B*H, N) base-2 log-sum-exp of the forward
   const float* delta;  // (B*H, N) sum_d dO*O
-  float* dqc;          // (B*H, N, D) content part of dq
+  __nv_bfloat16* dq;   // (B,H,N,D) output, element strides below
+  int64_t dq_sb, dq_sh, dq_sn;
+  float* cs_dq;        // (grid, D) per-CTA column sums of dq (fp32), for du
   float* dtb;          // (B*H, N, T) zero-initialised; column T-1-(t_i-t_k)
   float* dcb;          // (B*H, N, C) column C-1-|c_i-c_k|
   // per query row, kept for the key-side kernel (which visits every query tile many times):
@@ -62,6 +67,7 @@ struct BqArgs {
 
 enum BarrierIndex {
   kBarProFull = 0, kBarProMma, kBarProDone, kBarSdpFull, kBarDsFull, kBarAllDone,
+  kBarFinFull, kBarFinLoaded, kBarFinDone,
   kBarSlotFull,  // NS, then slot_free NS
 };
 
@@ -167,6 +173,9 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
     mbar_init(&bars[kBarSdpFull], 1);
     mbar_init(&bars[kBarDsFull], kSoftmaxThreads);
     mbar_init(&bars[kBarAllDone], 1);
+    mbar_init(&bars[kBarFinFull], kSoftmaxThreads);
+    mbar_init(&bars[kBarFinLoaded], 1);
+    mbar_init(&bars[kBarFinDone], 1);
     for (int i = 0; i < NS; ++i) {
       mbar_init(&slot_full[i], 1);
       mbar_init(&slot_free[i], 1);
@@ -215,6 +224,17 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
         const int J = tile_of(s);
         if (s < n_dense) load_slot(&maps.k, q_of_k(s), J);
         if (ok) load_slot(&maps.v, q_of_v(s), J);
+      }
+      // finish: the relative keys once more (the ring is idle once every product has completed)
+      if (ok) ok = mbar_wait(&bars[kBarAllDone], 0, p.status, 112);
+      if (ok) {
+        uint8_t* fR = ring + 65536;
+        uint8_t* fC = fR + TILE;
+        mbar_arrive_expect_tx(&bars[kBarFinLoaded], TILE + NH * CP * 128);
+        for (int hh = 0; hh < NH; ++hh) {
+          tma_load_3d(fR + hh * HALF, &maps.rt, &bars[kBarFinLoaded], hh * 64, 0, hk);
+          tma_load_3d(fC + hh * CP * 128, &maps.rc, &bars[kBarFinLoaded], hh * 64, 0, hk);
+        }
       }
     }
   } else if (warp == 9) {
@@ -293,6 +313,20 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
         mma_commit(&slot_free[vsl]);
       }
       mma_commit(&bars[kBarAllDone]);
+      // finish: dQ += dTB r_time + dCB r_chan  (autograd through `_rel_bias`, `attentions/attn.py:1305-1314`);
+      // the softmax warps have put dTB / dCB of the tile's rows into TMEM as bf16
+      if (ok) ok = mbar_wait(&bars[kBarFinFull], 0, p.status, 125);
+      if (ok) ok = mbar_wait(&bars[kBarFinLoaded], 0, p.status, 126);
+      if (ok) {
+        tc_fence_after();
+        const DescHalves dfr = make_desc_halves_sw128(smem_u32(ring + 65536), HALF, 1024);
+        const DescHalves dfc = make_desc_halves_sw128(smem_u32(ring + 65536 + TILE), CP * 128, 1024);
+        mma_ts_x4(tmem + kColDQ, tmem + kColS, dfr.lo, dfr.hi, 2048 >> 4, idesc_q, 1u);
+        mma_ts_x4(tmem + kColDQ, tmem + kColS + 32, dfr.lo + 4 * (2048 >> 4), dfr.hi, 2048 >> 4, idesc_q, 1u);
+#pragma unroll
+        for (int kk = 0; kk < CP / 16; ++kk) mma_ts_h(tmem + kColDQ, tmem + kColDP + kk * 8, dfc, kk * 2048, idesc_q, 1u);
+      }
+      mma_commit(&bars[kBarFinDone]);
     }
   }
   } else {
@@ -464,6 +498,28 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
     }
     // ------------------------------- epilogue ---------------------------------
     if (ok) ok = warp_wait(&bars[kBarAllDone], 0, p.status, 134);
+    // du = sum over rows of dq's content part (`attentions/attn.py:1305-1306`: q + q_bias feeds the content
+    // term only): column sums of the accumulator before the relative terms are added to it
+    float* cs = reinterpret_cast<float*>(ring);  // [2 wg][128 rows][DW], columns rotated by the row
+    if (ok) {
+      tc_fence_after();
+#pragma unroll
+      for (int c0 = 0; c0 < DW; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld32(lane_base + kColDQ + wg * DW + c0, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj)
+          cs[(wg * 128 + row) * DW + ((c0 + jj + row) & (DW - 1))] = row_valid ? __uint_as_float(v[jj]) : 0.f;
+      }
+    }
+    softmax_bar();
+    if (row < DW) {  // fixed summation order: deterministic
+      float sum = 0.f;
+      for (int r = 0; r < 128; ++r) sum += cs[(wg * 128 + r) * DW + ((row + r) & (DW - 1))];
+      p.cs_dq[(size_t)blockIdx.x * D + wg * DW + row] = sum;
+    }
+    softmax_bar();
     // channel-score gradient: from key-channel slots to |c_i - c_k| slots, through shared memory
     float* sc = reinterpret_cast<float*>(ring);  // [128][CP]; every TMA load has been consumed by now
     if (CP == 128 || wg == 0) {
@@ -476,17 +532,77 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
       for (int k = 0; k < NCH; ++k) sc[row * CP + ((k + 2 * row) & (CP - 1))] += dcb_acc[k];
     }
     softmax_bar();
-    if (ok && row_valid) {
-      for (int e = wg * (CP / 2); e < (wg + 1) * (CP / 2) && e < C; ++e) {
+    {
+      // e = |c_i - c_k| slots of this thread's half, kept in registers across the barrier below
+      float ev[CP / 2];
+#pragma unroll
+      for (int m = 0; m < CP / 2; ++m) {
+        const int e = wg * (CP / 2) + m;
         float val = 0.f;
-        if (c_i - e >= 0) val += sc[row * CP + ((c_i - e + 2 * row) & (CP - 1))];
-        if (e > 0 && c_i + e < C) val += sc[row * CP + ((c_i + e + 2 * row) & (CP - 1))];
-        p.dcb[n_row * C + (C - 1 - e)] = val;
+        if (row_valid && e < C) {
+          if (c_i - e >= 0) val += sc[row * CP + ((c_i - e + 2 * row) & (CP - 1))];
+          if (e > 0 && c_i + e < C) val += sc[row * CP + ((c_i + e + 2 * row) & (CP - 1))];
+          p.dcb[n_row * C + (C - 1 - e)] = val;
+        }
+        ev[m] = val;
+      }
+      softmax_bar();  // everyone has read the key-slot sums: the rows are rewritten in r_chan-row order
+#pragma unroll
+      for (int m = 0; m < CP / 2; ++m) {
+        const int e = wg * (CP / 2) + m, j = C - 1 - e;
+        if (j >= 0) sc[row * CP + ((j + 2 * row) & (CP - 1))] = ev[m];
+      }
+      if (wg == 0) {  // columns C .. CP-1 do not exist: zero for the product
+        for (int j = C; j < CP; ++j) sc[row * CP + ((j + 2 * row) & (CP - 1))] = 0.f;
       }
     }
+    __threadfence();  // this CTA's atomic row sums in dtb are complete before anyone re-reads them
+    softmax_bar();
+    if (ok) {
+      // dTB (this thread's 64 of the 128 r_time rows) and dCB (its half of the CP r_chan rows) as bf16 A operands
+      uint32_t pk[32];
+#pragma unroll
+      for (int m = 0; m < 32; ++m) {
+        const int j = 64 * wg + 2 * m;
+        const float a0 = (row_valid && j < T) ? __ldcg(&p.dtb[n_row * T + j]) : 0.f;
+        const float a1 = (row_valid && j + 1 < T) ? __ldcg(&p.dtb[n_row * T + j + 1]) : 0.f;
+        pk[m] = pack_bf16(a0, a1);
+      }
+      {
+        uint32_t lo[16], hi[16];
+#pragma unroll
+        for (int m = 0; m < 16; ++m) { lo[m] = pk[m]; hi[m] = pk[16 + m]; }
+        tmem_st16(lane_base + kColS + 32 * wg, lo);
+        tmem_st16(lane_base + kColS + 32 * wg + 16, hi);
+      }
+      // CP = 32: 16 packed columns in all, written by the first warpgroup alone
+      constexpr int NPC = CP == 32 ? 16 : CP / 4;
+      const int jb = CP == 32 ? 0 : wg * (CP / 2);
+      uint32_t pc[NPC];
+#pragma unroll
+      for (int m = 0; m < NPC; ++m) {
+        const int j = jb + 2 * m;
+        pc[m] = pack_bf16(sc[row * CP + ((j + 2 * row) & (CP - 1))], sc[row * CP + ((j + 1 + 2 * row) & (CP - 1))]);
+      }
+      if constexpr (CP == 128) {
+        uint32_t lo[16], hi[16];
+#pragma unroll
+        for (int m = 0; m < 16; ++m) { lo[m] = pc[m]; hi[m] = pc[16 + m]; }
+        tmem_st16(lane_base + kColDP + 32 * wg, lo);
+        tmem_st16(lane_base + kColDP + 32 * wg + 16, hi);
+      } else if constexpr (CP == 64) {
+        tmem_st16(lane_base + kColDP + 16 * wg, pc);
+      } else {
+        if (wg == 0) tmem_st16(lane_base + kColDP, pc);
+      }
+      tmem_st_wait();
+    }
+    tc_fence_before();
+    mbar_arrive(&bars[kBarFinFull]);
+    if (ok) ok = warp_wait(&bars[kBarFinDone], 0, p.status, 135);
     if (ok) {
       tc_fence_after();
-      float* out = p.dqc + n_row * D + wg * DW;
+      __nv_bfloat16* out = p.dq + b * p.dq_sb + h * p.dq_sh + ((int64_t)ti_abs * C + c_i) * p.dq_sn + wg * DW;
 #pragma unroll
       for (int c0 = 0; c0 < DW; c0 += 32) {
         uint32_t v[32];
@@ -494,8 +610,13 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
         tmem_ld_wait();
         if (row_valid) {
 #pragma unroll
-          for (int q4 = 0; q4 < 8; ++q4)
-            *reinterpret_cast<uint4*>(out + c0 + q4 * 4) = make_uint4(v[q4 * 4], v[q4 * 4 + 1], v[q4 * 4 + 2], v[q4 * 4 + 3]);
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              w[e] = pack_bf16(__uint_as_float(v[q4 * 8 + 2 * e]), __uint_as_float(v[q4 * 8 + 2 * e + 1]));
+            *reinterpret_cast<uint4*>(out + c0 + q4 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
         }
       }
     }
@@ -860,8 +981,38 @@ int make_maps(BqMaps& m, const BwdArgs& bw, int CP) {
   return MVPA_OK;
 }
 
+// du / dvt / dz of one kv head: du = sum of the query tiles' content column sums; dvt = (column sums
+// of dTB) r_time, dz = (column sums of dCB) r_chan, the column sums coming from the split partials
+// the relative-key reduction leaves (`_rel_bias` adds q_btime / q_bchan to every row, so their
+// gradients are the row sums of dq's temporal / channel parts).
+__global__ void __launch_bounds__(128) tc_dbias_kernel(const float* __restrict__ cs_dq, const float* __restrict__ drel_cs,
+                                                       int n_split, const __nv_bfloat16* __restrict__ rt,
+                                                       const __nv_bfloat16* __restrict__ rc, float* __restrict__ du,
+                                                       float* __restrict__ dvt, float* __restrict__ dz, int B, int H,
+                                                       int Hkv, int g, int T, int C, int D, int n_qt) {
+  __shared__ float s_cs[256];
+  const int hk = blockIdx.x, S = T + C;
+  for (int j = threadIdx.x; j < S; j += blockDim.x) {
+    float sum = 0.f;
+    for (int zz = 0; zz < n_split; ++zz) sum += drel_cs[((size_t)zz * Hkv + hk) * S + j];
+    s_cs[j] = sum;
+  }
+  __syncthreads();
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float su = 0.f, st = 0.f, sz = 0.f;
+    for (int it = 0; it < n_qt; ++it)
+      for (int b = 0; b < B; ++b)
+        for (int hh = 0; hh < g; ++hh) su += cs_dq[((size_t)it * B * H + (size_t)b * H + hk * g + hh) * D + d];
+    for (int j = 0; j < T; ++j) st += s_cs[j] * __bfloat162float(rt[((size_t)hk * T + j) * D + d]);
+    for (int j = 0; j < C; ++j) sz += s_cs[T + j] * __bfloat162float(rc[((size_t)hk * C + j) * D + d]);
+    du[hk * D + d] = su;
+    dvt[hk * D + d] = st;
+    dz[hk * D + d] = sz;
+  }
+}
+
 template <int D, int CP>
-int launch(const BwdArgs& bw, float* dqc, int* status, float* relc, float* rows_ws, cudaStream_t s) {
+int launch(const BwdArgs& bw, float* cs_dq, int* status, float* relc, float* rows_ws, cudaStream_t s) {
   const Args& a = bw.a;
   BqMaps maps;
   int rc = make_maps(maps, bw, CP);
@@ -869,7 +1020,8 @@ int launch(const BwdArgs& bw, float* dqc, int* status, float* relc, float* rows_
   BqArgs t;
   t.u = (const __nv_bfloat16*)a.u;
   t.relc = relc; t.lse = a.lse; t.delta = bw.delta;
-  t.dqc = dqc; t.dtb = bw.dtbg; t.dcb = bw.dcbg;
+  t.dq = (__nv_bfloat16*)bw.dq; t.dq_sb = bw.dq_sb; t.dq_sh = bw.dq_sh; t.dq_sn = bw.dq_sn;
+  t.cs_dq = cs_dq; t.dtb = bw.dtbg; t.dcb = bw.dcbg;
   {
     const size_t rows = (size_t)a.B * a.H * a.N;
     t.qp = reinterpret_cast<__nv_bfloat16*>(rows_ws);
@@ -901,19 +1053,35 @@ int launch(const BwdArgs& bw, float* dqc, int* status, float* relc, float* rows_
 
 bool tc_bwd_q_supported(const Args& a) { return (a.D == 64 || a.D == 128) && a.C <= 128 && a.T <= 128; }
 
-// extra fp32 workspace elements of the tensor-core query-side backward: dq content part, status, constants
+namespace {
+// per-CTA column sums of dq's content part: at most one query tile per time step
+size_t cs_dq_floats(int B, int H, int T, int D) { return (((size_t)B * H * T * D) + 63) & ~(size_t)63; }
+}  // namespace
+
+// extra fp32 workspace elements of the tensor-core backward
 size_t tc_bwd_q_workspace_floats(const mvpa_problem* p) {
   const size_t rows = (size_t)p->B * p->H * p->T * p->C;
-  // dq content + status + constants + per-row data for the key side (Q' bf16, channel scores fp16
+  // column sums + status + constants + per-row data for the key side (Q' bf16, channel scores fp16
   // padded to 128 slots, offset, temporal scores)
-  return rows * p->D + 64 + (size_t)p->Hkv * 256 + rows * (p->D / 2) + rows * 64 + ((rows + 3) & ~(size_t)3) +
-         rows * p->T + 64;
+  return cs_dq_floats(p->B, p->H, p->T, p->D) + 64 + (size_t)p->Hkv * 256 + rows * (p->D / 2) + rows * 64 +
+         ((rows + 3) & ~(size_t)3) + rows * p->T + 64;
+}
+
+int tc_bwd_bias(const BwdArgs& bw, float* extra, int n_split, cudaStream_t s) {
+  const Args& a = bw.a;
+  const int CP = a.C <= 32 ? 32 : (a.C <= 64 ? 64 : 128), TPB = 128 / CP;
+  tc_dbias_kernel<<<a.Hkv, 128, 0, s>>>(extra, bw.drel_cs, n_split, (const __nv_bfloat16*)a.rt,
+                                       (const __nv_bfloat16*)a.rc, bw.du, bw.dvt, bw.dz, a.B, a.H, a.Hkv, a.g, a.T,
+                                       a.C, a.D, (a.T + TPB - 1) / TPB);
+  count_launch();
+  MVPA_CUDA_CHECK(cudaGetLastError());
+  return MVPA_OK;
 }
 
 int tc_bwd_q(const BwdArgs& bw, float* extra, cudaStream_t s) {
   const Args& a = bw.a;
-  float* dqc = extra;
-  int* status = reinterpret_cast<int*>(extra + (size_t)a.B * a.H * a.N * a.D);
+  float* dqc = extra;  // column sums of dq's content part, one row of D per query-side CTA
+  int* status = reinterpret_cast<int*>(extra + cs_dq_floats(a.B, a.H, a.T, a.D));
   float* relc = reinterpret_cast<float*>(status) + 64;
   float* rows_ws = relc + (size_t)a.Hkv * 256;
   const int CP = a.C <= 32 ? 32 : (a.C <= 64 ? 64 : 128);
