@@ -197,9 +197,19 @@ def make_inputs(torch, dev, w, seed, pinned=False):
     return host, {n: x.to(dev) for n, x in host.items()}
 
 
-def time_kernel(torch, attentions, t, w, steps, warmup, flush):
-    call = lambda: attentions.flashmvpa(t["q"], t["u"], t["v"], t["z"], t["k"], t["rt"], t["rc"], t["val"],
-                                        causal=True, sm_scale=w["D"] ** -0.5, window_size=w["window"])
+def time_kernel(torch, attentions, t, w, steps, warmup, flush, gout=None):
+    """Device time of `steps` calls; with `gout` (the gradient of the output) each call is forward + backward."""
+    fwd = lambda: attentions.flashmvpa(t["q"], t["u"], t["v"], t["z"], t["k"], t["rt"], t["rc"], t["val"],
+                                       causal=True, sm_scale=w["D"] ** -0.5, window_size=w["window"])
+    if gout is None:
+        call = fwd
+    else:
+        t = {n: x.detach().clone().requires_grad_(True) for n, x in t.items()}
+
+        def call():
+            for x in t.values():
+                x.grad = None
+            fwd().backward(gout)
     for _ in range(warmup):
         call()
     torch.cuda.synchronize()
@@ -221,6 +231,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS),
                     help="cfg2 is the benchmark; the others exist for profiling and extra points")
+    ap.add_argument("--pass", dest="passes", default="fwd", choices=["fwd", "fwd_bwd"],
+                    help="fwd is the benchmark; fwd_bwd times forward + backward (training step of the operator)")
     ap.add_argument("--no-extra", action="store_true", help="skip the extra reported points")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
@@ -246,6 +258,11 @@ def main():
     host, t = make_inputs(torch, dev, w, seed=1 + rank, pinned=True)
     flush = torch.zeros(64 * 1024 * 1024, dtype=torch.float32, device=dev)
     f = flops(**w)
+    train = args.passes == "fwd_bwd"
+    gout = torch.randn(t["q"].shape, device=dev, dtype=torch.bfloat16) if train else None
+    if train:  # flops of the step: forward + backward
+        fb = flops_bwd(**w)
+        f = {"f_alg": f["f_alg"] + fb, "f_dense": f["f_dense"] + fb}
 
     def sync_all():
         if world > 1:
@@ -258,7 +275,7 @@ def main():
     clk = ClockSampler(local)
     clk.__enter__()
     sync_all()
-    ms = time_kernel(torch, attentions, t, w, args.steps, args.warmup, flush)
+    ms = time_kernel(torch, attentions, t, w, args.steps, args.warmup, flush, gout)
     sync_all()
     per_call = (lib.mvpa_launch_count() - n0) // (args.steps + args.warmup)  # kernels of the library per call
     launches = per_call * args.steps
@@ -271,14 +288,21 @@ def main():
     # ---- end to end: pinned host inputs -> device -> flashmvpa -> host ----
     big = ("q", "k", "val")
     o_host = torch.empty(host["q"].shape, dtype=torch.bfloat16).pin_memory()
-    h2d = sum(host[n].numel() * 2 for n in host)
+    gout_host = gout.cpu().pin_memory() if train else None
+    h2d = sum(host[n].numel() * 2 for n in host) + (gout_host.numel() * 2 if train else 0)
     d2h = o_host.numel() * 2
 
     def e2e_step():
         d = {n: host[n].to(dev, non_blocking=True) for n in host}
+        if train:
+            d = {n: x.requires_grad_(True) for n, x in d.items()}
         o = attentions.flashmvpa(d["q"], d["u"], d["v"], d["z"], d["k"], d["rt"], d["rc"], d["val"],
                                  causal=True, sm_scale=w["D"] ** -0.5, window_size=w["window"])
-        o_host.copy_(o, non_blocking=True)
+        if train:  # the step's result read back is dq
+            o.backward(gout_host.to(dev, non_blocking=True))
+            o_host.copy_(d["q"].grad, non_blocking=True)
+        else:
+            o_host.copy_(o, non_blocking=True)
 
     for _ in range(args.warmup):
         e2e_step()
@@ -303,14 +327,16 @@ def main():
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": NAME, "per_gpu_batch": w["B"], "global_batch": w["B"] * world,
+            "config": {"workload": NAME + (" (forward + backward)" if train else ""), "per_gpu_batch": w["B"], "global_batch": w["B"] * world,
                        "l2": "256 MiB buffer rewritten between timed launches", "parallelism": f"batch x{world}"},
             "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": int(launches),
             "clocks": clk.summary(),
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": achieved / peak, "traffic": NCU_DRAM_BYTES.get(args.workload), "peak_source": peak_src,
-                         "kernel": "tc_fwd_kernel<%d,%d>" % (w["D"], 32 if w["C"] <= 32 else 64 if w["C"] <= 64 else 128),
+                         "frac": achieved / peak, "traffic": None if train else NCU_DRAM_BYTES.get(args.workload), "peak_source": peak_src,
+                         "kernel": ("whole step (tc_fwd_kernel, tc_bwd_q_kernel, tc_bwd_kv_kernel, simt_drel_kernel)"
+                                    if train else "tc_fwd_kernel<%d,%d>" %
+                                    (w["D"], 32 if w["C"] <= 32 else 64 if w["C"] <= 64 else 128)),
                          "flops_per_launch": f["f_alg"],
                          "achieved_dense_convention": f["f_dense"] / (kernel_ms * 1e-3) / 1e12},
         }
@@ -324,28 +350,15 @@ def main():
                 extra[name] = {"ms": m2, "tflops_f_alg": ff["f_alg"] / m2 / 1e9, "tflops_f_dense": ff["f_dense"] / m2 / 1e9,
                                "frac_of_peak_f_alg": ff["f_alg"] / m2 / 1e9 / peak}
                 del tt
-            # training path (BASELINE config 3): forward + backward through autograd, dO ~ N(0,1)
-            ww = WORKLOADS["cfg3"][0]
-            _, tt = make_inputs(torch, dev, ww, seed=2)
-            leaves = {n: x.clone().requires_grad_(True) for n, x in tt.items()}
-            gout = torch.randn(tt["q"].shape, device=dev, dtype=torch.bfloat16)
-            times = []
-            for it in range(6):
-                flush.add_(1)
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record()
-                o = attentions.flashmvpa(leaves["q"], leaves["u"], leaves["v"], leaves["z"], leaves["k"], leaves["rt"],
-                                         leaves["rc"], leaves["val"], causal=True, sm_scale=ww["D"] ** -0.5,
-                                         window_size=ww["window"])
-                o.backward(gout)
-                b.record()
-                torch.cuda.synchronize()
-                if it >= 2:
-                    times.append(a.elapsed_time(b))
-            m3 = statistics.mean(times)
-            f3 = flops(**ww)["f_alg"] + flops_bwd(**ww)
-            extra["cfg3_fwd_bwd_B8_T128_C32_D64"] = {"ms": m3, "tflops_f_alg": f3 / m3 / 1e9,
-                                                     "frac_of_peak_f_alg": f3 / m3 / 1e9 / peak}
+            # training path: forward + backward through autograd, dO ~ N(0,1)
+            for name, ww in (("cfg3_fwd_bwd_B8_T128_C32_D64", WORKLOADS["cfg3"][0]),
+                             ("16k_tokens_fwd_bwd_D128_H16_Hkv8_B1", WORKLOADS["16k"][0])):
+                _, tt = make_inputs(torch, dev, ww, seed=2)
+                g2 = torch.randn(tt["q"].shape, device=dev, dtype=torch.bfloat16)
+                m3 = statistics.mean(time_kernel(torch, attentions, tt, ww, 10, 3, flush, g2))
+                f3 = flops(**ww)["f_alg"] + flops_bwd(**ww)
+                extra[name] = {"ms": m3, "tflops_f_alg": f3 / m3 / 1e9, "frac_of_peak_f_alg": f3 / m3 / 1e9 / peak}
+                del tt, g2
             out["extra"] = extra
         if not args.no_cpu and world == 1:  # the CPU leg belongs to the single-GPU run (torchrun pins OMP threads to 1)
             sample = dict(w, B=1)

@@ -38,7 +38,8 @@ struct BwdArgs {
   float *du, *dvt, *dz, *drt, *drc;
   // workspace carve-up (fp32 elements)
   float *tbg, *cbg;    // (B*H, N, T), (B*H, N, C) relative scores, base-2 scaled
-  float *dtbg, *dcbg;  // gradients w.r.t. the unscaled relative scores
+  float *dtbg, *dcbg;  // gradients w.r.t. the unscaled relative scores; (B*H, N, slots) from the CUDA-core
+                       // kernels, (B*H, slots, N) from the tensor-core ones
   float* delta;        // (B*H, N)
   float* partial;      // (B*H*nQT, 3, D) per-tile column sums for du/dvt/dz
   float* drel_part;    // (split, Hkv, T + C, D) split-K partials of dr_time / dr_chan

@@ -590,10 +590,18 @@ __global__ void __launch_bounds__(kThreads) simt_drel_kernel(BwdArgs bw, int whi
       {
         __syncthreads();
         load_tile<Tin, D>(Qs, q, p.q_sn, m0, p.N, kBN, bias, 1.f);
-        for (int idx = tid; idx < kBN * 32; idx += kThreads) {
-          const int r = idx / 32, s = idx % 32;
-          const int i = m0 + r;
-          Xs[r * 33 + s] = (i < p.N && s0 + s < S) ? dx[((int64_t)bh * p.N + i) * S + s0 + s] : 0.f;
+        if (bw.tc_extra != nullptr) {  // the tensor-core kernels leave (bh, slot, row): rows innermost
+          for (int idx = tid; idx < kBN * 32; idx += kThreads) {
+            const int r = idx % kBN, s = idx / kBN;
+            const int i = m0 + r;
+            Xs[r * 33 + s] = (i < p.N && s0 + s < S) ? dx[((int64_t)bh * S + s0 + s) * p.N + i] : 0.f;
+          }
+        } else {
+          for (int idx = tid; idx < kBN * 32; idx += kThreads) {
+            const int r = idx / 32, s = idx % 32;
+            const int i = m0 + r;
+            Xs[r * 33 + s] = (i < p.N && s0 + s < S) ? dx[((int64_t)bh * p.N + i) * S + s0 + s] : 0.f;
+          }
         }
         __syncthreads();
         // rows >= N hold bias only in Qs but zero in Xs, so they add nothing

@@ -41,8 +41,17 @@ constexpr uint32_t kColDP = 128;
 constexpr uint32_t kColDQ = 256;
 constexpr uint32_t kColTB = 384;
 
+// Optional in-kernel timeline of the query-side kernel (build with -DMVPA_TC_TRACE): 64 clock64
+// stamps per CTA behind the regular workspace.
+#ifdef MVPA_TC_TRACE
+#define BTRACE(slot) do { if (trace_on) p.trace[(size_t)blockIdx.x * 64 + (slot)] = clock64(); } while (0)
+#else
+#define BTRACE(slot) do { } while (0)
+#endif
+
 struct BqMaps {
   CUtensorMap q, k, v, dout, rt, rc;
+  CUtensorMap qp, dq;  // stores: Q' rows for the key-side kernel, the dq output
 };
 
 struct BqArgs {
@@ -50,19 +59,20 @@ struct BqArgs {
   const float* relc;   // (Hkv, 256): vt.r_time[j] at [0,128), z.r_chan[j] at [128,256)
   const float* lse;    // (B*H, N) base-2 log-sum-exp of the forward
   const float* delta;  // (B*H, N) sum_d dO*O
-  __nv_bfloat16* dq;   // (B,H,N,D) output, element strides below
-  int64_t dq_sb, dq_sh, dq_sn;
   float* cs_dq;        // (grid, D) per-CTA column sums of dq (fp32), for du
-  float* dtb;          // (B*H, N, T) zero-initialised; column T-1-(t_i-t_k)
-  float* dcb;          // (B*H, N, C) column C-1-|c_i-c_k|
+  // Everything a thread (= query row) reads or writes per row is stored row-innermost, so that the 32
+  // rows of a warp touch consecutive addresses.
+  float* dtb;          // (B*H, T, N) zero-initialised; slot T-1-(t_i-t_k)
+  float* dcb;          // (B*H, C, N) slot C-1-|c_i-c_k|
   // per query row, kept for the key-side kernel (which visits every query tile many times):
-  __nv_bfloat16* qp;   // (B*H, N, D)  Q' = (q+u) c2
-  __half* cblw;        // (B*H, N, CP) channel scores gathered by key channel slot, relative to their max
+  //   Q' = (q+u) c2 as (B*H, N, D) bf16, written through the `qp` tensor map
+  __half* cblw;        // (B*H, CP/8, N, 8) channel scores gathered by key channel slot, relative to their max
   float* offw;         // (B*H, N)     that max minus L
-  float* tbw;          // (B*H, N, T)  temporal scores, log2 units
+  float* tbw;          // (B*H, T, N)  temporal scores, log2 units
   int B, H, Hkv, T, C, g, window, n_qt;
   float c2, sm_scale;
   int* status;
+  long long* trace;
 };
 
 enum BarrierIndex {
@@ -265,6 +275,11 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
         }
         mma_commit(&bars[kBarProMma]);
         ok = mbar_wait(&bars[kBarProDone], 0, p.status, 121);
+        if (ok) {  // Q' (written to sQ and fenced by the softmax warps) goes out for the key-side kernel
+#pragma unroll
+          for (int hh = 0; hh < NH; ++hh) tma_store_5d(&maps.qp, sQ + hh * HALF, hh * 64, 0, I * TPB, h, b);
+          tma_store_commit();
+        }
       }
       int prev_k_sl = -1;  // K slot of the previous tile if it was dense (its dQ product is still owed)
       for (int s = 0; ok && s <= n_tiles; ++s) {
@@ -315,8 +330,13 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
       mma_commit(&bars[kBarAllDone]);
       // finish: dQ += dTB r_time + dCB r_chan  (autograd through `_rel_bias`, `attentions/attn.py:1305-1314`);
       // the softmax warps have put dTB / dCB of the tile's rows into TMEM as bf16
+#ifdef MVPA_TC_TRACE
+      const bool trace_on = true;
+#endif
       if (ok) ok = mbar_wait(&bars[kBarFinFull], 0, p.status, 125);
+      BTRACE(28);
       if (ok) ok = mbar_wait(&bars[kBarFinLoaded], 0, p.status, 126);
+      BTRACE(29);
       if (ok) {
         tc_fence_after();
         const DescHalves dfr = make_desc_halves_sw128(smem_u32(ring + 65536), HALF, 1024);
@@ -327,6 +347,8 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
         for (int kk = 0; kk < CP / 16; ++kk) mma_ts_h(tmem + kColDQ, tmem + kColDP + kk * 8, dfc, kk * 2048, idesc_q, 1u);
       }
       mma_commit(&bars[kBarFinDone]);
+      BTRACE(30);
+      tma_store_wait_all();  // the store reads sQ: it has to finish before the CTA can go away
     }
   }
   } else {
@@ -334,10 +356,16 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
     // ------------------------------ softmax warps ------------------------------
     const int row = tid & 127;
     const int wg = tid >> 7;
+#ifdef MVPA_TC_TRACE
+    const bool trace_on = tid == 0;
+#endif
+    BTRACE(0);
     const int ti_loc = row / CP, c_i = row % CP;
     const int ti_abs = I * TPB + ti_loc;
     const bool row_valid = c_i < C && ti_abs < T;
-    const int64_t n_row = (int64_t)bh * T * C + (int64_t)ti_abs * C + c_i;  // global row of this thread
+    const int N = T * C;
+    const int n_loc = ti_abs * C + c_i;                   // row within the (b,h) slice
+    const int64_t n_row = (int64_t)bh * N + n_loc;        // global row of this thread
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const int tt_base = (64 * wg) / CP;
     const int ck_base = CP == 128 ? 64 * wg : 0;
@@ -348,73 +376,98 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
     const float delta_i = row_valid ? p.delta[n_row] : 0.f;
     softmax_bar();
     bool ok = warp_wait(&bars[kBarProMma], 0, p.status, 131);
+    BTRACE(1);
     if (ok) {
       tc_fence_after();
+      // The prologue and the epilogue run once per CTA, so their instructions come from memory rather
+      // than the instruction cache: they are written as short loops, not unrolled.
       // temporal scores of the row, for the key-side kernel (each warpgroup dumps half of the columns)
-#pragma unroll
-      for (int c0 = 0; c0 < 64; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld32(lane_base + kColTB + 64 * wg + c0, v);
-        tmem_ld_wait();
-        if (row_valid) {
-#pragma unroll
-          for (int jj = 0; jj < 32; ++jj) {
-            const int j = 64 * wg + c0 + jj;
-            if (j < T) p.tbw[n_row * T + j] = p.c2 * (__uint_as_float(v[jj]) + s_vr[j]);
-          }
-        }
-      }
-#pragma unroll
-      for (int ci = 0; ci < CP / 32; ++ci) {
-        if ((ci & 1) == wg) {
-          uint32_t v[32];
-          tmem_ld32(lane_base + kColS + ci * 32, v);
+      {
+        float* dst = p.tbw + ((int64_t)bh * T + 64 * wg) * N + (row_valid ? n_loc : 0);
+#pragma unroll 1
+        for (int c8 = 0; c8 < 64; c8 += 8) {
+          uint32_t v[8];
+          tmem_ld8(lane_base + kColTB + 64 * wg + c8, v);
           tmem_ld_wait();
+          if (row_valid) {
 #pragma unroll
-          for (int j4 = 0; j4 < 8; ++j4) {
-            const float4 zc = reinterpret_cast<const float4*>(s_zc)[ci * 8 + j4];
-            const float zz[4] = {zc.x, zc.y, zc.z, zc.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int jj = j4 * 4 + e;
-              scratch[row * CP + ((ci * 32 + jj + 2 * row) & (CP - 1))] = p.c2 * (__uint_as_float(v[jj]) + zz[e]);
+            for (int e = 0; e < 8; ++e) {
+              const int j = 64 * wg + c8 + e;
+              if (j < T) dst[(int64_t)(c8 + e) * N] = p.c2 * (__uint_as_float(v[e]) + s_vr[j]);
             }
           }
         }
       }
+      BTRACE(32);
+      // channel scores by |c_i - c_k| slot to shared memory (8-column chunks alternate between the warpgroups)
+#pragma unroll 1
+      for (int c8 = 8 * wg; c8 < CP; c8 += 16) {
+        uint32_t v[8];
+        tmem_ld8(lane_base + kColS + c8, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          scratch[row * CP + ((c8 + e + 2 * row) & (CP - 1))] = p.c2 * (__uint_as_float(v[e]) + s_zc[c8 + e]);
+      }
       tc_fence_before();
     }
+    BTRACE(33);
     softmax_bar();
+    BTRACE(34);
     __half2 cbl[NCH / 2];
     float mc = 0.f;
     {
-      float g[NCH];
-      float mx = -INFINITY;
-#pragma unroll
-      for (int k = 0; k < NCH; ++k) {
+      // gather by key channel slot: g_k = CB[i, C-1-|c_i - c_k|]; first the row maximum, then fp16 values
+      // relative to it, staged in this thread's own row of s_cbl (16-byte chunks swizzled by the row)
+      auto gathered = [&](int k) {
         const int ck = ck_base + k;
         const int jc = min(max(C - 1 - abs(c_i - ck), 0), CP - 1);
         const float val = ok ? scratch[row * CP + ((jc + 2 * row) & (CP - 1))] : 0.f;
-        g[k] = (c_i < C && ck < C) ? val : -INFINITY;
-        mx = fmaxf(mx, g[k]);
-      }
+        return (c_i < C && ck < C) ? val : -INFINITY;
+      };
+      float mx = -INFINITY;
+#pragma unroll 4
+      for (int k = 0; k < NCH; ++k) mx = fmaxf(mx, gathered(k));
       s_max[wg * 128 + row] = mx;
+      BTRACE(35);
       softmax_bar();
+      BTRACE(36);
       mx = fmaxf(mx, s_max[(wg ^ 1) * 128 + row]);
       mc = (mx == -INFINITY) ? 0.f : mx;
+      // fp16 pairs relative to the maximum, staged in this thread's lane of idle TMEM columns so that the
+      // loop stays short and the values still end up in registers
+#pragma unroll 1
+      for (int k16 = 0; k16 < NCH; k16 += 16) {
+        uint32_t pk[8];
 #pragma unroll
-      for (int k2 = 0; k2 < NCH / 2; ++k2) cbl[k2] = __floats2half2_rn(g[2 * k2] - mc, g[2 * k2 + 1] - mc);
-      if (ok && row_valid && (CP == 128 || wg == 0)) {
-        uint4* dst = reinterpret_cast<uint4*>(p.cblw + n_row * CP + ck_base);
+        for (int e = 0; e < 8; ++e) {
+          const __half2 hh2 = __floats2half2_rn(gathered(k16 + 2 * e) - mc, gathered(k16 + 2 * e + 1) - mc);
+          pk[e] = *reinterpret_cast<const uint32_t*>(&hh2);
+        }
+        tmem_st8(lane_base + kColDP + 32 * wg + k16 / 2, pk);
+      }
+      tmem_st_wait();
+      {
+        uint32_t w[32];
+        tmem_ld32(lane_base + kColDP + 32 * wg, w);
+        tmem_ld_wait();
+#pragma unroll
+        for (int k2 = 0; k2 < NCH / 2; ++k2) *reinterpret_cast<uint32_t*>(&cbl[k2]) = w[k2];
+      }
+      tc_fence_before();
+      uint4* dst = reinterpret_cast<uint4*>(p.cblw) + ((int64_t)bh * (CP / 8) + ck_base / 8) * N + n_loc;
+      const bool store_cbl = ok && row_valid && (CP == 128 || wg == 0);
+      if (store_cbl) {
 #pragma unroll
         for (int m = 0; m < NCH / 8; ++m)
-          dst[m] = make_uint4(*reinterpret_cast<uint32_t*>(&cbl[4 * m]), *reinterpret_cast<uint32_t*>(&cbl[4 * m + 1]),
-                              *reinterpret_cast<uint32_t*>(&cbl[4 * m + 2]), *reinterpret_cast<uint32_t*>(&cbl[4 * m + 3]));
-        if (wg == 0) p.offw[n_row] = mc - L_i;
+          dst[(int64_t)m * N] = make_uint4(*reinterpret_cast<uint32_t*>(&cbl[4 * m]), *reinterpret_cast<uint32_t*>(&cbl[4 * m + 1]),
+                                           *reinterpret_cast<uint32_t*>(&cbl[4 * m + 2]), *reinterpret_cast<uint32_t*>(&cbl[4 * m + 3]));
       }
+      if (store_cbl && wg == 0) p.offw[n_row] = mc - L_i;
+      BTRACE(37);
       if (ok) {
         const float4* u4 = reinterpret_cast<const float4*>(s_bias);
-#pragma unroll
+#pragma unroll 1
         for (int cc = 0; cc < D / 16; ++cc) {
           const int chunk = wg * (D / 16) + cc, hh = chunk / 8, c = chunk % 8;
           const uint32_t off = hh * HALF + row * 128 + ((c ^ (row & 7)) << 4);
@@ -426,12 +479,12 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
           out.z = pack_bf16((__uint_as_float(raw.z << 16) + b1.x) * p.c2, (__uint_as_float(raw.z & 0xffff0000u) + b1.y) * p.c2);
           out.w = pack_bf16((__uint_as_float(raw.w << 16) + b1.z) * p.c2, (__uint_as_float(raw.w & 0xffff0000u) + b1.w) * p.c2);
           *reinterpret_cast<uint4*>(sQ + off) = out;
-          if (row_valid) *reinterpret_cast<uint4*>(p.qp + n_row * D + hh * 64 + c * 8) = out;
         }
         fence_proxy_async_smem();
       }
     }
     mbar_arrive(&bars[kBarProDone]);
+    BTRACE(2);
 
     // gradient of the channel scores, per channel slot of this thread's columns (summed over time)
     float dcb_acc[NCH];
@@ -444,6 +497,7 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
       const int J = tile_of(s);
       ok = warp_wait(&bars[kBarSdpFull], s & 1, p.status, 132);
       if (!ok) break;
+      if (s < 16) BTRACE(12 + s);
       tc_fence_after();
       // temporal scores of this thread's key time steps
       float offs[TPW], wmul[TPW], dtb_acc[TPW];
@@ -494,132 +548,132 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
       // row sums per key time step; both warpgroups may own part of a time step (CP = 128)
 #pragma unroll
       for (int tl = 0; tl < TPW; ++tl)
-        if (valid[tl]) atomicAdd(&p.dtb[n_row * T + slot[tl]], dtb_acc[tl]);
+        if (valid[tl]) atomicAdd(&p.dtb[((int64_t)bh * T + slot[tl]) * N + n_loc], dtb_acc[tl]);
     }
     // ------------------------------- epilogue ---------------------------------
+    BTRACE(3);
     if (ok) ok = warp_wait(&bars[kBarAllDone], 0, p.status, 134);
+    BTRACE(4);
     // du = sum over rows of dq's content part (`attentions/attn.py:1305-1306`: q + q_bias feeds the content
     // term only): column sums of the accumulator before the relative terms are added to it
     float* cs = reinterpret_cast<float*>(ring);  // [2 wg][128 rows][DW], columns rotated by the row
     if (ok) {
       tc_fence_after();
-#pragma unroll
-      for (int c0 = 0; c0 < DW; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld32(lane_base + kColDQ + wg * DW + c0, v);
+#pragma unroll 1
+      for (int c8 = 0; c8 < DW; c8 += 8) {
+        uint32_t v[8];
+        tmem_ld8(lane_base + kColDQ + wg * DW + c8, v);
         tmem_ld_wait();
 #pragma unroll
-        for (int jj = 0; jj < 32; ++jj)
-          cs[(wg * 128 + row) * DW + ((c0 + jj + row) & (DW - 1))] = row_valid ? __uint_as_float(v[jj]) : 0.f;
+        for (int e = 0; e < 8; ++e)
+          cs[(wg * 128 + row) * DW + ((c8 + e + row) & (DW - 1))] = row_valid ? __uint_as_float(v[e]) : 0.f;
       }
     }
+    BTRACE(5);
     softmax_bar();
     if (row < DW) {  // fixed summation order: deterministic
       float sum = 0.f;
+#pragma unroll 4
       for (int r = 0; r < 128; ++r) sum += cs[(wg * 128 + r) * DW + ((row + r) & (DW - 1))];
       p.cs_dq[(size_t)blockIdx.x * D + wg * DW + row] = sum;
     }
     softmax_bar();
+    BTRACE(6);
     // channel-score gradient: from key-channel slots to |c_i - c_k| slots, through shared memory
     float* sc = reinterpret_cast<float*>(ring);  // [128][CP]; every TMA load has been consumed by now
     if (CP == 128 || wg == 0) {
 #pragma unroll
       for (int k = 0; k < NCH; ++k) sc[row * CP + ((ck_base + k + 2 * row) & (CP - 1))] = dcb_acc[k];
     }
+    BTRACE(40);
     softmax_bar();
     if (CP < 128 && wg == 1) {  // both warpgroups hold sums for the same channel slots (different time steps)
 #pragma unroll
       for (int k = 0; k < NCH; ++k) sc[row * CP + ((k + 2 * row) & (CP - 1))] += dcb_acc[k];
     }
     softmax_bar();
-    {
-      // e = |c_i - c_k| slots of this thread's half, kept in registers across the barrier below
-      float ev[CP / 2];
+    BTRACE(42);
+    // dCB[i, j], j = C-1-e, e = |c_i - c_k|: to the workspace (for dr_chan) and, as bf16 pairs, into TMEM
+    // columns kColDP + j/2 as the A operand of dQ += dCB r_chan.  Each warpgroup takes half of the slots.
+    if (ok) {
+      const int jb = wg * (CP / 2);
+      float* dst = p.dcb + (int64_t)bh * C * N + (row_valid ? n_loc : 0);
+#pragma unroll 2
+      for (int m = 0; m < CP / 4; ++m) {
+        float vv[2];
 #pragma unroll
-      for (int m = 0; m < CP / 2; ++m) {
-        const int e = wg * (CP / 2) + m;
-        float val = 0.f;
-        if (row_valid && e < C) {
-          if (c_i - e >= 0) val += sc[row * CP + ((c_i - e + 2 * row) & (CP - 1))];
-          if (e > 0 && c_i + e < C) val += sc[row * CP + ((c_i + e + 2 * row) & (CP - 1))];
-          p.dcb[n_row * C + (C - 1 - e)] = val;
+        for (int t2 = 0; t2 < 2; ++t2) {
+          const int j = jb + 2 * m + t2, e = C - 1 - j;
+          float val = 0.f;
+          if (row_valid && e >= 0) {
+            if (c_i - e >= 0) val += sc[row * CP + ((c_i - e + 2 * row) & (CP - 1))];
+            if (e > 0 && c_i + e < C) val += sc[row * CP + ((c_i + e + 2 * row) & (CP - 1))];
+            dst[(int64_t)j * N] = val;
+          }
+          vv[t2] = val;
         }
-        ev[m] = val;
-      }
-      softmax_bar();  // everyone has read the key-slot sums: the rows are rewritten in r_chan-row order
-#pragma unroll
-      for (int m = 0; m < CP / 2; ++m) {
-        const int e = wg * (CP / 2) + m, j = C - 1 - e;
-        if (j >= 0) sc[row * CP + ((j + 2 * row) & (CP - 1))] = ev[m];
-      }
-      if (wg == 0) {  // columns C .. CP-1 do not exist: zero for the product
-        for (int j = C; j < CP; ++j) sc[row * CP + ((j + 2 * row) & (CP - 1))] = 0.f;
+        tmem_st1(lane_base + kColDP + jb / 2 + m, pack_bf16(vv[0], vv[1]));
       }
     }
+    BTRACE(43);
+    BTRACE(7);
     __threadfence();  // this CTA's atomic row sums in dtb are complete before anyone re-reads them
     softmax_bar();
+    BTRACE(8);
     if (ok) {
-      // dTB (this thread's 64 of the 128 r_time rows) and dCB (its half of the CP r_chan rows) as bf16 A operands
-      uint32_t pk[32];
+      // dTB of the row (this thread's 64 of the 128 r_time rows) as bf16 pairs: A operand of dQ += dTB r_time
+      const float* src = p.dtb + ((int64_t)bh * T + 64 * wg) * N + (row_valid ? n_loc : 0);
+      const float keep = row_valid ? 1.f : 0.f;
+#pragma unroll 1
+      for (int m8 = 0; m8 < 32; m8 += 8) {
+        float a[16];
 #pragma unroll
-      for (int m = 0; m < 32; ++m) {
-        const int j = 64 * wg + 2 * m;
-        const float a0 = (row_valid && j < T) ? __ldcg(&p.dtb[n_row * T + j]) : 0.f;
-        const float a1 = (row_valid && j + 1 < T) ? __ldcg(&p.dtb[n_row * T + j + 1]) : 0.f;
-        pk[m] = pack_bf16(a0, a1);
-      }
-      {
-        uint32_t lo[16], hi[16];
+        for (int e = 0; e < 16; ++e) {
+          const int jl = 2 * m8 + e;
+          a[e] = (64 * wg + jl < T) ? __ldcg(src + (int64_t)jl * N) : 0.f;
+        }
+        uint32_t pk[8];
 #pragma unroll
-        for (int m = 0; m < 16; ++m) { lo[m] = pk[m]; hi[m] = pk[16 + m]; }
-        tmem_st16(lane_base + kColS + 32 * wg, lo);
-        tmem_st16(lane_base + kColS + 32 * wg + 16, hi);
+        for (int e = 0; e < 8; ++e) pk[e] = pack_bf16(a[2 * e] * keep, a[2 * e + 1] * keep);
+        tmem_st8(lane_base + kColS + 32 * wg + m8, pk);
       }
-      // CP = 32: 16 packed columns in all, written by the first warpgroup alone
-      constexpr int NPC = CP == 32 ? 16 : CP / 4;
-      const int jb = CP == 32 ? 0 : wg * (CP / 2);
-      uint32_t pc[NPC];
-#pragma unroll
-      for (int m = 0; m < NPC; ++m) {
-        const int j = jb + 2 * m;
-        pc[m] = pack_bf16(sc[row * CP + ((j + 2 * row) & (CP - 1))], sc[row * CP + ((j + 1 + 2 * row) & (CP - 1))]);
-      }
-      if constexpr (CP == 128) {
-        uint32_t lo[16], hi[16];
-#pragma unroll
-        for (int m = 0; m < 16; ++m) { lo[m] = pc[m]; hi[m] = pc[16 + m]; }
-        tmem_st16(lane_base + kColDP + 32 * wg, lo);
-        tmem_st16(lane_base + kColDP + 32 * wg + 16, hi);
-      } else if constexpr (CP == 64) {
-        tmem_st16(lane_base + kColDP + 16 * wg, pc);
-      } else {
-        if (wg == 0) tmem_st16(lane_base + kColDP, pc);
-      }
+      BTRACE(45);
       tmem_st_wait();
     }
     tc_fence_before();
     mbar_arrive(&bars[kBarFinFull]);
+    BTRACE(9);
     if (ok) ok = warp_wait(&bars[kBarFinDone], 0, p.status, 135);
+    BTRACE(10);
+    uint8_t* s_out = ring;  // dq tile as bf16, laid out like a Q tile (128-byte swizzled rows)
     if (ok) {
       tc_fence_after();
-      __nv_bfloat16* out = p.dq + b * p.dq_sb + h * p.dq_sh + ((int64_t)ti_abs * C + c_i) * p.dq_sn + wg * DW;
-#pragma unroll
+#pragma unroll 1
       for (int c0 = 0; c0 < DW; c0 += 32) {
         uint32_t v[32];
         tmem_ld32(lane_base + kColDQ + wg * DW + c0, v);
         tmem_ld_wait();
-        if (row_valid) {
 #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            uint32_t w[4];
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint32_t w[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
-              w[e] = pack_bf16(__uint_as_float(v[q4 * 8 + 2 * e]), __uint_as_float(v[q4 * 8 + 2 * e + 1]));
-            *reinterpret_cast<uint4*>(out + c0 + q4 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
-          }
+          for (int e = 0; e < 4; ++e)
+            w[e] = pack_bf16(__uint_as_float(v[q4 * 8 + 2 * e]), __uint_as_float(v[q4 * 8 + 2 * e + 1]));
+          const int col = wg * DW + c0 + q4 * 8, hh = col / 64, c = (col % 64) / 8;
+          *reinterpret_cast<uint4*>(s_out + hh * HALF + row * 128 + ((c ^ (row & 7)) << 4)) =
+              make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
+      fence_proxy_async_smem();
     }
+    softmax_bar();
+    if (ok && tid == 0) {
+#pragma unroll
+      for (int hh = 0; hh < NH; ++hh) tma_store_5d(&maps.dq, s_out + hh * HALF, hh * 64, 0, I * TPB, h, b);
+      tma_store_commit();
+      tma_store_wait_all();
+    }
+    BTRACE(11);
     tc_fence_before();
   }
   __syncthreads();
@@ -811,15 +865,16 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
       const bool light = pair_is_light(i);
       const int ti_abs = i * TPB + ti_loc;
       const bool row_valid = c_i < C && ti_abs < T;
-      const int64_t n_row = ((int64_t)b * p.H + h) * T * C + (int64_t)ti_abs * C + c_i;
+      const int N = T * C, n_loc = ti_abs * C + c_i;
+      const int64_t bhq = (int64_t)b * p.H + h, n_row = bhq * N + n_loc;
       // per-row quantities of this query tile, from the query-side kernel's workspace
       __half2 cbl[NCH / 2];
       float off_row = -INFINITY, delta_i = 0.f;
       if (row_valid) {
-        const uint4* src = reinterpret_cast<const uint4*>(p.cblw + n_row * CP + ck_base);
+        const uint4* src = reinterpret_cast<const uint4*>(p.cblw) + (bhq * (CP / 8) + ck_base / 8) * N + n_loc;
 #pragma unroll
         for (int m = 0; m < NCH / 8; ++m) {
-          const uint4 w = src[m];
+          const uint4 w = src[(int64_t)m * N];
           *reinterpret_cast<uint32_t*>(&cbl[4 * m]) = w.x;
           *reinterpret_cast<uint32_t*>(&cbl[4 * m + 1]) = w.y;
           *reinterpret_cast<uint32_t*>(&cbl[4 * m + 2]) = w.z;
@@ -837,7 +892,7 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
         const int tk_abs = J * TPB + tt_base + tl, dt = ti_abs - tk_abs;
         const bool valid = dt >= 0 && tk_abs < T && row_valid;
         wmul[tl] = (p.window > 0 && dt > p.window && ti_abs != T - 1) ? 0.f : 1.f;
-        offs[tl] = valid ? p.tbw[n_row * T + (T - 1 - dt)] + off_row : -INFINITY;
+        offs[tl] = valid ? p.tbw[(bhq * T + (T - 1 - dt)) * N + n_loc] + off_row : -INFINITY;
       }
       ok = warp_wait(&bars[kBkSdpFull], s & 1, p.status, 232);
       if (!ok) break;
@@ -918,7 +973,7 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
 }
 
 template <int D, int CP>
-int launch_kv(const BwdArgs& bw, const BqArgs& q, cudaStream_t s) {
+int launch_kv(const BwdArgs& bw, const BqArgs& q, const void* qp, cudaStream_t s) {
   const Args& a = bw.a;
   constexpr int TPB = 128 / CP;
   const uint64_t es = 2;
@@ -930,7 +985,7 @@ int launch_kv(const BwdArgs& bw, const BqArgs& q, cudaStream_t s) {
     const uint64_t str[4] = {(uint64_t)sn * es, (uint64_t)sn * a.C * es, (uint64_t)sh * es, (uint64_t)sb * es};
     return encode_bf16_sw128(map, ptr, 5, dims, str, box);
   };
-  if ((rc = enc5(&m.qp, q.qp, a.H, a.D, (int64_t)a.N * a.D, (int64_t)a.H * a.N * a.D))) return rc;
+  if ((rc = enc5(&m.qp, qp, a.H, a.D, (int64_t)a.N * a.D, (int64_t)a.H * a.N * a.D))) return rc;
   if ((rc = enc5(&m.dout, bw.d_o, a.H, bw.do_sn, bw.do_sh, bw.do_sb))) return rc;
   if ((rc = enc5(&m.k, a.k, a.Hkv, a.k_sn, a.k_sh, a.k_sb))) return rc;
   if ((rc = enc5(&m.v, a.v, a.Hkv, a.v_sn, a.v_sh, a.v_sb))) return rc;
@@ -951,7 +1006,7 @@ int launch_kv(const BwdArgs& bw, const BqArgs& q, cudaStream_t s) {
   return MVPA_OK;
 }
 
-int make_maps(BqMaps& m, const BwdArgs& bw, int CP) {
+int make_maps(BqMaps& m, const BwdArgs& bw, int CP, const void* qp) {
   const Args& a = bw.a;
   const int TPB = 128 / CP;
   const uint64_t es = 2;
@@ -966,6 +1021,8 @@ int make_maps(BqMaps& m, const BwdArgs& bw, int CP) {
   if ((rc = enc5(&m.dout, bw.d_o, a.H, bw.do_sn, bw.do_sh, bw.do_sb))) return rc;
   if ((rc = enc5(&m.k, a.k, a.Hkv, a.k_sn, a.k_sh, a.k_sb))) return rc;
   if ((rc = enc5(&m.v, a.v, a.Hkv, a.v_sn, a.v_sh, a.v_sb))) return rc;
+  if ((rc = enc5(&m.qp, qp, a.H, a.D, (int64_t)a.N * a.D, (int64_t)a.H * a.N * a.D))) return rc;
+  if ((rc = enc5(&m.dq, bw.dq, a.H, bw.dq_sn, bw.dq_sh, bw.dq_sb))) return rc;
   {
     const uint64_t dims[3] = {(uint64_t)a.D, (uint64_t)a.T, (uint64_t)a.Hkv};
     const uint64_t str[2] = {(uint64_t)a.D * es, (uint64_t)a.T * a.D * es};
@@ -1015,16 +1072,14 @@ template <int D, int CP>
 int launch(const BwdArgs& bw, float* cs_dq, int* status, float* relc, float* rows_ws, cudaStream_t s) {
   const Args& a = bw.a;
   BqMaps maps;
-  int rc = make_maps(maps, bw, CP);
+  int rc = make_maps(maps, bw, CP, rows_ws);
   if (rc) return rc;
   BqArgs t;
   t.u = (const __nv_bfloat16*)a.u;
   t.relc = relc; t.lse = a.lse; t.delta = bw.delta;
-  t.dq = (__nv_bfloat16*)bw.dq; t.dq_sb = bw.dq_sb; t.dq_sh = bw.dq_sh; t.dq_sn = bw.dq_sn;
   t.cs_dq = cs_dq; t.dtb = bw.dtbg; t.dcb = bw.dcbg;
   {
     const size_t rows = (size_t)a.B * a.H * a.N;
-    t.qp = reinterpret_cast<__nv_bfloat16*>(rows_ws);
     t.cblw = reinterpret_cast<__half*>(rows_ws + rows * (D / 2));
     t.offw = rows_ws + rows * (D / 2) + rows * 64;
     t.tbw = t.offw + ((rows + 3) & ~(size_t)3);
@@ -1034,6 +1089,15 @@ int launch(const BwdArgs& bw, float* cs_dq, int* status, float* relc, float* row
   t.n_qt = (a.T + TPB - 1) / TPB;
   t.c2 = a.c2; t.sm_scale = a.sm_scale;
   t.status = status;
+  t.trace = nullptr;
+#ifdef MVPA_TC_TRACE
+  {
+    mvpa_problem pr{};
+    pr.B = a.B; pr.H = a.H; pr.Hkv = a.Hkv; pr.T = a.T; pr.C = a.C; pr.D = a.D;
+    t.trace = reinterpret_cast<long long*>(cs_dq + tc_bwd_q_workspace_floats(&pr) - (size_t)a.B * a.H * a.T * 128);
+    MVPA_CUDA_CHECK(cudaMemsetAsync(t.trace, 0, sizeof(long long) * 64 * (size_t)a.B * a.H * t.n_qt, s));
+  }
+#endif
   constexpr int smem = Cfg<D>::SMEM_BYTES;
   static_assert(smem <= 232448, "shared memory budget");
   static_assert(Cfg<D>::EARLY >= 2, "the first tile's K and V load while the prologue runs");
@@ -1046,7 +1110,7 @@ int launch(const BwdArgs& bw, float* cs_dq, int* status, float* relc, float* row
   tc_bwd_q_kernel<D, CP><<<grid, kThreads, smem, s>>>(maps, t);
   count_launch(2);
   MVPA_CUDA_CHECK(cudaGetLastError());
-  return launch_kv<D, CP>(bw, t, s);
+  return launch_kv<D, CP>(bw, t, rows_ws, s);
 }
 
 }  // namespace
@@ -1063,8 +1127,12 @@ size_t tc_bwd_q_workspace_floats(const mvpa_problem* p) {
   const size_t rows = (size_t)p->B * p->H * p->T * p->C;
   // column sums + status + constants + per-row data for the key side (Q' bf16, channel scores fp16
   // padded to 128 slots, offset, temporal scores)
-  return cs_dq_floats(p->B, p->H, p->T, p->D) + 64 + (size_t)p->Hkv * 256 + rows * (p->D / 2) + rows * 64 +
-         ((rows + 3) & ~(size_t)3) + rows * p->T + 64;
+  size_t n = cs_dq_floats(p->B, p->H, p->T, p->D) + 64 + (size_t)p->Hkv * 256 + rows * (p->D / 2) + rows * 64 +
+             ((rows + 3) & ~(size_t)3) + rows * p->T + 64;
+#ifdef MVPA_TC_TRACE
+  n = ((n + 63) & ~(size_t)63) + (size_t)p->B * p->H * p->T * 128;  // the timeline sits at the very end
+#endif
+  return n;
 }
 
 int tc_bwd_bias(const BwdArgs& bw, float* extra, int n_split, cudaStream_t s) {
