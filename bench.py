@@ -292,25 +292,57 @@ def main():
     h2d = sum(host[n].numel() * 2 for n in host) + (gout_host.numel() * 2 if train else 0)
     d2h = o_host.numel() * 2
 
-    def e2e_step():
-        d = {n: host[n].to(dev, non_blocking=True) for n in host}
-        if train:
-            d = {n: x.requires_grad_(True) for n, x in d.items()}
-        o = attentions.flashmvpa(d["q"], d["u"], d["v"], d["z"], d["k"], d["rt"], d["rc"], d["val"],
-                                 causal=True, sm_scale=w["D"] ** -0.5, window_size=w["window"])
-        if train:  # the step's result read back is dq
-            o.backward(gout_host.to(dev, non_blocking=True))
-            o_host.copy_(d["q"].grad, non_blocking=True)
-        else:
-            o_host.copy_(o, non_blocking=True)
+    # Three streams and two sets of device buffers: the host->device copy of step i+1, the kernels of
+    # step i and the device->host copy of step i-1 overlap, as in a serving loop fed from pinned memory.
+    # Every step's copies and kernels are inside the timed region.
+    s_in, s_run, s_out = (torch.cuda.Stream(device=dev) for _ in range(3))
+    NBUF = 2
+    dbuf = [{n: torch.empty_like(t[n]) for n in host} for _ in range(NBUF)]
+    gbuf = [torch.empty_like(gout) for _ in range(NBUF)] if train else None
+    obuf = [torch.empty_like(t["q"]) for _ in range(NBUF)]
+    ev_in = [torch.cuda.Event() for _ in range(NBUF)]      # inputs of the buffer have landed
+    ev_run = [torch.cuda.Event() for _ in range(NBUF)]     # kernels reading / writing the buffer are done
+    ev_out = [torch.cuda.Event() for _ in range(NBUF)]     # the result has left the buffer
 
-    for _ in range(args.warmup):
-        e2e_step()
+    def e2e_step(i):
+        j = i % NBUF
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(ev_run[j])                      # the kernels of step i - NBUF no longer read these inputs
+            for n in host:
+                dbuf[j][n].copy_(host[n], non_blocking=True)
+            if train:
+                gbuf[j].copy_(gout_host, non_blocking=True)
+            ev_in[j].record(s_in)
+        with torch.cuda.stream(s_run):
+            s_run.wait_event(ev_in[j])
+            s_run.wait_event(ev_out[j])                     # the result of step i - NBUF has been copied out
+            d = dbuf[j]
+            if train:
+                d = {n: x.detach().requires_grad_(True) for n, x in d.items()}
+            o = attentions.flashmvpa(d["q"], d["u"], d["v"], d["z"], d["k"], d["rt"], d["rc"], d["val"],
+                                     causal=True, sm_scale=w["D"] ** -0.5, window_size=w["window"])
+            if train:  # the step's result read back is dq
+                o.backward(gbuf[j])
+                obuf[j].copy_(d["q"].grad)
+            else:
+                obuf[j].copy_(o)
+            ev_run[j].record(s_run)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_run[j])
+            o_host.copy_(obuf[j], non_blocking=True)
+            ev_out[j].record(s_out)
+
+    for i in range(args.warmup):
+        e2e_step(i)
     sync_all()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(args.steps):
-        e2e_step()
+    a.record()                                               # default stream: the side streams start after it
+    for st in (s_in, s_run, s_out):
+        st.wait_stream(torch.cuda.current_stream())
+    for i in range(args.steps):
+        e2e_step(i)
+    for st in (s_in, s_run, s_out):
+        torch.cuda.current_stream().wait_stream(st)
     b.record()
     sync_all()
     clk.__exit__()

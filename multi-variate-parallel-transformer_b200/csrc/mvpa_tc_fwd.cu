@@ -51,6 +51,18 @@ constexpr float kRescaleThreshold = 8.f;  // log2 units: P stays below 2^8
 #else
 #define TRACE(slot) do { } while (0)
 #endif
+#ifdef MVPA_TRACE_DENSE
+#define LTRACE_ON false
+#else
+#define LTRACE_ON true
+#endif
+#if defined(MVPA_TC_TRACE) && defined(MVPA_TRACE_DENSE)
+#define DTRACE(s, k) do { if ((s) == 2 || (s) == 3) TRACE(112 + 8 * ((s) - 2) + (k)); } while (0)
+#define ATRACE(s, k) do { if ((s) == 2 || (s) == 4) TRACE(112 + 4 * ((s) - 2) + (k)); } while (0)
+#else
+#define DTRACE(s, k) do { } while (0)
+#define ATRACE(s, k) do { } while (0)
+#endif
 
 struct TcMaps {
   CUtensorMap q, k, v, rt, rc;
@@ -91,7 +103,7 @@ struct Cfg {
   static constexpr int SMEM_PRO = SMEM_RING + EARLY * TILE;
   static constexpr int SMEM_TAIL = SMEM_RING + NS * TILE;
   // tail: u/vt/z (3D f32), vR[128], zC[128], smax[2][2][128], lsum[2][128], barriers, tmem slot, abort
-  static constexpr int TAIL_FLOATS = 3 * D + 128 + 128 + 512 + 256;
+  static constexpr int TAIL_FLOATS = 3 * D + 128 + 128 + 512 + 256 + 512;
   static constexpr int TAIL_BYTES = TAIL_FLOATS * 4 + (kBarSlotFull + 2 * NS) * 8 + 16;
   static constexpr int SMEM_BYTES = SMEM_TAIL + TAIL_BYTES + 1024;  // + alignment slack
 };
@@ -152,6 +164,11 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
   constexpr int NCH = CP < 64 ? CP : 64;       // distinct channel slots inside those columns
   constexpr int KSTEPS = D / 16;
   constexpr int DW = D / 2;                    // O columns each warpgroup rescales / stores
+  // Alternating dense tiles (head_dim 64, at most 64 channel slots): each softmax warpgroup takes every
+  // other dense tile with whole rows and its own O accumulator, so the two warps that share a
+  // scheduler are in different phases (one in its exponentials, the other loading or reducing)
+  // and no barrier is needed inside a tile; the accumulators are merged before the light tiles.
+  constexpr bool ALT = (D == 64) && (CP <= 64);
   static_assert(CP >= 32 && CP <= 128 && (CP & (CP - 1)) == 0, "CP in {32,64,128}");
 
   extern __shared__ uint8_t smem_raw[];
@@ -166,7 +183,8 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
   float* s_zc = s_vr + 128;                     // z  . r_chan[j]
   float* s_max = s_zc + 128;                    // [2 slots][2 wg][128 rows]
   float* s_lsum = s_max + 512;                  // [2 wg][128]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_lsum + 256);
+  float* s_merge = s_lsum + 256;                // [m, l][2 wg][128]: accumulator merge of the alternating path
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_merge + 512);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kBarSlotFull + 2 * NS);
   int* s_abort = reinterpret_cast<int*>(tmem_slot + 1);
   int* s_giveup = s_abort + 1;
@@ -174,6 +192,17 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
   uint64_t* slot_free = slot_full + NS;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef MVPA_TC_TRACE
+  if (tid == 0) {  // kernel entry: SM id and the global nanosecond timer, to find the gaps between CTAs of an SM
+    uint32_t smid;
+    unsigned long long gt;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+    p.trace[(size_t)blockIdx.x * 128 + 124] = clock64();
+    p.trace[(size_t)blockIdx.x * 128 + 125] = smid;
+    p.trace[(size_t)blockIdx.x * 128 + 126] = (long long)gt;
+  }
+#endif
   const int BH = p.B * p.H;
   const int I_loc = p.q_tiles - 1 - (int)(blockIdx.x / BH);  // latest (heaviest) query tiles first
   const int I = p.q_t0 / TPB + I_loc;                         // tile index in the whole sequence
@@ -197,7 +226,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
     mbar_init(&bars[kBarXchg], kSoftmaxThreads);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars[kBarSFull + i], 1);
-      mbar_init(&bars[kBarPFull + i], kSoftmaxThreads);
+      mbar_init(&bars[kBarPFull + i], ALT ? kSoftmaxThreads / 2 : kSoftmaxThreads);
     }
     for (int i = 0; i < 4; ++i) mbar_init(&bars[kBarPlFull + i], kSoftmaxThreads);
     for (int i = 0; i < NS; ++i) {
@@ -342,10 +371,13 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
         // A blocking wait for P_{s+1} here could deadlock against a rescale that waits for PV_s;
         // a peek cannot.
         const bool dn = s + 1 < n_dense;
-        pre_p = mma_ts_x4_peek(tmem + kColO, a0, b_lo, dv0.hi, 2048 >> 4, idesc_o, (uint32_t)(s > 0),
+        // alternating path: P_s is one contiguous 64-column block, O of even / odd tiles are separate
+        const uint32_t d_o = ALT ? tmem + kColO + 64 * (s & 1) : tmem + kColO;
+        const uint32_t acc0 = ALT ? (uint32_t)(s > 1) : (uint32_t)(s > 0);
+        pre_p = mma_ts_x4_peek(d_o, a0, b_lo, dv0.hi, 2048 >> 4, idesc_o, acc0,
                                dn ? a_pfull + 8 * ((s + 1) & 1) : a_plfull, dn ? ((s + 1) >> 1) & 1 : 0);
         if (s + 1 >= n_tiles) pre_p = false;
-        mma_ts_x4(tmem + kColO, a0 + 64, b_lo + 4 * (2048 >> 4), dv0.hi, 2048 >> 4, idesc_o, 1u);
+        mma_ts_x4(d_o, a0 + (ALT ? 32 : 64), b_lo + 4 * (2048 >> 4), dv0.hi, 2048 >> 4, idesc_o, 1u);
         mma_commit_a(a_free + 8 * v_sl);
         advance_v(dn ? 2 : 1);  // a dense successor's V is two loads on, a light successor's one
         if (s < 24) TRACE(36 + s);
@@ -524,6 +556,158 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
     // Abort protocol: this loop contains a named barrier, which must never lose a participant.
     // A warp whose bounded wait runs out raises s_giveup, stops touching TMEM, and keeps walking
     // to the next named barrier; there every warp sees the flag and all leave together.
+    if constexpr (ALT) {
+      const uint32_t s_addr = lane_base + kColS + 128 * wg;  // this warpgroup's tiles use S buffer `wg`
+      const uint32_t o_addr = lane_base + kColO + 64 * wg;
+      for (int s = wg; ok && s < n_dense; s += 2) {
+        const int J = tile_of(s);
+        float tb_all[TPB], wmul[TPB];
+        bool valid_all[TPB];
+        ATRACE(s, 0);
+        {
+          uint32_t tb_raw[TPB];
+          int tb_col[TPB];
+          tb_issue(J, tb_raw, tb_col, valid_all);
+          ok = warp_wait(&bars[kBarSFull + wg], (s >> 1) & 1, p.status, 32);
+          tmem_ld_wait();
+          ATRACE(s, 1);
+          if (!ok) break;
+          tc_fence_after();
+          tb_finish(tb_raw, tb_col, tb_all);
+        }
+#pragma unroll
+        for (int tt = 0; tt < TPB; ++tt) {
+          const int dt = ti_abs - (J * TPB + tt);
+          wmul[tt] = (p.window > 0 && dt > p.window && ti_abs != T - 1) ? 0.f : 1.f;
+        }
+        // pass 1: the row's maximum over the tile.  The TMEM load of the next 32 columns is always in
+        // flight while the current ones are processed (two register buffers).
+        float m_tile = -INFINITY;
+        uint32_t va[32], vb[32];
+        auto max_chunk = [&](const uint32_t (&v)[32], int c) {
+          const int tt = (32 * c) / CP;
+          float g0 = -INFINITY, g1 = -INFINITY;
+#pragma unroll
+          for (int jj = 0; jj < 32; jj += 2) {
+            const float2 cb = __half22float2(cbl[((32 * c + jj) % CP) / 2]);
+            g0 = fmaxf(g0, fmaf(__uint_as_float(v[jj]), wmul[tt], cb.x));
+            g1 = fmaxf(g1, fmaf(__uint_as_float(v[jj + 1]), wmul[tt], cb.y));
+          }
+          if (valid_all[tt]) m_tile = fmaxf(m_tile, fmaxf(g0, g1) + tb_all[tt]);
+        };
+        tmem_ld32(s_addr, va);
+        tmem_ld_wait();
+        tmem_ld32(s_addr + 32, vb);
+        max_chunk(va, 0);
+        tmem_ld_wait();
+        tmem_ld32(s_addr + 64, va);
+        max_chunk(vb, 1);
+        tmem_ld_wait();
+        tmem_ld32(s_addr + 96, vb);
+        max_chunk(va, 2);
+        tmem_ld_wait();
+        tmem_ld32(s_addr, va);  // first chunk of pass 2
+        max_chunk(vb, 3);
+        ATRACE(s, 2);
+        if (!wait_v(s)) { ok = false; break; }  // these warps vouch for V_s when they report P_s
+        if (s == wg) {
+          m_used = (m_tile == -INFINITY) ? 0.f : m_tile;
+        } else {
+          const bool need = m_tile > m_used + kRescaleThreshold;
+          if (__any_sync(0xffffffffu, need)) {
+            const int qp = q_of_v(s - 2);  // this accumulator's previous product
+            if (!warp_wait(&slot_free[qp % NS], (qp / NS) & 1, p.status, 33)) { ok = false; break; }
+            tc_fence_after();
+            const float alpha = need ? ex2(m_used - m_tile) : 1.f;
+#pragma unroll
+            for (int c0 = 0; c0 < D; c0 += 32) {
+              uint32_t v[32];
+              tmem_ld32(o_addr + c0, v);
+              tmem_ld_wait();
+#pragma unroll
+              for (int jj = 0; jj < 32; ++jj) v[jj] = __float_as_uint(__uint_as_float(v[jj]) * alpha);
+              tmem_st32(o_addr + c0, v);
+            }
+            tmem_st_wait();
+            l_sum *= alpha;
+            if (need) m_used = m_tile;
+          }
+        }
+        ATRACE(s, 3);
+        // pass 2: P = exp2(S2 - m) as bf16 over the consumed S columns (chunk c lands in columns 16c..16c+15,
+        // always behind the columns still to be read)
+        float psum = 0.f, psum1 = 0.f;
+        auto exp_chunk = [&](const uint32_t (&v)[32], int c) {
+          const int tt = (32 * c) / CP;
+          const float negmu = valid_all[tt] ? tb_all[tt] - m_used : -INFINITY;
+          uint32_t pk[16];
+#pragma unroll
+          for (int jj = 0; jj < 32; jj += 2) {
+            const float2 cb = __half22float2(cbl[((32 * c + jj) % CP) / 2]);
+            const float p0 = ex2(fmaf(__uint_as_float(v[jj]), wmul[tt], cb.x) + negmu);
+            const float p1 = ex2(fmaf(__uint_as_float(v[jj + 1]), wmul[tt], cb.y) + negmu);
+            psum += p0;
+            psum1 += p1;
+            pk[jj / 2] = pack_bf16(p0, p1);
+          }
+          tmem_st16(s_addr + 16 * c, pk);
+        };
+        tmem_ld_wait();
+        tmem_ld32(s_addr + 32, vb);
+        exp_chunk(va, 0);
+        tmem_ld_wait();
+        tmem_ld32(s_addr + 64, va);
+        exp_chunk(vb, 1);
+        tmem_ld_wait();
+        tmem_ld32(s_addr + 96, vb);
+        exp_chunk(va, 2);
+        tmem_ld_wait();
+        exp_chunk(vb, 3);
+        psum += psum1;
+        ATRACE(s, 4);
+        l_sum += psum;
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(&bars[kBarPFull + wg]);
+        if (s < 24) TRACE(8 + s);
+        ATRACE(s, 5);
+      }
+      // ---- merge the two accumulators: O_even <- O_even 2^(m_e - m) + O_odd 2^(m_o - m) ----
+      s_merge[wg * 128 + row] = m_used;
+      s_merge[256 + wg * 128 + row] = l_sum;
+      if (!ok) *s_giveup = 1;
+      softmax_bar();
+      if (*s_giveup != 0) ok = false;
+      if (ok) {
+        const float m_other = s_merge[(wg ^ 1) * 128 + row], l_other = s_merge[256 + (wg ^ 1) * 128 + row];
+        if (n_dense >= 2) {
+          const float m_new = fmaxf(m_used, m_other);
+          const float a_self = ex2(m_used - m_new), a_oth = ex2(m_other - m_new);
+          const int q1 = q_of_v(n_dense - 1), q2 = q_of_v(n_dense - 2);
+          ok = warp_wait(&slot_free[q1 % NS], (q1 / NS) & 1, p.status, 36);
+          if (ok) ok = warp_wait(&slot_free[q2 % NS], (q2 / NS) & 1, p.status, 36);
+          if (ok) {
+            tc_fence_after();
+            const float a_e = wg == 0 ? a_self : a_oth, a_o = wg == 0 ? a_oth : a_self;
+            uint32_t ve[32], vo[32];
+            tmem_ld32(lane_base + kColO + wg * DW, ve);
+            tmem_ld32(lane_base + kColO + 64 + wg * DW, vo);
+            tmem_ld_wait();
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj)
+              ve[jj] = __float_as_uint(__uint_as_float(ve[jj]) * a_e + __uint_as_float(vo[jj]) * a_o);
+            tmem_st32(lane_base + kColO + wg * DW, ve);
+            tmem_st_wait();
+            tc_fence_before();
+          }
+          l_sum = wg == 0 ? l_sum * a_self + l_other * a_oth : 0.f;
+          m_used = m_new;
+        } else if (wg == 1) {  // a single dense tile: the second warpgroup adopts the first one's maximum
+          m_used = m_other;
+          l_sum = 0.f;
+        }
+      }
+    } else {
     for (int s = 0; s < n_dense; ++s) {
       const int buf = s & 1;
       const int J = tile_of(s);
@@ -534,12 +718,14 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
       int tb_col[TPB];
 #pragma unroll
       for (int tt = 0; tt < TPB; ++tt) { tb_all[tt] = 0.f; valid_all[tt] = false; tb_raw[tt] = 0; tb_col[tt] = 0; }
+      DTRACE(s, 0);
       if (ok) tb_issue(J, tb_raw, tb_col, valid_all);
       float tbv[TPW], wmul[TPW];
       bool valid[TPW];
       float sreg[64];
       if (ok && !warp_wait(&bars[kBarSFull + buf], (s >> 1) & 1, p.status, 32)) ok = false;
       float m_part = -INFINITY;
+      DTRACE(s, 1);
       if (ok) {
         tc_fence_after();
         uint32_t v0[32], v1[32];
@@ -547,6 +733,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
         tmem_ld32(s_addr + 32, v1);
         if (!wait_v(s)) ok = false;  // overlaps the TMEM round trips
         tmem_ld_wait();
+        DTRACE(s, 2);
         tb_finish(tb_raw, tb_col, tb_all);
 #pragma unroll
         for (int jj = 0; jj < 32; ++jj) {
@@ -586,7 +773,9 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
       // the two column halves of a row must agree on the tile maximum
       s_max[(buf * 2 + wg) * 128 + row] = m_part;
       if (!ok) *s_giveup = 1;
+      DTRACE(s, 3);
       softmax_bar();
+      DTRACE(s, 4);
       if (*s_giveup != 0) { ok = false; break; }  // some warp's wait ran out: everyone leaves together
       const float m_tile = fmaxf(m_part, s_max[(buf * 2 + (wg ^ 1)) * 128 + row]);
       if (s == 0) {
@@ -597,6 +786,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
       }
       // (P_s reuses the columns of S_s / P_{s-2}; S_full of this tile already implies PV_{s-2} is done)
       float negmu[TPW];
+      DTRACE(s, 5);
 #pragma unroll
       for (int tl = 0; tl < TPW; ++tl) negmu[tl] = valid[tl] ? tbv[tl] - m_used : -INFINITY;
       float psum = 0.f;
@@ -612,11 +802,15 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
       l_sum += psum;
       tmem_st16(s_addr, lo);  // P (bf16) over this thread's own, already consumed S columns
       tmem_st16(s_addr + 16, hi);
+      DTRACE(s, 6);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bars[kBarPFull + buf]);
+      DTRACE(s, 7);
       if (s < 24) TRACE(8 + s);
     }
+
+    }  // !ALT
 
     // ------------------------------ light tiles ------------------------------
     // P[i,k] = a_i[t_k] * bc_i[c_k]: one exponential per (row, key time step), packed bf16
@@ -641,7 +835,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
         if (!ok) break;
         tb_finish(tb_raw, tb_col, tb_all);
       }
-      if (s >= 12 && s < 16) TRACE(112 + 4 * (s - 12));
+      if (LTRACE_ON && s >= 12 && s < 16) TRACE(112 + 4 * (s - 12));
       float m_tile = -INFINITY;
 #pragma unroll
       for (int tt = 0; tt < TPB; ++tt)
@@ -654,7 +848,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
         if (!ok) break;
         tc_fence_after();
       }
-      if (s >= 12 && s < 16) TRACE(113 + 4 * (s - 12));
+      if (LTRACE_ON && s >= 12 && s < 16) TRACE(113 + 4 * (s - 12));
       uint32_t lo[16], hi[16];
 #pragma unroll
       for (int tl = 0; tl < TPW; ++tl) {
@@ -677,9 +871,9 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
       const uint32_t p_addr = lane_base + kColS + 64 * (l & 3) + 32 * wg;
       tmem_st16(p_addr, lo);
       tmem_st16(p_addr + 16, hi);
-      if (s >= 12 && s < 16) TRACE(114 + 4 * (s - 12));
+      if (LTRACE_ON && s >= 12 && s < 16) TRACE(114 + 4 * (s - 12));
       tmem_st_wait();
-      if (s >= 12 && s < 16) TRACE(115 + 4 * (s - 12));
+      if (LTRACE_ON && s >= 12 && s < 16) TRACE(115 + 4 * (s - 12));
       tc_fence_before();
       mbar_arrive(&bars[kBarPlFull + (l & 3)]);
       if (s < 24) TRACE(8 + s);
@@ -724,6 +918,14 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
     tc_fence_after();
     tmem_dealloc(tmem, kTmemCols);
   }
+#ifdef MVPA_TC_TRACE
+  if (tid == 0) {
+    unsigned long long gt;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+    p.trace[(size_t)blockIdx.x * 128 + 127] = (long long)gt;
+    p.trace[(size_t)blockIdx.x * 128 + 7] = clock64();
+  }
+#endif
 }
 
 int make_maps(TcMaps& m, const Args& a, int CP) {
