@@ -38,12 +38,11 @@ struct BwdArgs {
   float *du, *dvt, *dz, *drt, *drc;
   // workspace carve-up (fp32 elements)
   float *tbg, *cbg;    // (B*H, N, T), (B*H, N, C) relative scores, base-2 scaled
-  float *dtbg, *dcbg;  // gradients w.r.t. the unscaled relative scores; (B*H, N, slots) from the CUDA-core
-                       // kernels, (B*H, slots, N) from the tensor-core ones
+  float *dtbg, *dcbg;  // gradients w.r.t. the unscaled relative scores, (B*H, N, slots); the tensor-core
+                       // kernels use dtbg as (B*H, T, N) scratch and leave dcbg alone
   float* delta;        // (B*H, N)
   float* partial;      // (B*H*nQT, 3, D) per-tile column sums for du/dvt/dz
   float* drel_part;    // (split, Hkv, T + C, D) split-K partials of dr_time / dr_chan
-  float* drel_cs;      // (split, Hkv, T + C) split partials of the column sums of dtbg / dcbg
   float* tc_extra;     // workspace of the tensor-core query-side kernel (bf16 problems it supports)
 };
 
@@ -62,13 +61,12 @@ size_t tc_fwd_workspace_bytes(const mvpa_problem* p);
 int tc_fwd(const Args& a, void* workspace, size_t workspace_bytes, cudaStream_t s);
 int tc_fwd_static(const Args& a, cudaStream_t s);  // same, scratch in a built-in device array
 
-// tcgen05 backward for bf16 (mvpa_tc_bwd.cu): dq, dk, dv and the gradients of the two relative score
-// matrices (into the workspace of the CUDA-core backward, which reduces them to dr_time / dr_chan);
-// tc_bwd_bias then turns the column sums both leave behind into du / dvt / dz.
+// tcgen05 backward for bf16 (mvpa_tc_bwd.cu): dq, dk, dv, and per-kv-head accumulators of the
+// relative-key gradients; tc_bwd_bias turns those into dr_time / dr_chan / du / dvt / dz.
 bool tc_bwd_q_supported(const Args& a);
 size_t tc_bwd_q_workspace_floats(const mvpa_problem* p);
 int tc_bwd_q(const BwdArgs& b, float* extra_workspace, cudaStream_t s);
-int tc_bwd_bias(const BwdArgs& b, float* extra_workspace, int n_split, cudaStream_t s);
+int tc_bwd_bias(const BwdArgs& b, float* extra_workspace, cudaStream_t s);
 
 template <typename T>
 __device__ __forceinline__ float to_f32(T x);

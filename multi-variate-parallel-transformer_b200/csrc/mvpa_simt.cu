@@ -557,9 +557,7 @@ __global__ void __launch_bounds__(kThreads) simt_dkv_kernel(BwdArgs bw) {
 }
 
 // dr[hk][slot][d] = sum_{b, h in group, i} dX[b,h,i,slot] * (q[b,h,i,d] + bias[hk][d])
-// One CTA per (32 slots, kv head, split); streams its share of the group's query rows in chunks
-// of 64.  Also leaves the plain column sums sum_i dX[.,i,slot] per split (they become dvt / dz on
-// the tensor-core path).
+// One CTA per (32 slots, kv head, split); streams its share of the group's query rows in chunks of 64.
 template <typename Tin, int D>
 __global__ void __launch_bounds__(kThreads) simt_drel_kernel(BwdArgs bw, int which) {
   constexpr int LD = D + 4;
@@ -580,7 +578,6 @@ __global__ void __launch_bounds__(kThreads) simt_drel_kernel(BwdArgs bw, int whi
   const int per_z = (n_chunks + gridDim.z - 1) / gridDim.z;
   const int c_begin = blockIdx.z * per_z, c_end = min(n_chunks, c_begin + per_z);
   float acc[2][DV] = {};
-  float colsum = 0.f;  // threads 0..31: one slot each
   for (int ch = c_begin; ch < c_end; ++ch) {
     {
       const int b = ch / (p.g * chunks_per_head), hh = (ch / chunks_per_head) % p.g;
@@ -590,25 +587,13 @@ __global__ void __launch_bounds__(kThreads) simt_drel_kernel(BwdArgs bw, int whi
       {
         __syncthreads();
         load_tile<Tin, D>(Qs, q, p.q_sn, m0, p.N, kBN, bias, 1.f);
-        if (bw.tc_extra != nullptr) {  // the tensor-core kernels leave (bh, slot, row): rows innermost
-          for (int idx = tid; idx < kBN * 32; idx += kThreads) {
-            const int r = idx % kBN, s = idx / kBN;
-            const int i = m0 + r;
-            Xs[r * 33 + s] = (i < p.N && s0 + s < S) ? dx[((int64_t)bh * S + s0 + s) * p.N + i] : 0.f;
-          }
-        } else {
-          for (int idx = tid; idx < kBN * 32; idx += kThreads) {
-            const int r = idx / 32, s = idx % 32;
-            const int i = m0 + r;
-            Xs[r * 33 + s] = (i < p.N && s0 + s < S) ? dx[((int64_t)bh * p.N + i) * S + s0 + s] : 0.f;
-          }
+        for (int idx = tid; idx < kBN * 32; idx += kThreads) {
+          const int r = idx / 32, s = idx % 32;
+          const int i = m0 + r;
+          Xs[r * 33 + s] = (i < p.N && s0 + s < S) ? dx[((int64_t)bh * p.N + i) * S + s0 + s] : 0.f;
         }
         __syncthreads();
         // rows >= N hold bias only in Qs but zero in Xs, so they add nothing
-        if (tid < 32) {
-#pragma unroll 8
-          for (int r = 0; r < kBN; ++r) colsum += Xs[r * 33 + tid];
-        }
 #pragma unroll 4
         for (int r = 0; r < kBN; ++r) {
           const float x0 = Xs[r * 33 + 2 * ty], x1 = Xs[r * 33 + 2 * ty + 1];
@@ -630,8 +615,6 @@ __global__ void __launch_bounds__(kThreads) simt_drel_kernel(BwdArgs bw, int whi
       for (int e = 0; e < DV; ++e) out[(int64_t)s * D + tx + 16 * e] = acc[a][e];
     }
   }
-  if (tid < 32 && s0 + tid < S)
-    bw.drel_cs[((int64_t)blockIdx.z * p.Hkv + hk) * (p.T + p.C) + (which == 0 ? 0 : p.T) + s0 + tid] = colsum;
 }
 
 // dr_time / dr_chan = sum of the split-K partials of simt_drel_kernel (fixed order: deterministic).
@@ -731,6 +714,10 @@ int launch_bwd(const BwdArgs& b, cudaStream_t s) {
     simt_dkv_kernel<Tin, D><<<grid, kThreads, smem, s>>>(b);
     count_launch();
   }
+  if (b.tc_extra != nullptr) {  // the tensor-core kernels have accumulated the relative-key gradients already
+    MVPA_CUDA_CHECK(cudaGetLastError());
+    return tc_bwd_bias(b, b.tc_extra, s);
+  }
   {
     const size_t smem = sizeof(float) * ((size_t)kBN * 33 + kBN * LD);
     int rc = set_smem(simt_drel_kernel<Tin, D>, smem);
@@ -739,10 +726,6 @@ int launch_bwd(const BwdArgs& b, cudaStream_t s) {
     simt_drel_kernel<Tin, D><<<dim3((a.C + 31) / 32, a.Hkv, kDrelSplit), kThreads, smem, s>>>(b, 1);
     simt_drel_reduce_kernel<<<148, 256, 0, s>>>(b, kDrelSplit);
     count_launch(3);
-  }
-  if (b.tc_extra != nullptr) {
-    MVPA_CUDA_CHECK(cudaGetLastError());
-    return tc_bwd_bias(b, b.tc_extra, kDrelSplit, s);
   }
   simt_dbias_kernel<<<dim3(a.Hkv, 3), 128, 0, s>>>(b, n_qt);
   count_launch();
@@ -786,7 +769,7 @@ size_t simt_bwd_workspace_floats(const mvpa_problem* p) {
   const size_t BH = (size_t)p->B * p->H, N = (size_t)p->T * p->C;
   const size_t n_qt = (N + kBM - 1) / kBM;
   size_t n = 2 * BH * N * (p->T + p->C) + BH * N + BH * n_qt * 3 * p->D +
-             (size_t)kDrelSplit * p->Hkv * (p->T + p->C) * (p->D + 1);
+             (size_t)kDrelSplit * p->Hkv * (p->T + p->C) * p->D;
   n = (n + 63) & ~(size_t)63;  // keep what follows 256-byte aligned
   if (p->dtype == MVPA_BF16) n += tc_bwd_q_workspace_floats(p);
   return n;
@@ -803,8 +786,7 @@ void simt_bwd_carve(BwdArgs& b, float* ws) {
   b.delta = b.dcbg + BH * N * a.C;
   b.partial = b.delta + BH * N;
   b.drel_part = b.partial + BH * n_qt * 3 * a.D;
-  b.drel_cs = b.drel_part + (size_t)kDrelSplit * a.Hkv * (a.T + a.C) * a.D;
-  size_t used = (size_t)(b.drel_cs - ws) + (size_t)kDrelSplit * a.Hkv * (a.T + a.C);
+  size_t used = (size_t)(b.drel_part - ws) + (size_t)kDrelSplit * a.Hkv * (a.T + a.C) * a.D;
   used = (used + 63) & ~(size_t)63;
   b.tc_extra = ws + used;  // only meaningful for bf16 problems; the caller clears it otherwise
 }

@@ -63,7 +63,8 @@ struct BqArgs {
   // Everything a thread (= query row) reads or writes per row is stored row-innermost, so that the 32
   // rows of a warp touch consecutive addresses.
   float* dtb;          // (B*H, T, N) zero-initialised; slot T-1-(t_i-t_k)
-  float* dcb;          // (B*H, C, N) slot C-1-|c_i-c_k|
+  float* racc;         // (Hkv, 2, D, 128) fp32, zero-initialised: sum over query rows of dTB^T Q' / dCB^T Q'
+  float* cacc;         // (Hkv, 2, 128)    fp32, zero-initialised: column sums of dTB / dCB (as bf16, like racc)
   // per query row, kept for the key-side kernel (which visits every query tile many times):
   //   Q' = (q+u) c2 as (B*H, N, D) bf16, written through the `qp` tensor map
   __half* cblw;        // (B*H, CP/8, N, 8) channel scores gathered by key channel slot, relative to their max
@@ -77,7 +78,7 @@ struct BqArgs {
 
 enum BarrierIndex {
   kBarProFull = 0, kBarProMma, kBarProDone, kBarSdpFull, kBarDsFull, kBarAllDone,
-  kBarFinFull, kBarFinLoaded, kBarFinDone,
+  kBarFinFull, kBarFinLoaded, kBarFinDone, kBarRelDone,
   kBarSlotFull,  // NS, then slot_free NS
 };
 
@@ -186,6 +187,7 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
     mbar_init(&bars[kBarFinFull], kSoftmaxThreads);
     mbar_init(&bars[kBarFinLoaded], 1);
     mbar_init(&bars[kBarFinDone], 1);
+    mbar_init(&bars[kBarRelDone], 1);
     for (int i = 0; i < NS; ++i) {
       mbar_init(&slot_full[i], 1);
       mbar_init(&slot_free[i], 1);
@@ -348,6 +350,30 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
       }
       mma_commit(&bars[kBarFinDone]);
       BTRACE(30);
+      // Relative-key gradients of this tile's rows (autograd through `_rel_bias`, `attentions/attn.py:1305-1314`):
+      //   R_t[j, d] = sum_i dTB[i, j] Q'[i, d],  R_c[j, d] = sum_i dCB[i, j] Q'[i, d]   (A = the bf16 tiles the
+      //   softmax warps left in shared memory, keys-of-the-sum = query rows; B = Q' as MN-major operand)
+      // and the column sums of dTB / dCB as products with a tile of ones.  Accumulators: the idle S, dP
+      // and temporal-score columns.
+      if (ok) {
+        constexpr uint32_t idesc_r = make_idesc_bf16_ab(128, D, 1, 1);
+        constexpr uint32_t idesc_1 = make_idesc_bf16_ab(128, 16, 1, 0);
+        const DescHalves dtbt = make_desc_halves_sw128(smem_u32(ring), HALF, 1024);
+        const DescHalves dcbt = make_desc_halves_sw128(smem_u32(D == 128 ? sDO : ring + 98304), HALF, 1024);
+        const DescHalves dqm = make_desc_halves_sw128(smem_u32(sQ), HALF, 1024);
+        const DescHalves dones = make_desc_halves_sw128(smem_u32(ring + 32768), 16, 1024);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) mma_ss_h(tmem + kColTB, dtbt, kk * 2048, dqm, kk * 2048, idesc_r, kk > 0);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) mma_ss_h(tmem + kColS, dcbt, kk * 2048, dqm, kk * 2048, idesc_r, kk > 0);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t offb = (kk / 4) * 2048 + (kk % 4) * 32;
+          mma_ss_h(tmem + kColDP, dtbt, kk * 2048, dones, offb, idesc_1, kk > 0);
+          mma_ss_h(tmem + kColDP + 16, dcbt, kk * 2048, dones, offb, idesc_1, kk > 0);
+        }
+      }
+      mma_commit(&bars[kBarRelDone]);
       tma_store_wait_all();  // the store reads sQ: it has to finish before the CTA can go away
     }
   }
@@ -593,11 +619,12 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
     }
     softmax_bar();
     BTRACE(42);
-    // dCB[i, j], j = C-1-e, e = |c_i - c_k|: to the workspace (for dr_chan) and, as bf16 pairs, into TMEM
-    // columns kColDP + j/2 as the A operand of dQ += dCB r_chan.  Each warpgroup takes half of the slots.
+    // dCB[i, j], j = C-1-e, e = |c_i - c_k|, as bf16 pairs: into TMEM columns kColDP + j/2 (A operand of
+    // dQ += dCB r_chan) and into a shared-memory tile [row][j] (A operand, transposed, of the dr_chan product).
+    // Each warpgroup takes half of the slots.
+    uint8_t* s_cbt = D == 128 ? sDO : ring + 98304;  // dO is dead by now; at head_dim 64 the ring has room
     if (ok) {
       const int jb = wg * (CP / 2);
-      float* dst = p.dcb + (int64_t)bh * C * N + (row_valid ? n_loc : 0);
 #pragma unroll 2
       for (int m = 0; m < CP / 4; ++m) {
         float vv[2];
@@ -608,11 +635,14 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
           if (row_valid && e >= 0) {
             if (c_i - e >= 0) val += sc[row * CP + ((c_i - e + 2 * row) & (CP - 1))];
             if (e > 0 && c_i + e < C) val += sc[row * CP + ((c_i + e + 2 * row) & (CP - 1))];
-            dst[(int64_t)j * N] = val;
           }
           vv[t2] = val;
         }
-        tmem_st1(lane_base + kColDP + jb / 2 + m, pack_bf16(vv[0], vv[1]));
+        const uint32_t pk2 = pack_bf16(vv[0], vv[1]);
+        tmem_st1(lane_base + kColDP + jb / 2 + m, pk2);
+        const int j = jb + 2 * m;
+        *reinterpret_cast<uint32_t*>(s_cbt + (j >> 6) * HALF + row * 128 + ((((j & 63) >> 3) ^ (row & 7)) << 4) +
+                                     (j & 7) * 2) = pk2;
       }
     }
     BTRACE(43);
@@ -622,8 +652,10 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
     BTRACE(8);
     if (ok) {
       // dTB of the row (this thread's 64 of the 128 r_time rows) as bf16 pairs: A operand of dQ += dTB r_time
+      // in TMEM, and the [row][j] tile in shared memory for the dr_time product (the scatter area is dead)
       const float* src = p.dtb + ((int64_t)bh * T + 64 * wg) * N + (row_valid ? n_loc : 0);
       const float keep = row_valid ? 1.f : 0.f;
+      uint8_t* s_tbt = ring + wg * HALF + row * 128;
 #pragma unroll 1
       for (int m8 = 0; m8 < 32; m8 += 8) {
         float a[16];
@@ -636,7 +668,13 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
 #pragma unroll
         for (int e = 0; e < 8; ++e) pk[e] = pack_bf16(a[2 * e] * keep, a[2 * e + 1] * keep);
         tmem_st8(lane_base + kColS + 32 * wg + m8, pk);
+        const int c0 = m8 / 4;  // 16-byte chunks 2 m8/8 and the next one of this row's 128 bytes
+        *reinterpret_cast<uint4*>(s_tbt + (((c0) ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        *reinterpret_cast<uint4*>(s_tbt + (((c0 + 1) ^ (row & 7)) << 4)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
       }
+      // a [16 x 128] tile of ones (K-major): column sums of dTB / dCB come out of the tensor core too
+      *reinterpret_cast<uint4*>(ring + 32768 + tid * 16) = make_uint4(0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u);
+      fence_proxy_async_smem();
       BTRACE(45);
       tmem_st_wait();
     }
@@ -645,7 +683,7 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
     BTRACE(9);
     if (ok) ok = warp_wait(&bars[kBarFinDone], 0, p.status, 135);
     BTRACE(10);
-    uint8_t* s_out = ring;  // dq tile as bf16, laid out like a Q tile (128-byte swizzled rows)
+    uint8_t* s_out = ring + 65536;  // dq tile as bf16, laid out like a Q tile (the relative keys are dead)
     if (ok) {
       tc_fence_after();
 #pragma unroll 1
@@ -672,6 +710,34 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
       for (int hh = 0; hh < NH; ++hh) tma_store_5d(&maps.dq, s_out + hh * HALF, hh * 64, 0, I * TPB, h, b);
       tma_store_commit();
       tma_store_wait_all();
+    }
+    // relative-key gradient partials: lane = slot j now; added to the per-kv-head accumulators
+    if (ok) ok = warp_wait(&bars[kBarRelDone], 0, p.status, 136);
+    if (ok) {
+      tc_fence_after();
+      const int j = row;
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        const bool jv = which == 0 ? j < T : j < C;
+        float* acc = p.racc + (((size_t)hk * 2 + which) * D + wg * DW) * 128 + j;
+        const uint32_t col = which == 0 ? kColTB : kColS;
+#pragma unroll 1
+        for (int c8 = 0; c8 < DW; c8 += 8) {
+          uint32_t v[8];
+          tmem_ld8(lane_base + col + wg * DW + c8, v);
+          tmem_ld_wait();
+          if (jv) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) atomicAdd(acc + (size_t)(c8 + e) * 128, __uint_as_float(v[e]));
+          }
+        }
+        if (wg == which) {  // column sums: one warpgroup each
+          uint32_t cs1;
+          tmem_ld1(lane_base + kColDP + 16 * which, cs1);
+          tmem_ld_wait();
+          if (jv) atomicAdd(p.cacc + ((size_t)hk * 2 + which) * 128 + j, __uint_as_float(cs1));
+        }
+      }
     }
     BTRACE(11);
     tc_fence_before();
@@ -1039,37 +1105,64 @@ int make_maps(BqMaps& m, const BwdArgs& bw, int CP, const void* qp) {
 }
 
 // du / dvt / dz of one kv head: du = sum of the query tiles' content column sums; dvt = (column sums
-// of dTB) r_time, dz = (column sums of dCB) r_chan, the column sums coming from the split partials
-// the relative-key reduction leaves (`_rel_bias` adds q_btime / q_bchan to every row, so their
-// gradients are the row sums of dq's temporal / channel parts).
-__global__ void __launch_bounds__(128) tc_dbias_kernel(const float* __restrict__ cs_dq, const float* __restrict__ drel_cs,
-                                                       int n_split, const __nv_bfloat16* __restrict__ rt,
+// of dTB) r_time, dz = (column sums of dCB) r_chan (`_rel_bias` adds q_btime / q_bchan to every row, so
+// their gradients are the row sums of dq's temporal / channel parts).
+__global__ void __launch_bounds__(512) tc_dbias_kernel(const float* __restrict__ cs_dq, const float* __restrict__ cacc,
+                                                       const __nv_bfloat16* __restrict__ rt,
                                                        const __nv_bfloat16* __restrict__ rc, float* __restrict__ du,
                                                        float* __restrict__ dvt, float* __restrict__ dz, int B, int H,
-                                                       int Hkv, int g, int T, int C, int D, int n_qt) {
+                                                       int g, int T, int C, int D, int n_qt) {
   __shared__ float s_cs[256];
-  const int hk = blockIdx.x, S = T + C;
-  for (int j = threadIdx.x; j < S; j += blockDim.x) {
-    float sum = 0.f;
-    for (int zz = 0; zz < n_split; ++zz) sum += drel_cs[((size_t)zz * Hkv + hk) * S + j];
-    s_cs[j] = sum;
-  }
+  __shared__ float s_part[3][512];
+  const int hk = blockIdx.x;
+  if (threadIdx.x < 256) s_cs[threadIdx.x] = cacc[(size_t)hk * 256 + threadIdx.x];
   __syncthreads();
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float su = 0.f, st = 0.f, sz = 0.f;
-    for (int it = 0; it < n_qt; ++it)
-      for (int b = 0; b < B; ++b)
-        for (int hh = 0; hh < g; ++hh) su += cs_dq[((size_t)it * B * H + (size_t)b * H + hk * g + hh) * D + d];
-    for (int j = 0; j < T; ++j) st += s_cs[j] * __bfloat162float(rt[((size_t)hk * T + j) * D + d]);
-    for (int j = 0; j < C; ++j) sz += s_cs[T + j] * __bfloat162float(rc[((size_t)hk * C + j) * D + d]);
+  const int d = threadIdx.x % D, part = threadIdx.x / D, parts = blockDim.x / D;
+  float su = 0.f, st = 0.f, sz = 0.f;
+  const int n_items = n_qt * B * g;
+  for (int it = part; it < n_items; it += parts) {
+    const int tq = it / (B * g), b = (it / g) % B, hh = it % g;
+    su += cs_dq[((size_t)tq * B * H + (size_t)b * H + hk * g + hh) * D + d];
+  }
+  for (int j = part; j < T; j += parts) st += s_cs[j] * __bfloat162float(rt[((size_t)hk * T + j) * D + d]);
+  for (int j = part; j < C; j += parts) sz += s_cs[128 + j] * __bfloat162float(rc[((size_t)hk * C + j) * D + d]);
+  s_part[0][threadIdx.x] = su;
+  s_part[1][threadIdx.x] = st;
+  s_part[2][threadIdx.x] = sz;
+  __syncthreads();
+  if (part == 0) {
+    for (int q = 1; q < parts; ++q) {
+      su += s_part[0][q * D + d];
+      st += s_part[1][q * D + d];
+      sz += s_part[2][q * D + d];
+    }
     du[hk * D + d] = su;
     dvt[hk * D + d] = st;
     dz[hk * D + d] = sz;
   }
 }
 
+// dr_time / dr_chan from the accumulators of the query-side kernel:
+//   dr[j, d] = sum_i dX[i, j] (q[i, d] + bias[d]) = R'[j, d] / c2 + colsum[j] (bias[d] - u[d]),   Q' = (q + u) c2.
+__global__ void __launch_bounds__(256) tc_drel_final_kernel(const float* __restrict__ racc, const float* __restrict__ cacc,
+                                                            const __nv_bfloat16* __restrict__ u,
+                                                            const __nv_bfloat16* __restrict__ vt,
+                                                            const __nv_bfloat16* __restrict__ z, float* __restrict__ drt,
+                                                            float* __restrict__ drc, int T, int C, int D, float inv_c2) {
+  const int hk = blockIdx.x, which = blockIdx.y, S = which == 0 ? T : C;
+  const float* acc = racc + ((size_t)hk * 2 + which) * D * 128;
+  const float* cs = cacc + ((size_t)hk * 2 + which) * 128;
+  const __nv_bfloat16* bias = (which == 0 ? vt : z) + (size_t)hk * D;
+  float* out = (which == 0 ? drt : drc) + (size_t)hk * S * D;
+  for (int idx = threadIdx.x; idx < S * D; idx += blockDim.x) {
+    const int j = idx / D, d = idx % D;
+    out[idx] = acc[(size_t)d * 128 + j] * inv_c2 +
+               cs[j] * (__bfloat162float(bias[d]) - __bfloat162float(u[(size_t)hk * D + d]));
+  }
+}
+
 template <int D, int CP>
-int launch(const BwdArgs& bw, float* cs_dq, int* status, float* relc, float* rows_ws, cudaStream_t s) {
+int launch(const BwdArgs& bw, float* cs_dq, int* status, float* relc, float* racc, float* rows_ws, cudaStream_t s) {
   const Args& a = bw.a;
   BqMaps maps;
   int rc = make_maps(maps, bw, CP, rows_ws);
@@ -1077,7 +1170,8 @@ int launch(const BwdArgs& bw, float* cs_dq, int* status, float* relc, float* row
   BqArgs t;
   t.u = (const __nv_bfloat16*)a.u;
   t.relc = relc; t.lse = a.lse; t.delta = bw.delta;
-  t.cs_dq = cs_dq; t.dtb = bw.dtbg; t.dcb = bw.dcbg;
+  t.cs_dq = cs_dq; t.dtb = bw.dtbg;
+  t.racc = racc; t.cacc = racc + (size_t)a.Hkv * 2 * D * 128;
   {
     const size_t rows = (size_t)a.B * a.H * a.N;
     t.cblw = reinterpret_cast<__half*>(rows_ws + rows * (D / 2));
@@ -1103,6 +1197,7 @@ int launch(const BwdArgs& bw, float* cs_dq, int* status, float* relc, float* row
   static_assert(Cfg<D>::EARLY >= 2, "the first tile's K and V load while the prologue runs");
   MVPA_CUDA_CHECK(cudaFuncSetAttribute(tc_bwd_q_kernel<D, CP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   MVPA_CUDA_CHECK(cudaMemsetAsync(status, 0, 256, s));
+  MVPA_CUDA_CHECK(cudaMemsetAsync(racc, 0, sizeof(float) * (size_t)a.Hkv * (2 * D * 128 + 256), s));
   MVPA_CUDA_CHECK(cudaMemsetAsync(bw.dtbg, 0, sizeof(float) * (size_t)a.B * a.H * a.N * a.T, s));
   rel_const_kernel<<<a.Hkv, 256, 0, s>>>((const __nv_bfloat16*)a.vt, (const __nv_bfloat16*)a.z,
                                         (const __nv_bfloat16*)a.rt, (const __nv_bfloat16*)a.rc, relc, a.T, a.C, D);
@@ -1127,7 +1222,8 @@ size_t tc_bwd_q_workspace_floats(const mvpa_problem* p) {
   const size_t rows = (size_t)p->B * p->H * p->T * p->C;
   // column sums + status + constants + per-row data for the key side (Q' bf16, channel scores fp16
   // padded to 128 slots, offset, temporal scores)
-  size_t n = cs_dq_floats(p->B, p->H, p->T, p->D) + 64 + (size_t)p->Hkv * 256 + rows * (p->D / 2) + rows * 64 +
+  size_t n = cs_dq_floats(p->B, p->H, p->T, p->D) + 64 + (size_t)p->Hkv * 256 +
+             (size_t)p->Hkv * (2 * p->D * 128 + 256) + rows * (p->D / 2) + rows * 64 +
              ((rows + 3) & ~(size_t)3) + rows * p->T + 64;
 #ifdef MVPA_TC_TRACE
   n = ((n + 63) & ~(size_t)63) + (size_t)p->B * p->H * p->T * 128;  // the timeline sits at the very end
@@ -1135,13 +1231,17 @@ size_t tc_bwd_q_workspace_floats(const mvpa_problem* p) {
   return n;
 }
 
-int tc_bwd_bias(const BwdArgs& bw, float* extra, int n_split, cudaStream_t s) {
+int tc_bwd_bias(const BwdArgs& bw, float* extra, cudaStream_t s) {
   const Args& a = bw.a;
   const int CP = a.C <= 32 ? 32 : (a.C <= 64 ? 64 : 128), TPB = 128 / CP;
-  tc_dbias_kernel<<<a.Hkv, 128, 0, s>>>(extra, bw.drel_cs, n_split, (const __nv_bfloat16*)a.rt,
-                                       (const __nv_bfloat16*)a.rc, bw.du, bw.dvt, bw.dz, a.B, a.H, a.Hkv, a.g, a.T,
-                                       a.C, a.D, (a.T + TPB - 1) / TPB);
-  count_launch();
+  const float* racc = extra + cs_dq_floats(a.B, a.H, a.T, a.D) + 64 + (size_t)a.Hkv * 256;
+  const float* cacc = racc + (size_t)a.Hkv * 2 * a.D * 128;
+  tc_dbias_kernel<<<a.Hkv, 512, 0, s>>>(extra, cacc, (const __nv_bfloat16*)a.rt, (const __nv_bfloat16*)a.rc, bw.du,
+                                       bw.dvt, bw.dz, a.B, a.H, a.g, a.T, a.C, a.D, (a.T + TPB - 1) / TPB);
+  tc_drel_final_kernel<<<dim3(a.Hkv, 2), 256, 0, s>>>(racc, cacc, (const __nv_bfloat16*)a.u,
+                                                     (const __nv_bfloat16*)a.vt, (const __nv_bfloat16*)a.z, bw.drt,
+                                                     bw.drc, a.T, a.C, a.D, 1.f / a.c2);
+  count_launch(2);
   MVPA_CUDA_CHECK(cudaGetLastError());
   return MVPA_OK;
 }
@@ -1151,16 +1251,17 @@ int tc_bwd_q(const BwdArgs& bw, float* extra, cudaStream_t s) {
   float* dqc = extra;  // column sums of dq's content part, one row of D per query-side CTA
   int* status = reinterpret_cast<int*>(extra + cs_dq_floats(a.B, a.H, a.T, a.D));
   float* relc = reinterpret_cast<float*>(status) + 64;
-  float* rows_ws = relc + (size_t)a.Hkv * 256;
+  float* racc = relc + (size_t)a.Hkv * 256;
+  float* rows_ws = racc + (size_t)a.Hkv * (2 * a.D * 128 + 256);
   const int CP = a.C <= 32 ? 32 : (a.C <= 64 ? 64 : 128);
   if (a.D == 64) {
-    if (CP == 32) return launch<64, 32>(bw, dqc, status, relc, rows_ws, s);
-    if (CP == 64) return launch<64, 64>(bw, dqc, status, relc, rows_ws, s);
-    return launch<64, 128>(bw, dqc, status, relc, rows_ws, s);
+    if (CP == 32) return launch<64, 32>(bw, dqc, status, relc, racc, rows_ws, s);
+    if (CP == 64) return launch<64, 64>(bw, dqc, status, relc, racc, rows_ws, s);
+    return launch<64, 128>(bw, dqc, status, relc, racc, rows_ws, s);
   }
-  if (CP == 32) return launch<128, 32>(bw, dqc, status, relc, rows_ws, s);
-  if (CP == 64) return launch<128, 64>(bw, dqc, status, relc, rows_ws, s);
-  return launch<128, 128>(bw, dqc, status, relc, rows_ws, s);
+  if (CP == 32) return launch<128, 32>(bw, dqc, status, relc, racc, rows_ws, s);
+  if (CP == 64) return launch<128, 64>(bw, dqc, status, relc, racc, rows_ws, s);
+  return launch<128, 128>(bw, dqc, status, relc, racc, rows_ws, s);
 }
 
 }  // namespace mvpa
