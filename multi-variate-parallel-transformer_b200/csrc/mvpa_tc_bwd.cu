@@ -20,8 +20,8 @@
 // cores: dQ += dTB r_time + dCB r_chan (autograd through `_rel_bias`, `attentions/attn.py:1305-1314`),
 // and dq leaves as bf16.
 //
-// TMEM columns: [0,128) S / dS, [128,256) dP, [256,256+D) dQ, [384,512) raw temporal products.
-// S / dP are single-buffered: MMA and softmax work alternate within a CTA.
+// TMEM columns: [0,128) and [128,256) S / dS (two buffers), [256,384) dP, [384,384+D) dQ: the score
+// product of the next tile runs while the softmax warps work on the current one.
 #include <cuda_fp16.h>
 
 #include "mvpa_common.cuh"
@@ -38,8 +38,6 @@ constexpr int kThreads = 384;  // warps 10, 11 only donate their registers
 constexpr int kTmemCols = 512;
 constexpr uint32_t kColS = 0;
 constexpr uint32_t kColDP = 128;
-constexpr uint32_t kColDQ = 256;
-constexpr uint32_t kColTB = 384;
 
 // Optional in-kernel timeline of the query-side kernel (build with -DMVPA_TC_TRACE): 64 clock64
 // stamps per CTA behind the regular workspace.
@@ -77,7 +75,7 @@ struct BqArgs {
 };
 
 enum BarrierIndex {
-  kBarProFull = 0, kBarProMma, kBarProDone, kBarSdpFull, kBarDsFull, kBarAllDone,
+  kBarProFull = 0, kBarProMma, kBarProDone, kBarSFull, kBarSFull1, kBarDpFull, kBarDpFull1, kBarDsFull, kBarDsFull1, kBarAllDone,
   kBarFinFull, kBarFinLoaded, kBarFinDone, kBarRelDone,
   kBarSlotFull,  // NS, then slot_free NS
 };
@@ -144,6 +142,11 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
   constexpr int NCH = CP < 64 ? CP : 64;
   constexpr int KSTEPS = D / 16;
   constexpr int DW = D / 2;
+  // TMEM columns: S / dS double-buffered, so that the score product of the next tile runs while the
+  // softmax warps work on this one.  The raw temporal products only pass through the dQ columns during
+  // the prologue (the scaled scores are re-read from the workspace, tile by tile); the dr_time
+  // accumulator of the epilogue takes the second S buffer.
+  constexpr uint32_t kQS = 0, kQS1 = 128, kQDP = 256, kQDQ = 384;
   static_assert(CP >= 32 && CP <= 128 && (CP & (CP - 1)) == 0, "CP in {32,64,128}");
 
   extern __shared__ uint8_t smem_raw[];
@@ -181,8 +184,12 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
     mbar_init(&bars[kBarProFull], 1);
     mbar_init(&bars[kBarProMma], 1);
     mbar_init(&bars[kBarProDone], kSoftmaxThreads);
-    mbar_init(&bars[kBarSdpFull], 1);
+    mbar_init(&bars[kBarSFull], 1);
+    mbar_init(&bars[kBarSFull + 1], 1);
+    mbar_init(&bars[kBarDpFull], 1);
+    mbar_init(&bars[kBarDpFull + 1], 1);
     mbar_init(&bars[kBarDsFull], kSoftmaxThreads);
+    mbar_init(&bars[kBarDsFull + 1], kSoftmaxThreads);
     mbar_init(&bars[kBarAllDone], 1);
     mbar_init(&bars[kBarFinFull], kSoftmaxThreads);
     mbar_init(&bars[kBarFinLoaded], 1);
@@ -267,13 +274,13 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
 #pragma unroll
         for (int kk = 0; kk < KSTEPS; ++kk) {
           const uint32_t off = (kk / 4) * HALF + (kk % 4) * 32;
-          mma_ss_h(tmem + kColTB, dq, off, dr, off, idesc_s, kk > 0);
+          mma_ss_h(tmem + kQDQ, dq, off, dr, off, idesc_s, kk > 0);
         }
 #pragma unroll
         for (int kk = 0; kk < KSTEPS; ++kk) {
           const uint32_t offa = (kk / 4) * HALF + (kk % 4) * 32;
           const uint32_t offb = (kk / 4) * (CP * 128) + (kk % 4) * 32;
-          mma_ss_h(tmem + kColS, dq, offa, dc, offb, idesc_c, kk > 0);
+          mma_ss_h(tmem + kQS, dq, offa, dc, offb, idesc_c, kk > 0);
         }
         mma_commit(&bars[kBarProMma]);
         ok = mbar_wait(&bars[kBarProDone], 0, p.status, 121);
@@ -283,51 +290,59 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
           tma_store_commit();
         }
       }
-      int prev_k_sl = -1;  // K slot of the previous tile if it was dense (its dQ product is still owed)
-      for (int s = 0; ok && s <= n_tiles; ++s) {
-        if (s > 0) {
-          // softmax warps are done with tile s-1: dS_w sits in the S columns, dP has been read
-          ok = mbar_wait(&bars[kBarDsFull], (s - 1) & 1, p.status, 122);
-          if (!ok) break;
-          tc_fence_after();
-          if (prev_k_sl >= 0) {  // dQ += dS_w K   (A from TMEM, K as MN-major operand)
-            const uint32_t b_lo = dmn0.lo + (uint32_t)prev_k_sl * (TILE >> 4);
-            mma_ts_x4(tmem + kColDQ, tmem + kColS, b_lo, dmn0.hi, 2048 >> 4, idesc_q, (uint32_t)(s - 1 > 0));
-            mma_ts_x4(tmem + kColDQ, tmem + kColS + 64, b_lo + 4 * (2048 >> 4), dmn0.hi, 2048 >> 4, idesc_q, 1u);
-            mma_commit(&slot_free[prev_k_sl]);
-          }
-        }
-        if (s == n_tiles) break;
-        const bool dense = s < n_dense;
-        const int qv = q_of_v(s), vsl = qv % NS;
-        if (dense) {
-          const int qk = q_of_k(s), ksl = qk % NS;
-          ok = mbar_wait(&slot_full[ksl], (qk / NS) & 1, p.status, 123);
-          if (!ok) break;
-          tc_fence_after();
-          DescHalves dk = dkm0;
-          dk.lo += (uint32_t)ksl * (TILE >> 4);
+      // Order on the tensor pipe: S_{s+1} (needs nothing from the softmax warps) runs while they work on
+      // tile s; once they report dS_s, dP_{s+1} goes first (their second phase waits for it), then dQ += dS_s K_s.
+      auto issue_s = [&](int s) {
+        const int qk = q_of_k(s), ksl = qk % NS;
+        ok = mbar_wait(&slot_full[ksl], (qk / NS) & 1, p.status, 123);
+        if (!ok) return;
+        tc_fence_after();
+        DescHalves dk = dkm0;
+        dk.lo += (uint32_t)ksl * (TILE >> 4);
 #pragma unroll
-          for (int kk = 0; kk < KSTEPS; ++kk) {  // S = Q' K^T
-            const uint32_t off = (kk / 4) * HALF + (kk % 4) * 32;
-            mma_ss_h(tmem + kColS, dq, off, dk, off, idesc_s, kk > 0);
-          }
-          prev_k_sl = ksl;
-        } else {
-          prev_k_sl = -1;
+        for (int kk = 0; kk < KSTEPS; ++kk) {  // S = Q' K^T
+          const uint32_t off = (kk / 4) * HALF + (kk % 4) * 32;
+          mma_ss_h(tmem + kQS + 128 * (s & 1), dq, off, dk, off, idesc_s, kk > 0);
         }
+        mma_commit(&bars[kBarSFull + (s & 1)]);
+      };
+      auto issue_dp = [&](int s) {
+        const int qv = q_of_v(s), vsl = qv % NS;
         ok = mbar_wait(&slot_full[vsl], (qv / NS) & 1, p.status, 124);
-        if (!ok) break;
+        if (!ok) return;
         tc_fence_after();
         DescHalves dv = dkm0;
         dv.lo += (uint32_t)vsl * (TILE >> 4);
 #pragma unroll
         for (int kk = 0; kk < KSTEPS; ++kk) {  // dP = dO V^T  (V rows = keys, D contiguous: K-major operand)
           const uint32_t off = (kk / 4) * HALF + (kk % 4) * 32;
-          mma_ss_h(tmem + kColDP, ddo, off, dv, off, idesc_s, kk > 0);
+          // a light tile has no score product: its dP takes the idle S buffer, so two are in flight
+          mma_ss_h(tmem + (s < n_dense ? kQDP : kQS + 128 * (s & 1)), ddo, off, dv, off, idesc_s, kk > 0);
         }
-        mma_commit(&bars[kBarSdpFull]);
+        mma_commit(&bars[kBarDpFull + (s & 1)]);
         mma_commit(&slot_free[vsl]);
+      };
+      if (ok) issue_s(0);  // the newest key tile is always dense
+      if (ok) issue_dp(0);
+      for (int s = 0; ok && s < n_tiles; ++s) {
+        if (s + 1 < n_dense) issue_s(s + 1);
+        // (S buffer (s+1)&1 is free: tile s-1 left it when its dS / dP was consumed)
+        if (ok && s + 1 >= n_dense && s + 1 < n_tiles) issue_dp(s + 1);
+        // (two barriers, by tile parity: in the light phase a fast warp may report tile s+1 before a slow
+        // one has reported tile s, and arrivals of two tiles must not mix in one phase)
+        if (ok) ok = mbar_wait(&bars[kBarDsFull + (s & 1)], (s >> 1) & 1, p.status, 122);  // dS_w in the S columns, dP read
+        if (!ok) break;
+        tc_fence_after();
+        if (s + 1 < n_dense) issue_dp(s + 1);
+        if (!ok) break;
+        if (s < n_dense) {  // dQ += dS_w K   (A from TMEM, K as MN-major operand)
+          const int ksl = q_of_k(s) % NS;
+          const uint32_t b_lo = dmn0.lo + (uint32_t)ksl * (TILE >> 4);
+          const uint32_t a0 = tmem + kQS + 128 * (s & 1);
+          mma_ts_x4(tmem + kQDQ, a0, b_lo, dmn0.hi, 2048 >> 4, idesc_q, (uint32_t)(s > 0));
+          mma_ts_x4(tmem + kQDQ, a0 + 64, b_lo + 4 * (2048 >> 4), dmn0.hi, 2048 >> 4, idesc_q, 1u);
+          mma_commit(&slot_free[ksl]);
+        }
       }
       mma_commit(&bars[kBarAllDone]);
       // finish: dQ += dTB r_time + dCB r_chan  (autograd through `_rel_bias`, `attentions/attn.py:1305-1314`);
@@ -343,10 +358,10 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
         tc_fence_after();
         const DescHalves dfr = make_desc_halves_sw128(smem_u32(ring + 65536), HALF, 1024);
         const DescHalves dfc = make_desc_halves_sw128(smem_u32(ring + 65536 + TILE), CP * 128, 1024);
-        mma_ts_x4(tmem + kColDQ, tmem + kColS, dfr.lo, dfr.hi, 2048 >> 4, idesc_q, 1u);
-        mma_ts_x4(tmem + kColDQ, tmem + kColS + 32, dfr.lo + 4 * (2048 >> 4), dfr.hi, 2048 >> 4, idesc_q, 1u);
+        mma_ts_x4(tmem + kQDQ, tmem + kQS, dfr.lo, dfr.hi, 2048 >> 4, idesc_q, 1u);
+        mma_ts_x4(tmem + kQDQ, tmem + kQS + 32, dfr.lo + 4 * (2048 >> 4), dfr.hi, 2048 >> 4, idesc_q, 1u);
 #pragma unroll
-        for (int kk = 0; kk < CP / 16; ++kk) mma_ts_h(tmem + kColDQ, tmem + kColDP + kk * 8, dfc, kk * 2048, idesc_q, 1u);
+        for (int kk = 0; kk < CP / 16; ++kk) mma_ts_h(tmem + kQDQ, tmem + kQDP + kk * 8, dfc, kk * 2048, idesc_q, 1u);
       }
       mma_commit(&bars[kBarFinDone]);
       BTRACE(30);
@@ -363,14 +378,14 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
         const DescHalves dqm = make_desc_halves_sw128(smem_u32(sQ), HALF, 1024);
         const DescHalves dones = make_desc_halves_sw128(smem_u32(ring + 32768), 16, 1024);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) mma_ss_h(tmem + kColTB, dtbt, kk * 2048, dqm, kk * 2048, idesc_r, kk > 0);
+        for (int kk = 0; kk < 8; ++kk) mma_ss_h(tmem + kQS1, dtbt, kk * 2048, dqm, kk * 2048, idesc_r, kk > 0);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) mma_ss_h(tmem + kColS, dcbt, kk * 2048, dqm, kk * 2048, idesc_r, kk > 0);
+        for (int kk = 0; kk < 8; ++kk) mma_ss_h(tmem + kQS, dcbt, kk * 2048, dqm, kk * 2048, idesc_r, kk > 0);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t offb = (kk / 4) * 2048 + (kk % 4) * 32;
-          mma_ss_h(tmem + kColDP, dtbt, kk * 2048, dones, offb, idesc_1, kk > 0);
-          mma_ss_h(tmem + kColDP + 16, dcbt, kk * 2048, dones, offb, idesc_1, kk > 0);
+          mma_ss_h(tmem + kQDP, dtbt, kk * 2048, dones, offb, idesc_1, kk > 0);
+          mma_ss_h(tmem + kQDP + 16, dcbt, kk * 2048, dones, offb, idesc_1, kk > 0);
         }
       }
       mma_commit(&bars[kBarRelDone]);
@@ -413,7 +428,7 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
 #pragma unroll 1
         for (int c8 = 0; c8 < 64; c8 += 8) {
           uint32_t v[8];
-          tmem_ld8(lane_base + kColTB + 64 * wg + c8, v);
+          tmem_ld8(lane_base + kQDQ + 64 * wg + c8, v);
           tmem_ld_wait();
           if (row_valid) {
 #pragma unroll
@@ -429,7 +444,7 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
 #pragma unroll 1
       for (int c8 = 8 * wg; c8 < CP; c8 += 16) {
         uint32_t v[8];
-        tmem_ld8(lane_base + kColS + c8, v);
+        tmem_ld8(lane_base + kQS + c8, v);
         tmem_ld_wait();
 #pragma unroll
         for (int e = 0; e < 8; ++e)
@@ -440,7 +455,8 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
     BTRACE(33);
     softmax_bar();
     BTRACE(34);
-    __half2 cbl[NCH / 2];
+    __half2 cbl[NCH / 2];  // channel scores relative to their maximum, log2 units (dense tiles)
+    __half2 bc[NCH / 2];   // exp2 of them (light tiles: P is an outer product, as in the forward)
     float mc = 0.f;
     {
       // gather by key channel slot: g_k = CB[i, C-1-|c_i - c_k|]; first the row maximum, then fp16 values
@@ -464,21 +480,29 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
       // loop stays short and the values still end up in registers
 #pragma unroll 1
       for (int k16 = 0; k16 < NCH; k16 += 16) {
-        uint32_t pk[8];
+        uint32_t pk[8], pb[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          const __half2 hh2 = __floats2half2_rn(gathered(k16 + 2 * e) - mc, gathered(k16 + 2 * e + 1) - mc);
+          const float x0 = gathered(k16 + 2 * e) - mc, x1 = gathered(k16 + 2 * e + 1) - mc;
+          const __half2 hh2 = __floats2half2_rn(x0, x1);
+          const __half2 eh2 = __floats2half2_rn(ex2(x0), ex2(x1));
           pk[e] = *reinterpret_cast<const uint32_t*>(&hh2);
+          pb[e] = *reinterpret_cast<const uint32_t*>(&eh2);
         }
-        tmem_st8(lane_base + kColDP + 32 * wg + k16 / 2, pk);
+        tmem_st8(lane_base + kQDP + 32 * wg + k16 / 2, pk);
+        tmem_st8(lane_base + kQDP + 64 + 32 * wg + k16 / 2, pb);
       }
       tmem_st_wait();
       {
         uint32_t w[32];
-        tmem_ld32(lane_base + kColDP + 32 * wg, w);
+        tmem_ld32(lane_base + kQDP + 32 * wg, w);
         tmem_ld_wait();
 #pragma unroll
         for (int k2 = 0; k2 < NCH / 2; ++k2) *reinterpret_cast<uint32_t*>(&cbl[k2]) = w[k2];
+        tmem_ld32(lane_base + kQDP + 64 + 32 * wg, w);
+        tmem_ld_wait();
+#pragma unroll
+        for (int k2 = 0; k2 < NCH / 2; ++k2) *reinterpret_cast<uint32_t*>(&bc[k2]) = w[k2];
       }
       tc_fence_before();
       uint4* dst = reinterpret_cast<uint4*>(p.cblw) + ((int64_t)bh * (CP / 8) + ck_base / 8) * N + n_loc;
@@ -518,59 +542,97 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
     for (int k = 0; k < NCH; ++k) dcb_acc[k] = 0.f;
     const float off_row = mc - L_i;  // every exponent carries +mc (cbl is relative to it) and -L
 
+    // Temporal scores of the row come back from the workspace (this CTA wrote them in the prologue; the
+    // barriers since then order the accesses): TPW values per tile, fetched one tile ahead.
+    const float* tb_src = p.tbw + (int64_t)bh * T * N + (row_valid ? n_loc : 0);
+    auto tb_slot = [&](int s, int tl) {
+      const int tk_abs = tile_of(s) * TPB + tt_base + tl;
+      return T - 1 - min(max(ti_abs - tk_abs, 0), T - 1);
+    };
+    float tb_next[TPW];
+#pragma unroll
+    for (int tl = 0; tl < TPW; ++tl) tb_next[tl] = ok ? __ldcg(tb_src + (int64_t)tb_slot(0, tl) * N) : 0.f;
+
+    // sm_scale is folded into the exponent: the loop works with P' = sm_scale * P, so dS = P' (dP - delta)
+    const float lscale = log2f(p.sm_scale);
     for (int s = 0; ok && s < n_tiles; ++s) {
       const bool dense = s < n_dense;
       const int J = tile_of(s);
-      ok = warp_wait(&bars[kBarSdpFull], s & 1, p.status, 132);
-      if (!ok) break;
-      if (s < 16) BTRACE(12 + s);
-      tc_fence_after();
-      // temporal scores of this thread's key time steps
       float offs[TPW], wmul[TPW], dtb_acc[TPW];
       int slot[TPW];
       bool valid[TPW];
-      {
-        uint32_t raw[TPW];
 #pragma unroll
-        for (int tl = 0; tl < TPW; ++tl) {
-          const int tk_abs = J * TPB + tt_base + tl, dt = ti_abs - tk_abs;
-          valid[tl] = dt >= 0 && tk_abs < T && row_valid;
-          slot[tl] = T - 1 - min(max(dt, 0), T - 1);
-          wmul[tl] = (p.window > 0 && dt > p.window && ti_abs != T - 1) ? 0.f : 1.f;
-          dtb_acc[tl] = 0.f;
-          tmem_ld1(lane_base + kColTB + slot[tl], raw[tl]);
-        }
-        tmem_ld_wait();
-#pragma unroll
-        for (int tl = 0; tl < TPW; ++tl)
-          offs[tl] = valid[tl] ? p.c2 * (__uint_as_float(raw[tl]) + s_vr[slot[tl]]) + off_row : -INFINITY;
+      for (int tl = 0; tl < TPW; ++tl) {
+        const int tk_abs = J * TPB + tt_base + tl, dt = ti_abs - tk_abs;
+        valid[tl] = dt >= 0 && tk_abs < T && row_valid;
+        slot[tl] = T - 1 - min(max(dt, 0), T - 1);
+        wmul[tl] = (p.window > 0 && dt > p.window && ti_abs != T - 1) ? 0.f : 1.f;
+        dtb_acc[tl] = 0.f;
+        offs[tl] = valid[tl] ? tb_next[tl] + off_row + lscale : -INFINITY;
       }
+      if (s + 1 < n_tiles) {
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t sv[32], dp[32];
-        if (dense) tmem_ld32(lane_base + kColS + 64 * wg + 32 * half, sv);
-        tmem_ld32(lane_base + kColDP + 64 * wg + 32 * half, dp);
-        tmem_ld_wait();
-        uint32_t pk[16];
-#pragma unroll
-        for (int jj = 0; jj < 32; jj += 2) {
-          const int lc = 32 * half + jj, tl = lc / CP, k = lc % NCH;
-          const float2 cb = __half22float2(cbl[k / 2]);
-          const float s0 = dense ? fmaf(__uint_as_float(sv[jj]), wmul[tl], cb.x) : cb.x;
-          const float s1 = dense ? fmaf(__uint_as_float(sv[jj + 1]), wmul[tl], cb.y) : cb.y;
-          const float p0 = ex2(s0 + offs[tl]), p1 = ex2(s1 + offs[tl]);
-          const float ds0 = p0 * (__uint_as_float(dp[jj]) - delta_i) * p.sm_scale;      // `attentions/attn.py:680`
-          const float ds1 = p1 * (__uint_as_float(dp[jj + 1]) - delta_i) * p.sm_scale;
-          dcb_acc[k] += ds0;
-          dcb_acc[k + 1] += ds1;
-          dtb_acc[tl] += ds0 + ds1;
-          pk[jj / 2] = pack_bf16(ds0 * wmul[tl], ds1 * wmul[tl]);  // content term only inside the window
-        }
-        if (dense) tmem_st16(lane_base + kColS + 64 * wg + 16 * half, pk);  // dS_w over consumed S columns
+        for (int tl = 0; tl < TPW; ++tl) tb_next[tl] = __ldcg(tb_src + (int64_t)tb_slot(s + 1, tl) * N);
       }
-      if (dense) tmem_st_wait();
+      if (dense) {
+        ok = warp_wait(&bars[kBarSFull + (s & 1)], (s >> 1) & 1, p.status, 132);
+        if (!ok) break;
+      }
+      ok = warp_wait(&bars[kBarDpFull + (s & 1)], (s >> 1) & 1, p.status, 133);
+      if (!ok) break;
+      if (s < 16) BTRACE(12 + s);
+      tc_fence_after();
+      if (dense) {
+        // P' = exp2(S2 - L + log2 sm_scale), dS = P' (dP - delta)   (`attentions/attn.py:680`)
+        const uint32_t s_addr = lane_base + kQS + 128 * (s & 1) + 64 * wg;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t sv[32], dp[32];
+          tmem_ld32(s_addr + 32 * half, sv);
+          tmem_ld32(lane_base + kQDP + 64 * wg + 32 * half, dp);
+          tmem_ld_wait();
+          uint32_t pk[16];
+#pragma unroll
+          for (int jj = 0; jj < 32; jj += 2) {
+            const int lc = 32 * half + jj, tl = lc / CP, k = lc % NCH;
+            const float2 cb = __half22float2(cbl[k / 2]);
+            const float p0 = ex2(fmaf(__uint_as_float(sv[jj]), wmul[tl], cb.x) + offs[tl]);
+            const float p1 = ex2(fmaf(__uint_as_float(sv[jj + 1]), wmul[tl], cb.y) + offs[tl]);
+            const float ds0 = p0 * (__uint_as_float(dp[jj]) - delta_i);
+            const float ds1 = p1 * (__uint_as_float(dp[jj + 1]) - delta_i);
+            dcb_acc[k] += ds0;
+            dcb_acc[k + 1] += ds1;
+            dtb_acc[tl] += ds0 + ds1;
+            const uint32_t both = pack_bf16(ds0, ds1);
+            pk[jj / 2] = wmul[tl] != 0.f ? both : 0u;  // content term only inside the window
+          }
+          tmem_st16(s_addr + 16 * half, pk);  // dS_w over this thread's consumed S columns
+        }
+        tmem_st_wait();
+      } else {
+        // outside the content window P' = a[t_k] bc[c_k]: one exponential per key time step
+        __half2 a2[TPW];
+#pragma unroll
+        for (int tl = 0; tl < TPW; ++tl) a2[tl] = __float2half2_rn(ex2(offs[tl]));
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t dp[32];
+          tmem_ld32(lane_base + kQS + 128 * (s & 1) + 64 * wg + 32 * half, dp);
+          tmem_ld_wait();
+#pragma unroll
+          for (int jj = 0; jj < 32; jj += 2) {
+            const int lc = 32 * half + jj, tl = lc / CP, k = lc % NCH;
+            const float2 pp = __half22float2(__hmul2(bc[k / 2], a2[tl]));
+            const float ds0 = pp.x * (__uint_as_float(dp[jj]) - delta_i);
+            const float ds1 = pp.y * (__uint_as_float(dp[jj + 1]) - delta_i);
+            dcb_acc[k] += ds0;
+            dcb_acc[k + 1] += ds1;
+            dtb_acc[tl] += ds0 + ds1;
+          }
+        }
+      }
       tc_fence_before();
-      mbar_arrive(&bars[kBarDsFull]);
+      mbar_arrive(&bars[kBarDsFull + (s & 1)]);
       // row sums per key time step; both warpgroups may own part of a time step (CP = 128)
 #pragma unroll
       for (int tl = 0; tl < TPW; ++tl)
@@ -588,7 +650,7 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
 #pragma unroll 1
       for (int c8 = 0; c8 < DW; c8 += 8) {
         uint32_t v[8];
-        tmem_ld8(lane_base + kColDQ + wg * DW + c8, v);
+        tmem_ld8(lane_base + kQDQ + wg * DW + c8, v);
         tmem_ld_wait();
 #pragma unroll
         for (int e = 0; e < 8; ++e)
@@ -619,7 +681,7 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
     }
     softmax_bar();
     BTRACE(42);
-    // dCB[i, j], j = C-1-e, e = |c_i - c_k|, as bf16 pairs: into TMEM columns kColDP + j/2 (A operand of
+    // dCB[i, j], j = C-1-e, e = |c_i - c_k|, as bf16 pairs: into TMEM columns kQDP + j/2 (A operand of
     // dQ += dCB r_chan) and into a shared-memory tile [row][j] (A operand, transposed, of the dr_chan product).
     // Each warpgroup takes half of the slots.
     uint8_t* s_cbt = D == 128 ? sDO : ring + 98304;  // dO is dead by now; at head_dim 64 the ring has room
@@ -639,7 +701,7 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
           vv[t2] = val;
         }
         const uint32_t pk2 = pack_bf16(vv[0], vv[1]);
-        tmem_st1(lane_base + kColDP + jb / 2 + m, pk2);
+        tmem_st1(lane_base + kQDP + jb / 2 + m, pk2);
         const int j = jb + 2 * m;
         *reinterpret_cast<uint32_t*>(s_cbt + (j >> 6) * HALF + row * 128 + ((((j & 63) >> 3) ^ (row & 7)) << 4) +
                                      (j & 7) * 2) = pk2;
@@ -667,7 +729,7 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
         uint32_t pk[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) pk[e] = pack_bf16(a[2 * e] * keep, a[2 * e + 1] * keep);
-        tmem_st8(lane_base + kColS + 32 * wg + m8, pk);
+        tmem_st8(lane_base + kQS + 32 * wg + m8, pk);
         const int c0 = m8 / 4;  // 16-byte chunks 2 m8/8 and the next one of this row's 128 bytes
         *reinterpret_cast<uint4*>(s_tbt + (((c0) ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
         *reinterpret_cast<uint4*>(s_tbt + (((c0 + 1) ^ (row & 7)) << 4)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
@@ -689,7 +751,7 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
 #pragma unroll 1
       for (int c0 = 0; c0 < DW; c0 += 32) {
         uint32_t v[32];
-        tmem_ld32(lane_base + kColDQ + wg * DW + c0, v);
+        tmem_ld32(lane_base + kQDQ + wg * DW + c0, v);
         tmem_ld_wait();
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
@@ -720,7 +782,7 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
       for (int which = 0; which < 2; ++which) {
         const bool jv = which == 0 ? j < T : j < C;
         float* acc = p.racc + (((size_t)hk * 2 + which) * D + wg * DW) * 128 + j;
-        const uint32_t col = which == 0 ? kColTB : kColS;
+        const uint32_t col = which == 0 ? kQS1 : kQS;
 #pragma unroll 1
         for (int c8 = 0; c8 < DW; c8 += 8) {
           uint32_t v[8];
@@ -733,7 +795,7 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
         }
         if (wg == which) {  // column sums: one warpgroup each
           uint32_t cs1;
-          tmem_ld1(lane_base + kColDP + 16 * which, cs1);
+          tmem_ld1(lane_base + kQDP + 16 * which, cs1);
           tmem_ld_wait();
           if (jv) atomicAdd(p.cacc + ((size_t)hk * 2 + which) * 128 + j, __uint_as_float(cs1));
         }

@@ -993,7 +993,7 @@ int launch(const Args& a, int* status, cudaStream_t s) {
   static_assert(smem <= 232448, "shared memory budget");
   static_assert(Cfg<D>::EARLY >= 2, "the first tile's K and V load while the prologue runs");
   MVPA_CUDA_CHECK(cudaFuncSetAttribute(tc_fwd_kernel<D, CP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  MVPA_CUDA_CHECK(cudaMemsetAsync(status, 0, sizeof(int), s));
+  MVPA_CUDA_CHECK(cudaMemsetAsync(status, 0, 256, s));
   rel_const_kernel<<<a.Hkv, 256, 0, s>>>(t.vt, t.z, (const __nv_bfloat16*)a.rt, (const __nv_bfloat16*)a.rc, relc, a.T,
                                         a.C, D);
   count_launch();

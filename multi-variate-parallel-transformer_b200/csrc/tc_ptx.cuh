@@ -62,7 +62,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
   }
-  if (status != nullptr) atomicCAS(status, 0, code);
+  if (status != nullptr) {
+    atomicCAS(status, 0, code);
+    status[(code % 100) & 63] = code;  // every wait that gave up, for diagnosis (the first word keeps the first)
+  }
   return false;
 }
 
@@ -92,7 +95,10 @@ __device__ __forceinline__ bool mbar_wait_a(uint32_t bar, uint32_t parity, int* 
         : "memory");
     if (ok) return true;
   }
-  if (status != nullptr) atomicCAS(status, 0, code);
+  if (status != nullptr) {
+    atomicCAS(status, 0, code);
+    status[(code % 100) & 63] = code;
+  }
   return false;
 }
 __device__ __forceinline__ void mma_commit_a(uint32_t bar) {

@@ -87,3 +87,28 @@ def test_oracle_on_rows_of_config2(cuda):
                              f(t["k"][:1, :1]), f(t["rt"][0, :1]), f(t["rc"][0, :1]), f(t["val"][:1, :1]),
                              D ** -0.5, row_chunk=512)
     assert np.abs(o - ref[0, 0]).max() <= 2e-2
+
+
+BWD_CASES = [(1, 16, 16, 128, 32, 64),   # config 3's shape, one batch element: several CTAs per SM in a row
+             (1, 4, 2, 128, 128, 128),   # 16k tokens, grouped heads, head_dim 128
+             (2, 4, 4, 64, 64, 64)]      # config 2's shape, two batch elements
+
+
+@pytest.mark.parametrize("cfg", BWD_CASES)
+def test_backward_tensor_core_vs_fp32_path_full_size(cuda, cfg):
+    """Backward at the benchmark shapes (many key tiles outside the content window, more CTAs than SMs):
+    all eight gradients of the bf16 tensor-core kernels against the fp32 CUDA-core kernels fed the same
+    bf16-rounded values; the latter are pinned to the oracle at small sizes in test_gpu_op.
+    Tolerance: 3e-2 of the largest magnitude of each gradient (bf16 operands, fp32 accumulation)."""
+    t = make(cuda, 5, *cfg)
+    gout = torch.randn(t["q"].shape, generator=torch.Generator().manual_seed(6)).to(torch.bfloat16).to(cuda)
+    grads = []
+    for dtype in (torch.bfloat16, torch.float32):
+        leaves = {n: x.to(dtype).detach().clone().requires_grad_(True) for n, x in t.items()}
+        run(leaves).backward(gout.to(dtype))
+        grads.append({n: x.grad.float() for n, x in leaves.items()})
+    torch.cuda.synchronize()
+    for n in grads[0]:
+        a, b = grads[0][n], grads[1][n]
+        assert torch.isfinite(a).all(), n
+        assert (a - b).abs().max() <= 3e-2 * b.abs().max() + 1e-6, (n, float((a - b).abs().max()), float(b.abs().max()))
