@@ -66,6 +66,7 @@ struct BqArgs {
   // per query row, kept for the key-side kernel (which visits every query tile many times):
   //   Q' = (q+u) c2 as (B*H, N, D) bf16, written through the `qp` tensor map
   __half* cblw;        // (B*H, CP/8, N, 8) channel scores gathered by key channel slot, relative to their max
+  __nv_bfloat16* bcw;  // same layout: exp2 of them (the key-side kernel's light pairs are outer products)
   float* offw;         // (B*H, N)     that max minus L
   float* tbw;          // (B*H, T, N)  temporal scores, log2 units
   int B, H, Hkv, T, C, g, window, n_qt;
@@ -104,6 +105,12 @@ __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, int* s
 }
 // All 256 softmax threads; only called outside data-dependent control flow.
 __device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
 
 __device__ __forceinline__ int light_tiles(int I, int TPB, int window, int n_qt) {
   if (window <= 0 || I == n_qt - 1) return 0;
@@ -491,6 +498,17 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
         }
         tmem_st8(lane_base + kQDP + 32 * wg + k16 / 2, pk);
         tmem_st8(lane_base + kQDP + 64 + 32 * wg + k16 / 2, pb);
+        if (ok && row_valid && (CP == 128 || wg == 0)) {  // bf16 copies for the key-side kernel
+          uint4* bdst = reinterpret_cast<uint4*>(p.bcw) + ((int64_t)bh * (CP / 8) + (ck_base + k16) / 8) * N + n_loc;
+          uint32_t wb[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&pb[e]));
+            wb[e] = pack_bf16(f.x, f.y);
+          }
+          bdst[0] = make_uint4(wb[0], wb[1], wb[2], wb[3]);
+          bdst[N] = make_uint4(wb[4], wb[5], wb[6], wb[7]);
+        }
       }
       tmem_st_wait();
       {
@@ -830,6 +848,7 @@ struct BkMaps {
 };
 struct BkArgs {
   const __half* cblw;
+  const __nv_bfloat16* bcw;
   const float *offw, *tbw, *delta;
   __nv_bfloat16 *dk, *dv;
   int64_t dk_sb, dk_sh, dk_sn, dv_sb, dv_sh, dv_sn;
@@ -837,7 +856,11 @@ struct BkArgs {
   float c2, sm_scale;
   int* status;
 };
-enum BkBarrier { kKvFull = 0, kQdoFull, kBkSdpFull, kPdsFull, kPairDone, kBkAllDone, kBkBars };
+enum BkBarrier {
+  kKvFull = 0, kQdoFull, kBkSdpFull, kPdsFull, kPairDone, kBkAllDone,
+  kLdoFull, kLdoFull1, kLpFull, kLpFull1, kLFree, kLFree1,  // light pairs: two dO / P buffers
+  kBkBars
+};
 
 template <int D>
 struct BkCfg {
@@ -877,11 +900,25 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
   const int J = (int)(blockIdx.x / BK);  // earliest key tiles (seen by the most query tiles) first
   const int bk = blockIdx.x % BK, b = bk / p.Hkv, hk = bk % p.Hkv;
   const int n_i = p.n_qt - J;            // query tiles J .. n_qt-1
-  const int n_pairs = p.g * n_i;
   const int T = p.T, C = p.C;
-  auto pair_is_light = [&](int i) {
-    if (p.window <= 0 || i == p.n_qt - 1) return false;
-    return i * TPB - (J * TPB + TPB - 1) > p.window;
+  // Query tile i is "light" for this key tile when every pair lies outside the content window:
+  //   (i - J) TPB - (TPB - 1) > window, except the last tile (its row t = T-1 sees everything).
+  // Dense pairs of all g heads come first, then the light ones: a light pair needs neither S, dP, dS nor
+  // dK (the content term is zero there), only dV += P^T dO with P = a[t_k] bc[c_k], so the light phase
+  // runs with two dO / P buffers (the Q' and dS areas are idle then) and is bound by its MMAs.
+  const int dl = p.window > 0 ? (p.window + TPB - 1) / TPB + 1 : n_i;  // first light offset i - J
+  const int n_lead = min(dl, n_i);                                      // dense tiles J .. J+n_lead-1
+  const int n_dense_i = n_lead + ((p.window > 0 && n_i > dl) ? 1 : 0);  // ... plus the last tile
+  const int n_light_i = n_i - n_dense_i;
+  const int n_dense = p.g * n_dense_i, n_light = p.g * n_light_i;
+  auto dense_pair = [&](int s, int& h, int& i) {
+    h = hk * p.g + s / n_dense_i;
+    const int e = s % n_dense_i;
+    i = e < n_lead ? J + e : p.n_qt - 1;
+  };
+  auto light_pair = [&](int l, int& h, int& i) {
+    h = hk * p.g + l / n_light_i;
+    i = J + dl + l % n_light_i;
   };
 
   if (tid == 0) {
@@ -892,6 +929,11 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
     mbar_init(&bars[kPdsFull], kSoftmaxThreads);
     mbar_init(&bars[kPairDone], 1);
     mbar_init(&bars[kBkAllDone], 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars[kLdoFull + i], 1);
+      mbar_init(&bars[kLpFull + i], kSoftmaxThreads);
+      mbar_init(&bars[kLFree + i], 1);
+    }
     mbar_fence_init();
   }
   __syncthreads();
@@ -917,8 +959,9 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
         tma_load_5d(sV + hh * HALF, &maps.v, &bars[kKvFull], hh * 64, 0, J * TPB, hk, b);
       }
       bool ok = true;
-      for (int s = 0; ok && s < n_pairs; ++s) {
-        const int h = hk * p.g + s / n_i, i = J + s % n_i;
+      for (int s = 0; ok && s < n_dense; ++s) {
+        int h, i;
+        dense_pair(s, h, i);
         if (s > 0) ok = mbar_wait(&bars[kPairDone], (s - 1) & 1, p.status, 210);  // Q'/dO buffers are free
         if (!ok) break;
         mbar_arrive_expect_tx(&bars[kQdoFull], 2 * TILE);
@@ -926,6 +969,19 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
           tma_load_5d(sQ + hh * HALF, &maps.qp, &bars[kQdoFull], hh * 64, 0, i * TPB, h, b);
           tma_load_5d(sDO + hh * HALF, &maps.dout, &bars[kQdoFull], hh * 64, 0, i * TPB, h, b);
         }
+      }
+      // light pairs: dO only, alternately into the dO and the (now idle) Q' area
+      if (ok && n_light > 0) ok = mbar_wait(&bars[kPairDone], (n_dense - 1) & 1, p.status, 211);
+      for (int l = 0; ok && l < n_light; ++l) {
+        int h, i;
+        light_pair(l, h, i);
+        const int bsel = l & 1;
+        if (l >= 2) ok = mbar_wait(&bars[kLFree + bsel], ((l >> 1) - 1) & 1, p.status, 212);
+        if (!ok) break;
+        uint8_t* dst = bsel == 0 ? sDO : sQ;
+        mbar_arrive_expect_tx(&bars[kLdoFull + bsel], TILE);
+        for (int hh = 0; hh < NH; ++hh)
+          tma_load_5d(dst + hh * HALF, &maps.dout, &bars[kLdoFull + bsel], hh * 64, 0, i * TPB, h, b);
       }
     }
   } else if (warp == 9) {
@@ -941,19 +997,14 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
       const DescHalves dpm = make_desc_halves_sw128(smem_u32(sP), HALF, 1024);
       const DescHalves ddsm = make_desc_halves_sw128(smem_u32(sDS), HALF, 1024);
       bool ok = mbar_wait(&bars[kKvFull], 0, p.status, 220);
-      bool dk_started = false;
-      for (int s = 0; ok && s < n_pairs; ++s) {
-        const int i = J + s % n_i;
-        const bool light = pair_is_light(i);
+      for (int s = 0; ok && s < n_dense; ++s) {
         ok = mbar_wait(&bars[kQdoFull], s & 1, p.status, 221);
         if (!ok) break;
         tc_fence_after();
-        if (!light) {
 #pragma unroll
-          for (int kk = 0; kk < KSTEPS; ++kk) {  // S = Q' K^T
-            const uint32_t off = (kk / 4) * HALF + (kk % 4) * 32;
-            mma_ss_h(tmem + kColS, dqk, off, dk, off, idesc_s, kk > 0);
-          }
+        for (int kk = 0; kk < KSTEPS; ++kk) {  // S = Q' K^T
+          const uint32_t off = (kk / 4) * HALF + (kk % 4) * 32;
+          mma_ss_h(tmem + kColS, dqk, off, dk, off, idesc_s, kk > 0);
         }
 #pragma unroll
         for (int kk = 0; kk < KSTEPS; ++kk) {  // dP = dO V^T
@@ -967,16 +1018,24 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)  // dV += P^T dO   (K = 128 query rows, 16 per step)
           mma_ss_h(tmem + kColDV, dpm, kk * 2048, ddom, kk * 2048, idesc_g, (s > 0 || kk > 0));
-        if (!light) {
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)  // dK += dS_w^T Q'
-            mma_ss_h(tmem + kColDK, ddsm, kk * 2048, dqm, kk * 2048, idesc_g, (dk_started || kk > 0));
-          dk_started = true;
-        }
+        for (int kk = 0; kk < 8; ++kk)  // dK += dS_w^T Q'
+          mma_ss_h(tmem + kColDK, ddsm, kk * 2048, dqm, kk * 2048, idesc_g, (s > 0 || kk > 0));
         mma_commit(&bars[kPairDone]);
       }
+      for (int l = 0; ok && l < n_light; ++l) {  // dV += P^T dO from the buffers of parity l & 1
+        const int bsel = l & 1;
+        ok = mbar_wait(&bars[kLdoFull + bsel], (l >> 1) & 1, p.status, 223);
+        if (ok) ok = mbar_wait(&bars[kLpFull + bsel], (l >> 1) & 1, p.status, 224);
+        if (!ok) break;
+        tc_fence_after();
+        const DescHalves ap = bsel == 0 ? dpm : ddsm;   // P buffers: the P and the dS areas
+        const DescHalves bd = bsel == 0 ? ddom : dqm;   // dO buffers: the dO and the Q' areas
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) mma_ss_h(tmem + kColDV, ap, kk * 2048, bd, kk * 2048, idesc_g, 1u);
+        mma_commit(&bars[kLFree + bsel]);
+      }
       mma_commit(&bars[kBkAllDone]);
-      if (!dk_started) {}  // (a key tile always has its diagonal pair, which is dense)
     }
   }
   } else {
@@ -988,9 +1047,9 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
     const int tt_base = (64 * wg) / CP;
     const int ck_base = CP == 128 ? 64 * wg : 0;
     bool ok = true;
-    for (int s = 0; ok && s < n_pairs; ++s) {
-      const int h = hk * p.g + s / n_i, i = J + s % n_i;
-      const bool light = pair_is_light(i);
+    for (int s = 0; ok && s < n_dense; ++s) {
+      int h, i;
+      dense_pair(s, h, i);
       const int ti_abs = i * TPB + ti_loc;
       const bool row_valid = c_i < C && ti_abs < T;
       const int N = T * C, n_loc = ti_abs * C + c_i;
@@ -1028,7 +1087,7 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint32_t sv[32], dp[32];
-        if (!light) tmem_ld32(lane_base + kColS + 64 * wg + 32 * half, sv);
+        tmem_ld32(lane_base + kColS + 64 * wg + 32 * half, sv);
         tmem_ld32(lane_base + kColDP + 64 * wg + 32 * half, dp);
         tmem_ld_wait();
         uint32_t pp[16], pd[16];
@@ -1036,8 +1095,8 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
         for (int jj = 0; jj < 32; jj += 2) {
           const int lc = 32 * half + jj, tl = lc / CP, k = lc % NCH;
           const float2 cb = __half22float2(cbl[k / 2]);
-          const float s0 = !light ? fmaf(__uint_as_float(sv[jj]), wmul[tl], cb.x) : cb.x;
-          const float s1 = !light ? fmaf(__uint_as_float(sv[jj + 1]), wmul[tl], cb.y) : cb.y;
+          const float s0 = fmaf(__uint_as_float(sv[jj]), wmul[tl], cb.x);
+          const float s1 = fmaf(__uint_as_float(sv[jj + 1]), wmul[tl], cb.y);
           const float p0 = ex2(s0 + offs[tl]), p1 = ex2(s1 + offs[tl]);
           const float ds0 = p0 * (__uint_as_float(dp[jj]) - delta_i) * p.sm_scale * wmul[tl];
           const float ds1 = p1 * (__uint_as_float(dp[jj + 1]) - delta_i) * p.sm_scale * wmul[tl];
@@ -1051,13 +1110,62 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
           const int c = 4 * half + c4;
           const uint32_t o = wg * HALF + row * 128 + ((c ^ (row & 7)) << 4);
           *reinterpret_cast<uint4*>(sP + o) = make_uint4(pp[4 * c4], pp[4 * c4 + 1], pp[4 * c4 + 2], pp[4 * c4 + 3]);
-          if (!light)
-            *reinterpret_cast<uint4*>(sDS + o) = make_uint4(pd[4 * c4], pd[4 * c4 + 1], pd[4 * c4 + 2], pd[4 * c4 + 3]);
+          *reinterpret_cast<uint4*>(sDS + o) = make_uint4(pd[4 * c4], pd[4 * c4 + 1], pd[4 * c4 + 2], pd[4 * c4 + 3]);
         }
       }
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(&bars[kPdsFull]);
+    }
+    // ---- light pairs: P[i, k] = a_i[t_k] bc_i[c_k] straight into the operand layout ----
+    if (ok && n_light > 0) ok = warp_wait(&bars[kPairDone], (n_dense - 1) & 1, p.status, 235);  // P / dS areas are free
+    for (int l = 0; ok && l < n_light; ++l) {
+      int h, i;
+      light_pair(l, h, i);
+      const int bsel = l & 1;
+      const int ti_abs = i * TPB + ti_loc;
+      const bool row_valid = c_i < C && ti_abs < T;
+      const int N = T * C, n_loc = ti_abs * C + c_i;
+      const int64_t bhq = (int64_t)b * p.H + h, n_row = bhq * N + n_loc;
+      uint32_t bcr[NCH / 2];  // exp2(channel score - max) of the row, bf16 pairs
+      uint32_t a2[TPW];
+      if (row_valid) {
+        const uint4* src = reinterpret_cast<const uint4*>(p.bcw) + (bhq * (CP / 8) + ck_base / 8) * N + n_loc;
+#pragma unroll
+        for (int m = 0; m < NCH / 8; ++m) {
+          const uint4 w = src[(int64_t)m * N];
+          bcr[4 * m] = w.x; bcr[4 * m + 1] = w.y; bcr[4 * m + 2] = w.z; bcr[4 * m + 3] = w.w;
+        }
+        const float off_row = p.offw[n_row];
+#pragma unroll
+        for (int tl = 0; tl < TPW; ++tl) {
+          const int tk_abs = J * TPB + tt_base + tl, dt = ti_abs - tk_abs;  // dt > window > 0 here
+          const float a = tk_abs < T ? ex2(p.tbw[(bhq * T + (T - 1 - dt)) * N + n_loc] + off_row) : 0.f;
+          a2[tl] = pack_bf16(a, a);
+        }
+      } else {
+#pragma unroll
+        for (int k2 = 0; k2 < NCH / 2; ++k2) bcr[k2] = 0u;
+#pragma unroll
+        for (int tl = 0; tl < TPW; ++tl) a2[tl] = 0u;
+      }
+      if (l >= 2) {
+        ok = warp_wait(&bars[kLFree + bsel], ((l >> 1) - 1) & 1, p.status, 236);
+        if (!ok) break;
+      }
+      uint8_t* dstP = bsel == 0 ? sP : sDS;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {  // 16-byte chunk c = key columns 8c .. 8c+7 of this warpgroup's 64
+        uint32_t w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int lc = 8 * c + 2 * e, tl = lc / CP, k = lc % NCH;
+          w[e] = mul_bf16x2(a2[tl], bcr[k / 2]);
+        }
+        *reinterpret_cast<uint4*>(dstP + wg * HALF + row * 128 + ((c ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(&bars[kLpFull + bsel]);
     }
     // ---- epilogue: lane = key row now ----
     if (ok) ok = warp_wait(&bars[kBkAllDone], 0, p.status, 234);
@@ -1118,7 +1226,7 @@ int launch_kv(const BwdArgs& bw, const BqArgs& q, const void* qp, cudaStream_t s
   if ((rc = enc5(&m.k, a.k, a.Hkv, a.k_sn, a.k_sh, a.k_sb))) return rc;
   if ((rc = enc5(&m.v, a.v, a.Hkv, a.v_sn, a.v_sh, a.v_sb))) return rc;
   BkArgs t;
-  t.cblw = q.cblw; t.offw = q.offw; t.tbw = q.tbw; t.delta = bw.delta;
+  t.cblw = q.cblw; t.bcw = q.bcw; t.offw = q.offw; t.tbw = q.tbw; t.delta = bw.delta;
   t.dk = (__nv_bfloat16*)bw.dk; t.dv = (__nv_bfloat16*)bw.dv;
   t.dk_sb = bw.dk_sb; t.dk_sh = bw.dk_sh; t.dk_sn = bw.dk_sn;
   t.dv_sb = bw.dv_sb; t.dv_sh = bw.dv_sh; t.dv_sn = bw.dv_sn;
@@ -1237,7 +1345,8 @@ int launch(const BwdArgs& bw, float* cs_dq, int* status, float* relc, float* rac
   {
     const size_t rows = (size_t)a.B * a.H * a.N;
     t.cblw = reinterpret_cast<__half*>(rows_ws + rows * (D / 2));
-    t.offw = rows_ws + rows * (D / 2) + rows * 64;
+    t.bcw = reinterpret_cast<__nv_bfloat16*>(rows_ws + rows * (D / 2) + rows * 64);
+    t.offw = rows_ws + rows * (D / 2) + rows * 128;
     t.tbw = t.offw + ((rows + 3) & ~(size_t)3);
   }
   t.B = a.B; t.H = a.H; t.Hkv = a.Hkv; t.T = a.T; t.C = a.C; t.g = a.g; t.window = a.window;
@@ -1285,7 +1394,7 @@ size_t tc_bwd_q_workspace_floats(const mvpa_problem* p) {
   // column sums + status + constants + per-row data for the key side (Q' bf16, channel scores fp16
   // padded to 128 slots, offset, temporal scores)
   size_t n = cs_dq_floats(p->B, p->H, p->T, p->D) + 64 + (size_t)p->Hkv * 256 +
-             (size_t)p->Hkv * (2 * p->D * 128 + 256) + rows * (p->D / 2) + rows * 64 +
+             (size_t)p->Hkv * (2 * p->D * 128 + 256) + rows * (p->D / 2) + rows * 128 +
              ((rows + 3) & ~(size_t)3) + rows * p->T + 64;
 #ifdef MVPA_TC_TRACE
   n = ((n + 63) & ~(size_t)63) + (size_t)p->B * p->H * p->T * 128;  // the timeline sits at the very end
