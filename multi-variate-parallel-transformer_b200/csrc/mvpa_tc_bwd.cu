@@ -93,7 +93,10 @@ struct Cfg {
   static constexpr int SMEM_DO = TILE;
   static constexpr int SMEM_RING = 2 * TILE;
   static constexpr int SMEM_PRO = SMEM_RING + EARLY * TILE;
-  static constexpr int SMEM_TAIL = SMEM_RING + NS * TILE;
+  // head_dim 64 leaves room for the tile's temporal-score gradients, [row][slot] as bf16 in the operand
+  // layout, through the whole main loop (used when every (row, slot) has a single owning thread)
+  static constexpr int SMEM_TBT = SMEM_RING + NS * TILE;
+  static constexpr int SMEM_TAIL = SMEM_TBT + (D == 64 ? 32768 : 0);
   // tail: u (D f32), vR[128], zC[128], smax[2][128], barriers, tmem slot, abort
   static constexpr int TAIL_FLOATS = D + 128 + 128 + 256;
   static constexpr int TAIL_BYTES = TAIL_FLOATS * 4 + (kBarSlotFull + 2 * NS) * 8 + 16;
@@ -154,6 +157,10 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
   // the prologue (the scaled scores are re-read from the workspace, tile by tile); the dr_time
   // accumulator of the epilogue takes the second S buffer.
   constexpr uint32_t kQS = 0, kQS1 = 128, kQDP = 256, kQDQ = 384;
+  // With at most 64 channel slots a key time step belongs to one warpgroup, so each (row, slot) sum of
+  // dS has one owner and goes straight into a shared-memory tile; otherwise the two owners add into the
+  // workspace with atomics and the tile is rebuilt from there after the loop.
+  constexpr bool TBS = (D == 64) && (CP <= 64);
   static_assert(CP >= 32 && CP <= 128 && (CP & (CP - 1)) == 0, "CP in {32,64,128}");
 
   extern __shared__ uint8_t smem_raw[];
@@ -164,6 +171,7 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
   uint8_t* sR = smem + C_::SMEM_PRO;
   uint8_t* sC = sR + TILE;
   float* scratch = reinterpret_cast<float*>(smem + C_::SMEM_PRO);  // [128][CP]
+  uint8_t* s_tbt_main = smem + C_::SMEM_TBT;
   float* s_bias = reinterpret_cast<float*>(smem + C_::SMEM_TAIL);  // u as fp32
   float* s_vr = s_bias + D;
   float* s_zc = s_vr + 128;
@@ -380,7 +388,7 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
       if (ok) {
         constexpr uint32_t idesc_r = make_idesc_bf16_ab(128, D, 1, 1);
         constexpr uint32_t idesc_1 = make_idesc_bf16_ab(128, 16, 1, 0);
-        const DescHalves dtbt = make_desc_halves_sw128(smem_u32(ring), HALF, 1024);
+        const DescHalves dtbt = make_desc_halves_sw128(smem_u32(TBS ? s_tbt_main : ring), HALF, 1024);
         const DescHalves dcbt = make_desc_halves_sw128(smem_u32(D == 128 ? sDO : ring + 98304), HALF, 1024);
         const DescHalves dqm = make_desc_halves_sw128(smem_u32(sQ), HALF, 1024);
         const DescHalves dones = make_desc_halves_sw128(smem_u32(ring + 32768), 16, 1024);
@@ -417,6 +425,10 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const int tt_base = (64 * wg) / CP;
     const int ck_base = CP == 128 ? 64 * wg : 0;
+    if constexpr (TBS) {  // slots no key tile reaches stay zero
+#pragma unroll
+      for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(s_tbt_main + tid * 128 + c * 16) = make_uint4(0u, 0u, 0u, 0u);
+    }
     for (int d = tid; d < D; d += kSoftmaxThreads) s_bias[d] = __bfloat162float(p.u[hk * D + d]);
     s_vr[tid] = p.relc[hk * 256 + tid];  // s_vr and s_zc are adjacent: 256 floats
     // L = +inf on rows that do not exist: their P is 0 everywhere
@@ -653,8 +665,18 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
       mbar_arrive(&bars[kBarDsFull + (s & 1)]);
       // row sums per key time step; both warpgroups may own part of a time step (CP = 128)
 #pragma unroll
-      for (int tl = 0; tl < TPW; ++tl)
-        if (valid[tl]) atomicAdd(&p.dtb[((int64_t)bh * T + slot[tl]) * N + n_loc], dtb_acc[tl]);
+      for (int tl = 0; tl < TPW; ++tl) {
+        if (valid[tl]) {
+          if constexpr (TBS) {
+            const int sl = slot[tl];
+            *reinterpret_cast<__nv_bfloat16*>(s_tbt_main + (sl >> 6) * HALF + row * 128 +
+                                              ((((sl & 63) >> 3) ^ (row & 7)) << 4) + (sl & 7) * 2) =
+                __float2bfloat16_rn(dtb_acc[tl]);
+          } else {
+            atomicAdd(&p.dtb[((int64_t)bh * T + slot[tl]) * N + n_loc], dtb_acc[tl]);
+          }
+        }
+      }
     }
     // ------------------------------- epilogue ---------------------------------
     BTRACE(3);
@@ -677,11 +699,14 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
     }
     BTRACE(5);
     softmax_bar();
-    if (row < DW) {  // fixed summation order: deterministic
-      float sum = 0.f;
-#pragma unroll 4
-      for (int r = 0; r < 128; ++r) sum += cs[(wg * 128 + r) * DW + ((row + r) & (DW - 1))];
-      p.cs_dq[(size_t)blockIdx.x * D + wg * DW + row] = sum;
+    if (row < DW) {  // fixed summation order: deterministic; four chains hide the shared-memory latency
+      float s4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 2
+      for (int r = 0; r < 128; r += 4) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s4[e] += cs[(wg * 128 + r + e) * DW + ((row + r + e) & (DW - 1))];
+      }
+      p.cs_dq[(size_t)blockIdx.x * D + wg * DW + row] = (s4[0] + s4[1]) + (s4[2] + s4[3]);
     }
     softmax_bar();
     BTRACE(6);
@@ -711,12 +736,11 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
 #pragma unroll
         for (int t2 = 0; t2 < 2; ++t2) {
           const int j = jb + 2 * m + t2, e = C - 1 - j;
-          float val = 0.f;
-          if (row_valid && e >= 0) {
-            if (c_i - e >= 0) val += sc[row * CP + ((c_i - e + 2 * row) & (CP - 1))];
-            if (e > 0 && c_i + e < C) val += sc[row * CP + ((c_i + e + 2 * row) & (CP - 1))];
-          }
-          vv[t2] = val;
+          // both candidates are read from wrapped (always valid) positions and masked: no divergence
+          const float lo = sc[row * CP + ((c_i - e + 2 * row) & (CP - 1))];
+          const float hi = sc[row * CP + ((c_i + e + 2 * row) & (CP - 1))];
+          const bool on = row_valid && e >= 0;
+          vv[t2] = ((on && c_i - e >= 0) ? lo : 0.f) + ((on && e > 0 && c_i + e < C) ? hi : 0.f);
         }
         const uint32_t pk2 = pack_bf16(vv[0], vv[1]);
         tmem_st1(lane_base + kQDP + jb / 2 + m, pk2);
@@ -727,31 +751,42 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
     }
     BTRACE(43);
     BTRACE(7);
-    __threadfence();  // this CTA's atomic row sums in dtb are complete before anyone re-reads them
+    if constexpr (!TBS) __threadfence();  // this CTA's atomic row sums in dtb are complete before anyone re-reads them
     softmax_bar();
     BTRACE(8);
     if (ok) {
       // dTB of the row (this thread's 64 of the 128 r_time rows) as bf16 pairs: A operand of dQ += dTB r_time
-      // in TMEM, and the [row][j] tile in shared memory for the dr_time product (the scatter area is dead)
-      const float* src = p.dtb + ((int64_t)bh * T + 64 * wg) * N + (row_valid ? n_loc : 0);
-      const float keep = row_valid ? 1.f : 0.f;
-      uint8_t* s_tbt = ring + wg * HALF + row * 128;
-#pragma unroll 1
-      for (int m8 = 0; m8 < 32; m8 += 8) {
-        float a[16];
+      // in TMEM, and the [row][j] tile in shared memory for the dr_time product
+      if constexpr (TBS) {
+        const uint8_t* my = s_tbt_main + wg * HALF + row * 128;
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          const int jl = 2 * m8 + e;
-          a[e] = (64 * wg + jl < T) ? __ldcg(src + (int64_t)jl * N) : 0.f;
+        for (int m8 = 0; m8 < 32; m8 += 8) {
+          const uint4 w0 = *reinterpret_cast<const uint4*>(my + (((m8 / 4) ^ (row & 7)) << 4));
+          const uint4 w1 = *reinterpret_cast<const uint4*>(my + (((m8 / 4 + 1) ^ (row & 7)) << 4));
+          const uint32_t pk[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+          if (m8 == 0) BTRACE(46);
+          tmem_st8(lane_base + kQS + 32 * wg + m8, pk);
         }
-        uint32_t pk[8];
+      } else {
+        const float* src = p.dtb + ((int64_t)bh * T + 64 * wg) * N + (row_valid ? n_loc : 0);
+        const float keep = row_valid ? 1.f : 0.f;
+        uint8_t* s_tbt = ring + wg * HALF + row * 128;  // (the scatter area is dead)
+        float a[64];  // every load in flight at once
 #pragma unroll
-        for (int e = 0; e < 8; ++e) pk[e] = pack_bf16(a[2 * e] * keep, a[2 * e + 1] * keep);
-        tmem_st8(lane_base + kQS + 32 * wg + m8, pk);
-        const int c0 = m8 / 4;  // 16-byte chunks 2 m8/8 and the next one of this row's 128 bytes
-        *reinterpret_cast<uint4*>(s_tbt + (((c0) ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-        *reinterpret_cast<uint4*>(s_tbt + (((c0 + 1) ^ (row & 7)) << 4)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+        for (int jl = 0; jl < 64; ++jl) a[jl] = (64 * wg + jl < T) ? __ldcg(src + (int64_t)jl * N) : 0.f;
+#pragma unroll
+        for (int m8 = 0; m8 < 32; m8 += 8) {
+          uint32_t pk[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) pk[e] = pack_bf16(a[2 * (m8 + e)] * keep, a[2 * (m8 + e) + 1] * keep);
+          if (m8 == 0) BTRACE(46);
+          tmem_st8(lane_base + kQS + 32 * wg + m8, pk);
+          const int c0 = m8 / 4;  // 16-byte chunks c0 and c0 + 1 of this row's 128 bytes
+          *reinterpret_cast<uint4*>(s_tbt + (((c0) ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          *reinterpret_cast<uint4*>(s_tbt + (((c0 + 1) ^ (row & 7)) << 4)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+        }
       }
+      BTRACE(47);
       // a [16 x 128] tile of ones (K-major): column sums of dTB / dCB come out of the tensor core too
       *reinterpret_cast<uint4*>(ring + 32768 + tid * 16) = make_uint4(0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u);
       fence_proxy_async_smem();
@@ -1369,7 +1404,8 @@ int launch(const BwdArgs& bw, float* cs_dq, int* status, float* relc, float* rac
   MVPA_CUDA_CHECK(cudaFuncSetAttribute(tc_bwd_q_kernel<D, CP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   MVPA_CUDA_CHECK(cudaMemsetAsync(status, 0, 256, s));
   MVPA_CUDA_CHECK(cudaMemsetAsync(racc, 0, sizeof(float) * (size_t)a.Hkv * (2 * D * 128 + 256), s));
-  MVPA_CUDA_CHECK(cudaMemsetAsync(bw.dtbg, 0, sizeof(float) * (size_t)a.B * a.H * a.N * a.T, s));
+  if (!(D == 64 && CP <= 64))  // (the kernel keeps these sums in shared memory otherwise)
+    MVPA_CUDA_CHECK(cudaMemsetAsync(bw.dtbg, 0, sizeof(float) * (size_t)a.B * a.H * a.N * a.T, s));
   rel_const_kernel<<<a.Hkv, 256, 0, s>>>((const __nv_bfloat16*)a.vt, (const __nv_bfloat16*)a.z,
                                         (const __nv_bfloat16*)a.rt, (const __nv_bfloat16*)a.rc, relc, a.T, a.C, D);
   const unsigned grid = (unsigned)t.n_qt * a.B * a.H;
