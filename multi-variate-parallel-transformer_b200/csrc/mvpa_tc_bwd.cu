@@ -1153,37 +1153,48 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
       mbar_arrive(&bars[kPdsFull]);
     }
     // ---- light pairs: P[i, k] = a_i[t_k] bc_i[c_k] straight into the operand layout ----
+    // The row's data of pair l+1 is requested while pair l is processed: with nothing else to wait for,
+    // the latency of these loads would otherwise be the whole cost of a light pair.
     if (ok && n_light > 0) ok = warp_wait(&bars[kPairDone], (n_dense - 1) & 1, p.status, 235);  // P / dS areas are free
+    uint4 nbc[NCH / 8];
+    float ntb[TPW], noff = 0.f;
+    auto light_fetch = [&](int l) {
+      int h, i;
+      light_pair(l, h, i);
+      const int ti_abs = i * TPB + ti_loc;
+      const bool row_valid = c_i < C && ti_abs < T;
+      const int N = T * C, n_loc = row_valid ? ti_abs * C + c_i : 0;
+      const int64_t bhq = (int64_t)b * p.H + h;
+      const uint4* src = reinterpret_cast<const uint4*>(p.bcw) + (bhq * (CP / 8) + ck_base / 8) * N + n_loc;
+#pragma unroll
+      for (int m = 0; m < NCH / 8; ++m) nbc[m] = src[(int64_t)m * N];
+      noff = p.offw[bhq * N + n_loc];
+#pragma unroll
+      for (int tl = 0; tl < TPW; ++tl) {
+        const int dt = min(max(ti_abs - (J * TPB + tt_base + tl), 0), T - 1);
+        ntb[tl] = p.tbw[(bhq * T + (T - 1 - dt)) * N + n_loc];
+      }
+    };
+    if (ok && n_light > 0) light_fetch(0);
     for (int l = 0; ok && l < n_light; ++l) {
       int h, i;
       light_pair(l, h, i);
       const int bsel = l & 1;
       const int ti_abs = i * TPB + ti_loc;
       const bool row_valid = c_i < C && ti_abs < T;
-      const int N = T * C, n_loc = ti_abs * C + c_i;
-      const int64_t bhq = (int64_t)b * p.H + h, n_row = bhq * N + n_loc;
       uint32_t bcr[NCH / 2];  // exp2(channel score - max) of the row, bf16 pairs
       uint32_t a2[TPW];
-      if (row_valid) {
-        const uint4* src = reinterpret_cast<const uint4*>(p.bcw) + (bhq * (CP / 8) + ck_base / 8) * N + n_loc;
 #pragma unroll
-        for (int m = 0; m < NCH / 8; ++m) {
-          const uint4 w = src[(int64_t)m * N];
-          bcr[4 * m] = w.x; bcr[4 * m + 1] = w.y; bcr[4 * m + 2] = w.z; bcr[4 * m + 3] = w.w;
-        }
-        const float off_row = p.offw[n_row];
-#pragma unroll
-        for (int tl = 0; tl < TPW; ++tl) {
-          const int tk_abs = J * TPB + tt_base + tl, dt = ti_abs - tk_abs;  // dt > window > 0 here
-          const float a = tk_abs < T ? ex2(p.tbw[(bhq * T + (T - 1 - dt)) * N + n_loc] + off_row) : 0.f;
-          a2[tl] = pack_bf16(a, a);
-        }
-      } else {
-#pragma unroll
-        for (int k2 = 0; k2 < NCH / 2; ++k2) bcr[k2] = 0u;
-#pragma unroll
-        for (int tl = 0; tl < TPW; ++tl) a2[tl] = 0u;
+      for (int m = 0; m < NCH / 8; ++m) {
+        bcr[4 * m] = nbc[m].x; bcr[4 * m + 1] = nbc[m].y; bcr[4 * m + 2] = nbc[m].z; bcr[4 * m + 3] = nbc[m].w;
       }
+#pragma unroll
+      for (int tl = 0; tl < TPW; ++tl) {
+        const int tk_abs = J * TPB + tt_base + tl;  // (t_i - t_k > window > 0 here)
+        const float a = (row_valid && tk_abs < T) ? ex2(ntb[tl] + noff) : 0.f;
+        a2[tl] = pack_bf16(a, a);
+      }
+      if (l + 1 < n_light) light_fetch(l + 1);
       if (l >= 2) {
         ok = warp_wait(&bars[kLFree + bsel], ((l >> 1) - 1) & 1, p.status, 236);
         if (!ok) break;
