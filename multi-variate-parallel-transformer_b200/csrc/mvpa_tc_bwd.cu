@@ -892,7 +892,7 @@ struct BkArgs {
   int* status;
 };
 enum BkBarrier {
-  kKvFull = 0, kQdoFull, kBkSdpFull, kPdsFull, kPairDone, kBkAllDone,
+  kKvFull = 0, kQdoFull, kQdoFull1, kBkSdpFull, kPdsFull, kPairDone, kBkAllDone,
   kLdoFull, kLdoFull1, kLpFull, kLpFull1, kLFree, kLFree1,  // light pairs: two dO / P buffers
   kBkBars
 };
@@ -902,7 +902,11 @@ struct BkCfg {
   static constexpr int TILE = (D / 64) * 16384;
   static constexpr int SMEM_K = 0, SMEM_V = TILE, SMEM_Q = 2 * TILE, SMEM_DO = 3 * TILE;
   static constexpr int SMEM_P = 4 * TILE, SMEM_DS = 4 * TILE + 32768;
-  static constexpr int SMEM_TAIL = 4 * TILE + 65536;
+  // head_dim 64 has room for a second Q' / dO pair: the loads of the next dense pair and its S / dP
+  // products then overlap the softmax work and the dV / dK products of the current one
+  static constexpr int NSET = D == 64 ? 2 : 1;
+  static constexpr int SMEM_QDO1 = 4 * TILE + 65536;
+  static constexpr int SMEM_TAIL = SMEM_QDO1 + (NSET - 1) * 2 * TILE;
   static constexpr int SMEM_BYTES = SMEM_TAIL + kBkBars * 8 + 16 + 1024;
 };
 
@@ -924,6 +928,9 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
   uint8_t* sV = smem + C_::SMEM_V;
   uint8_t* sQ = smem + C_::SMEM_Q;
   uint8_t* sDO = smem + C_::SMEM_DO;
+  constexpr int NSET = C_::NSET;
+  uint8_t* sQ1 = smem + C_::SMEM_QDO1;  // second set (head_dim 64 only)
+  uint8_t* sDO1 = sQ1 + TILE;
   uint8_t* sP = smem + C_::SMEM_P;
   uint8_t* sDS = smem + C_::SMEM_DS;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C_::SMEM_TAIL);
@@ -960,6 +967,7 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
     *s_abort = *p.status;
     mbar_init(&bars[kKvFull], 1);
     mbar_init(&bars[kQdoFull], 1);
+    mbar_init(&bars[kQdoFull + 1], 1);
     mbar_init(&bars[kBkSdpFull], 1);
     mbar_init(&bars[kPdsFull], kSoftmaxThreads);
     mbar_init(&bars[kPairDone], 1);
@@ -997,15 +1005,22 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
       for (int s = 0; ok && s < n_dense; ++s) {
         int h, i;
         dense_pair(s, h, i);
-        if (s > 0) ok = mbar_wait(&bars[kPairDone], (s - 1) & 1, p.status, 210);  // Q'/dO buffers are free
+        const int set = s % NSET;
+        if (s >= NSET) ok = mbar_wait(&bars[kPairDone], (s - NSET) & 1, p.status, 210);  // the set's buffers are free
         if (!ok) break;
-        mbar_arrive_expect_tx(&bars[kQdoFull], 2 * TILE);
+        uint8_t* dq_ = set == 0 ? sQ : sQ1;
+        uint8_t* ddo_ = set == 0 ? sDO : sDO1;
+        mbar_arrive_expect_tx(&bars[kQdoFull + set], 2 * TILE);
         for (int hh = 0; hh < NH; ++hh) {
-          tma_load_5d(sQ + hh * HALF, &maps.qp, &bars[kQdoFull], hh * 64, 0, i * TPB, h, b);
-          tma_load_5d(sDO + hh * HALF, &maps.dout, &bars[kQdoFull], hh * 64, 0, i * TPB, h, b);
+          tma_load_5d(dq_ + hh * HALF, &maps.qp, &bars[kQdoFull + set], hh * 64, 0, i * TPB, h, b);
+          tma_load_5d(ddo_ + hh * HALF, &maps.dout, &bars[kQdoFull + set], hh * 64, 0, i * TPB, h, b);
         }
       }
       // light pairs: dO only, alternately into the dO and the (now idle) Q' area
+      // (a parity wait can only tell the current phase from the one before it: the phases are waited for
+      // one by one, none skipped)
+      if (ok && n_light > 0 && NSET == 2 && n_dense >= 2)
+        ok = mbar_wait(&bars[kPairDone], (n_dense - 2) & 1, p.status, 211);
       if (ok && n_light > 0) ok = mbar_wait(&bars[kPairDone], (n_dense - 1) & 1, p.status, 211);
       for (int l = 0; ok && l < n_light; ++l) {
         int h, i;
@@ -1032,31 +1047,47 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
       const DescHalves dpm = make_desc_halves_sw128(smem_u32(sP), HALF, 1024);
       const DescHalves ddsm = make_desc_halves_sw128(smem_u32(sDS), HALF, 1024);
       bool ok = mbar_wait(&bars[kKvFull], 0, p.status, 220);
-      for (int s = 0; ok && s < n_dense; ++s) {
-        ok = mbar_wait(&bars[kQdoFull], s & 1, p.status, 221);
-        if (!ok) break;
+      const uint32_t set1 = (uint32_t)(C_::SMEM_QDO1 - C_::SMEM_Q) >> 4;  // descriptor distance to the second set
+      auto issue_sdp = [&](int s) {  // S = Q' K^T, dP = dO V^T of dense pair s
+        const int set = s % NSET;
+        ok = mbar_wait(&bars[kQdoFull + set], (s / NSET) & 1, p.status, 221);
+        if (!ok) return;
         tc_fence_after();
+        DescHalves a_q = dqk, a_do = ddok;
+        a_q.lo += set * set1;
+        a_do.lo += set * set1;
 #pragma unroll
-        for (int kk = 0; kk < KSTEPS; ++kk) {  // S = Q' K^T
+        for (int kk = 0; kk < KSTEPS; ++kk) {
           const uint32_t off = (kk / 4) * HALF + (kk % 4) * 32;
-          mma_ss_h(tmem + kColS, dqk, off, dk, off, idesc_s, kk > 0);
+          mma_ss_h(tmem + kColS, a_q, off, dk, off, idesc_s, kk > 0);
         }
 #pragma unroll
-        for (int kk = 0; kk < KSTEPS; ++kk) {  // dP = dO V^T
+        for (int kk = 0; kk < KSTEPS; ++kk) {
           const uint32_t off = (kk / 4) * HALF + (kk % 4) * 32;
-          mma_ss_h(tmem + kColDP, ddok, off, dv, off, idesc_s, kk > 0);
+          mma_ss_h(tmem + kColDP, a_do, off, dv, off, idesc_s, kk > 0);
         }
         mma_commit(&bars[kBkSdpFull]);
-        ok = mbar_wait(&bars[kPdsFull], s & 1, p.status, 222);  // P / dS_w are in shared memory
+      };
+      if (ok && n_dense > 0) issue_sdp(0);
+      for (int s = 0; ok && s < n_dense; ++s) {
+        const int set = s % NSET;
+        ok = mbar_wait(&bars[kPdsFull], s & 1, p.status, 222);  // P / dS_w are in shared memory, S / dP consumed
         if (!ok) break;
         tc_fence_after();
+        // with a second buffer set the next pair's S / dP go first: the softmax warps wait for them
+        if (NSET == 2 && s + 1 < n_dense) issue_sdp(s + 1);
+        if (!ok) break;
+        DescHalves b_do = ddom, b_q = dqm;
+        b_do.lo += set * set1;
+        b_q.lo += set * set1;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)  // dV += P^T dO   (K = 128 query rows, 16 per step)
-          mma_ss_h(tmem + kColDV, dpm, kk * 2048, ddom, kk * 2048, idesc_g, (s > 0 || kk > 0));
+          mma_ss_h(tmem + kColDV, dpm, kk * 2048, b_do, kk * 2048, idesc_g, (s > 0 || kk > 0));
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)  // dK += dS_w^T Q'
-          mma_ss_h(tmem + kColDK, ddsm, kk * 2048, dqm, kk * 2048, idesc_g, (s > 0 || kk > 0));
+          mma_ss_h(tmem + kColDK, ddsm, kk * 2048, b_q, kk * 2048, idesc_g, (s > 0 || kk > 0));
         mma_commit(&bars[kPairDone]);
+        if (NSET == 1 && s + 1 < n_dense) issue_sdp(s + 1);
       }
       for (int l = 0; ok && l < n_light; ++l) {  // dV += P^T dO from the buffers of parity l & 1
         const int bsel = l & 1;
@@ -1108,12 +1139,13 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
 #pragma unroll
         for (int k2 = 0; k2 < NCH / 2; ++k2) cbl[k2] = __floats2half2_rn(0.f, 0.f);
       }
-      float offs[TPW], wmul[TPW];
+      float offs[TPW], wmul[TPW], scw[TPW];
 #pragma unroll
       for (int tl = 0; tl < TPW; ++tl) {
         const int tk_abs = J * TPB + tt_base + tl, dt = ti_abs - tk_abs;
         const bool valid = dt >= 0 && tk_abs < T && row_valid;
         wmul[tl] = (p.window > 0 && dt > p.window && ti_abs != T - 1) ? 0.f : 1.f;
+        scw[tl] = wmul[tl] * p.sm_scale;  // dS_w = P (dP - delta) sm_scale inside the window, 0 outside
         offs[tl] = valid ? p.tbw[(bhq * T + (T - 1 - dt)) * N + n_loc] + off_row : -INFINITY;
       }
       ok = warp_wait(&bars[kBkSdpFull], s & 1, p.status, 232);
@@ -1133,10 +1165,16 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
           const float s0 = fmaf(__uint_as_float(sv[jj]), wmul[tl], cb.x);
           const float s1 = fmaf(__uint_as_float(sv[jj + 1]), wmul[tl], cb.y);
           const float p0 = ex2(s0 + offs[tl]), p1 = ex2(s1 + offs[tl]);
-          const float ds0 = p0 * (__uint_as_float(dp[jj]) - delta_i) * p.sm_scale * wmul[tl];
-          const float ds1 = p1 * (__uint_as_float(dp[jj + 1]) - delta_i) * p.sm_scale * wmul[tl];
+          const float ds0 = p0 * (__uint_as_float(dp[jj]) - delta_i) * scw[tl];
+          const float ds1 = p1 * (__uint_as_float(dp[jj + 1]) - delta_i) * scw[tl];
           pp[jj / 2] = pack_bf16(p0, p1);
           pd[jj / 2] = pack_bf16(ds0, ds1);
+        }
+        // (with two buffer sets these warps run ahead of the previous pair's dV / dK products, which
+        // still read the P / dS areas)
+        if (NSET == 2 && half == 0 && s > 0) {
+          ok = warp_wait(&bars[kPairDone], (s - 1) & 1, p.status, 233);
+          if (!ok) break;
         }
         // MN-major operand layout: 64-key block = this warpgroup, one 128-byte row per query row,
         // 16-byte chunks swizzled by (row mod 8)
