@@ -890,10 +890,12 @@ struct BkArgs {
   int B, H, Hkv, T, C, g, window, n_qt;
   float c2, sm_scale;
   int* status;
+  long long* trace;
 };
 enum BkBarrier {
   kKvFull = 0, kQdoFull, kQdoFull1, kBkSdpFull, kPdsFull, kPairDone, kBkAllDone,
-  kLdoFull, kLdoFull1, kLpFull, kLpFull1, kLFree, kLFree1,  // light pairs: two dO / P buffers
+  kLdoFull, kLdoFull1, kLdoFull2, kLdoFull3, kLdoFree, kLdoFree1, kLdoFree2, kLdoFree3,  // light pairs: four dO buffers
+  kLpFull, kLpFull1, kLFree, kLFree1,                                                      // ... and two P buffers
   kBkBars
 };
 
@@ -972,8 +974,11 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
     mbar_init(&bars[kPdsFull], kSoftmaxThreads);
     mbar_init(&bars[kPairDone], 1);
     mbar_init(&bars[kBkAllDone], 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < 4; ++i) {
       mbar_init(&bars[kLdoFull + i], 1);
+      mbar_init(&bars[kLdoFree + i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(&bars[kLpFull + i], kSoftmaxThreads);
       mbar_init(&bars[kLFree + i], 1);
     }
@@ -1022,13 +1027,15 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
       if (ok && n_light > 0 && NSET == 2 && n_dense >= 2)
         ok = mbar_wait(&bars[kPairDone], (n_dense - 2) & 1, p.status, 211);
       if (ok && n_light > 0) ok = mbar_wait(&bars[kPairDone], (n_dense - 1) & 1, p.status, 211);
+      // Four dO buffers in the light phase: the dO, Q', K and V areas (K and V are dead once the dense pairs
+      // are done).  The loads run far enough ahead to cover the TMA latency.
       for (int l = 0; ok && l < n_light; ++l) {
         int h, i;
         light_pair(l, h, i);
-        const int bsel = l & 1;
-        if (l >= 2) ok = mbar_wait(&bars[kLFree + bsel], ((l >> 1) - 1) & 1, p.status, 212);
+        const int bsel = l & 3;
+        if (l >= 4) ok = mbar_wait(&bars[kLdoFree + bsel], ((l >> 2) - 1) & 1, p.status, 212);
         if (!ok) break;
-        uint8_t* dst = bsel == 0 ? sDO : sQ;
+        uint8_t* dst = bsel == 0 ? sDO : bsel == 1 ? sQ : bsel == 2 ? sK : sV;
         mbar_arrive_expect_tx(&bars[kLdoFull + bsel], TILE);
         for (int hh = 0; hh < NH; ++hh)
           tma_load_5d(dst + hh * HALF, &maps.dout, &bars[kLdoFull + bsel], hh * 64, 0, i * TPB, h, b);
@@ -1089,17 +1096,20 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
         mma_commit(&bars[kPairDone]);
         if (NSET == 1 && s + 1 < n_dense) issue_sdp(s + 1);
       }
-      for (int l = 0; ok && l < n_light; ++l) {  // dV += P^T dO from the buffers of parity l & 1
-        const int bsel = l & 1;
-        ok = mbar_wait(&bars[kLdoFull + bsel], (l >> 1) & 1, p.status, 223);
+      const DescHalves dkm = make_desc_halves_sw128(smem_u32(sK), HALF, 1024);  // K / V areas as dO buffers
+      const DescHalves dvm = make_desc_halves_sw128(smem_u32(sV), HALF, 1024);
+      for (int l = 0; ok && l < n_light; ++l) {  // dV += P^T dO
+        const int bsel = l & 1, dsel = l & 3;
+        ok = mbar_wait(&bars[kLdoFull + dsel], (l >> 2) & 1, p.status, 223);
         if (ok) ok = mbar_wait(&bars[kLpFull + bsel], (l >> 1) & 1, p.status, 224);
         if (!ok) break;
         tc_fence_after();
         const DescHalves ap = bsel == 0 ? dpm : ddsm;   // P buffers: the P and the dS areas
-        const DescHalves bd = bsel == 0 ? ddom : dqm;   // dO buffers: the dO and the Q' areas
+        const DescHalves bd = dsel == 0 ? ddom : dsel == 1 ? dqm : dsel == 2 ? dkm : dvm;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) mma_ss_h(tmem + kColDV, ap, kk * 2048, bd, kk * 2048, idesc_g, 1u);
         mma_commit(&bars[kLFree + bsel]);
+        mma_commit(&bars[kLdoFree + dsel]);
       }
       mma_commit(&bars[kBkAllDone]);
     }
@@ -1113,9 +1123,14 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
     const int tt_base = (64 * wg) / CP;
     const int ck_base = CP == 128 ? 64 * wg : 0;
     bool ok = true;
+#ifdef MVPA_TC_TRACE
+    const bool trace_on = tid == 0;
+#endif
+    BTRACE(0);
     for (int s = 0; ok && s < n_dense; ++s) {
       int h, i;
       dense_pair(s, h, i);
+      if (s < 8) BTRACE(8 + 4 * s);
       const int ti_abs = i * TPB + ti_loc;
       const bool row_valid = c_i < C && ti_abs < T;
       const int N = T * C, n_loc = ti_abs * C + c_i;
@@ -1150,6 +1165,7 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
       }
       ok = warp_wait(&bars[kBkSdpFull], s & 1, p.status, 232);
       if (!ok) break;
+      if (s < 8) BTRACE(9 + 4 * s);
       tc_fence_after();
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
@@ -1189,7 +1205,9 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(&bars[kPdsFull]);
+      if (s < 8) BTRACE(10 + 4 * s);
     }
+    BTRACE(1);
     // ---- light pairs: P[i, k] = a_i[t_k] bc_i[c_k] straight into the operand layout ----
     // The row's data of pair l+1 is requested while pair l is processed: with nothing else to wait for,
     // the latency of these loads would otherwise be the whole cost of a light pair.
@@ -1250,9 +1268,12 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
       }
       fence_proxy_async_smem();
       mbar_arrive(&bars[kLpFull + bsel]);
+      if (l < 16) BTRACE(40 + l);
     }
+    BTRACE(2);
     // ---- epilogue: lane = key row now ----
     if (ok) ok = warp_wait(&bars[kBkAllDone], 0, p.status, 234);
+    BTRACE(3);
     if (ok) {
       tc_fence_after();
       const int tk_abs = J * TPB + ti_loc;
@@ -1283,6 +1304,7 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
         }
       }
     }
+    BTRACE(4);
     tc_fence_before();
   }
   __syncthreads();
@@ -1316,6 +1338,7 @@ int launch_kv(const BwdArgs& bw, const BqArgs& q, const void* qp, cudaStream_t s
   t.dv_sb = bw.dv_sb; t.dv_sh = bw.dv_sh; t.dv_sn = bw.dv_sn;
   t.B = a.B; t.H = a.H; t.Hkv = a.Hkv; t.T = a.T; t.C = a.C; t.g = a.g; t.window = a.window;
   t.n_qt = q.n_qt; t.c2 = a.c2; t.sm_scale = a.sm_scale; t.status = q.status;
+  t.trace = q.trace == nullptr ? nullptr : q.trace + (size_t)64 * a.B * a.H * a.T;
   constexpr int smem = BkCfg<D>::SMEM_BYTES;
   static_assert(smem <= 232448, "shared memory budget");
   MVPA_CUDA_CHECK(cudaFuncSetAttribute(tc_bwd_kv_kernel<D, CP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -1443,8 +1466,8 @@ int launch(const BwdArgs& bw, float* cs_dq, int* status, float* relc, float* rac
   {
     mvpa_problem pr{};
     pr.B = a.B; pr.H = a.H; pr.Hkv = a.Hkv; pr.T = a.T; pr.C = a.C; pr.D = a.D;
-    t.trace = reinterpret_cast<long long*>(cs_dq + tc_bwd_q_workspace_floats(&pr) - (size_t)a.B * a.H * a.T * 128);
-    MVPA_CUDA_CHECK(cudaMemsetAsync(t.trace, 0, sizeof(long long) * 64 * (size_t)a.B * a.H * t.n_qt, s));
+    t.trace = reinterpret_cast<long long*>(cs_dq + tc_bwd_q_workspace_floats(&pr) - (size_t)a.B * a.H * a.T * 256);
+    MVPA_CUDA_CHECK(cudaMemsetAsync(t.trace, 0, sizeof(long long) * 128 * (size_t)a.B * a.H * a.T, s));
   }
 #endif
   constexpr int smem = Cfg<D>::SMEM_BYTES;
@@ -1482,7 +1505,7 @@ size_t tc_bwd_q_workspace_floats(const mvpa_problem* p) {
              (size_t)p->Hkv * (2 * p->D * 128 + 256) + rows * (p->D / 2) + rows * 128 +
              ((rows + 3) & ~(size_t)3) + rows * p->T + 64;
 #ifdef MVPA_TC_TRACE
-  n = ((n + 63) & ~(size_t)63) + (size_t)p->B * p->H * p->T * 128;  // the timeline sits at the very end
+  n = ((n + 63) & ~(size_t)63) + (size_t)p->B * p->H * p->T * 256;  // the timelines (query side, key side) sit at the very end
 #endif
   return n;
 }

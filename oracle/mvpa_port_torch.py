@@ -8,7 +8,7 @@ It performs the same sequence of dense operations as
 matmuls, two gathers, window zero-fill, scaling, time-block causal mask,
 softmax over a materialised (N,N) matrix and the PV matmul — so its run time on
 the host cores stands in for the reference's CPU path, which cannot be
-imported where `/root/reference` is absent.  Index maps are built in closed
+imported where the reference checkout is absent.  Index maps are built in closed
 form instead of by the reference's pad-and-reshape.
 """
 from __future__ import annotations

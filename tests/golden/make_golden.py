@@ -18,7 +18,7 @@ from types import SimpleNamespace as NS
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MVPA_REFERENCE_DIR", "reference")
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.modules.setdefault("loralib", types.ModuleType("loralib"))
 sys.path.insert(0, REF)
