@@ -188,10 +188,14 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
   const int bh = blockIdx.x % BH, b = bh / p.H, h = bh % p.H, hk = h / p.g;
   const int n_tiles = I + 1;
   const int n_light = light_tiles(I, TPB, p.window, p.n_qt);
-  const int n_dense = n_tiles - n_light;
-  auto tile_of = [&](int s) { return s < n_dense ? n_light + s : s - n_dense; };
-  auto q_of_k = [&](int s) { return 2 * s; };
-  auto q_of_v = [&](int s) { return s < n_dense ? 2 * s + 1 : n_dense + s; };
+  // Visit order: the light tiles 0 .. n_light-1 first, then the dense ones (natural key order).  In the
+  // light phase the channel-score gradient is accumulated unscaled (see the softmax warps) and folded
+  // into the ordinary accumulators at the transition, so it must come first.
+  auto tile_of = [&](int s) { return s; };
+  auto is_dense = [&](int s) { return s >= n_light; };
+  // position of a tile's K / V in the load sequence (a light tile loads V only)
+  auto q_of_k = [&](int s) { return n_light + 2 * (s - n_light); };
+  auto q_of_v = [&](int s) { return s < n_light ? s : n_light + 2 * (s - n_light) + 1; };
   const int T = p.T, C = p.C;
 
   if (tid == 0) {
@@ -256,7 +260,7 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
       };
       for (int s = 0; ok && s < n_tiles; ++s) {
         const int J = tile_of(s);
-        if (s < n_dense) load_slot(&maps.k, q_of_k(s), J);
+        if (is_dense(s)) load_slot(&maps.k, q_of_k(s), J);
         if (ok) load_slot(&maps.v, q_of_v(s), J);
       }
       // finish: the relative keys once more (the ring is idle once every product has completed)
@@ -332,29 +336,30 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
         for (int kk = 0; kk < KSTEPS; ++kk) {  // dP = dO V^T  (V rows = keys, D contiguous: K-major operand)
           const uint32_t off = (kk / 4) * HALF + (kk % 4) * 32;
           // a light tile has no score product: its dP takes the idle S buffer, so two are in flight
-          mma_ss_h(tmem + (s < n_dense ? kQDP : kQS + 128 * (s & 1)), ddo, off, dv, off, idesc_s, kk > 0);
+          mma_ss_h(tmem + (is_dense(s) ? kQDP : kQS + 128 * (s & 1)), ddo, off, dv, off, idesc_s, kk > 0);
         }
         mma_commit(&bars[kBarDpFull + (s & 1)]);
         mma_commit(&slot_free[vsl]);
       };
-      if (ok) issue_s(0);  // the newest key tile is always dense
+      if (ok && is_dense(0)) issue_s(0);
       if (ok) issue_dp(0);
       for (int s = 0; ok && s < n_tiles; ++s) {
-        if (s + 1 < n_dense) issue_s(s + 1);
+        const bool next = s + 1 < n_tiles, next_dense = next && is_dense(s + 1);
         // (S buffer (s+1)&1 is free: tile s-1 left it when its dS / dP was consumed)
-        if (ok && s + 1 >= n_dense && s + 1 < n_tiles) issue_dp(s + 1);
+        if (next_dense) issue_s(s + 1);
+        if (ok && next && !next_dense) issue_dp(s + 1);
         // (two barriers, by tile parity: in the light phase a fast warp may report tile s+1 before a slow
         // one has reported tile s, and arrivals of two tiles must not mix in one phase)
         if (ok) ok = mbar_wait(&bars[kBarDsFull + (s & 1)], (s >> 1) & 1, p.status, 122);  // dS_w in the S columns, dP read
         if (!ok) break;
         tc_fence_after();
-        if (s + 1 < n_dense) issue_dp(s + 1);
+        if (next_dense) issue_dp(s + 1);
         if (!ok) break;
-        if (s < n_dense) {  // dQ += dS_w K   (A from TMEM, K as MN-major operand)
+        if (is_dense(s)) {  // dQ += dS_w K   (A from TMEM, K as MN-major operand)
           const int ksl = q_of_k(s) % NS;
           const uint32_t b_lo = dmn0.lo + (uint32_t)ksl * (TILE >> 4);
           const uint32_t a0 = tmem + kQS + 128 * (s & 1);
-          mma_ts_x4(tmem + kQDQ, a0, b_lo, dmn0.hi, 2048 >> 4, idesc_q, (uint32_t)(s > 0));
+          mma_ts_x4(tmem + kQDQ, a0, b_lo, dmn0.hi, 2048 >> 4, idesc_q, (uint32_t)(s > n_light));
           mma_ts_x4(tmem + kQDQ, a0 + 64, b_lo + 4 * (2048 >> 4), dmn0.hi, 2048 >> 4, idesc_q, 1u);
           mma_commit(&slot_free[ksl]);
         }
@@ -474,8 +479,6 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
     BTRACE(33);
     softmax_bar();
     BTRACE(34);
-    __half2 cbl[NCH / 2];  // channel scores relative to their maximum, log2 units (dense tiles)
-    __half2 bc[NCH / 2];   // exp2 of them (light tiles: P is an outer product, as in the forward)
     float mc = 0.f;
     {
       // gather by key channel slot: g_k = CB[i, C-1-|c_i - c_k|]; first the row maximum, then fp16 values
@@ -510,39 +513,25 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
         }
         tmem_st8(lane_base + kQDP + 32 * wg + k16 / 2, pk);
         tmem_st8(lane_base + kQDP + 64 + 32 * wg + k16 / 2, pb);
-        if (ok && row_valid && (CP == 128 || wg == 0)) {  // bf16 copies for the key-side kernel
-          uint4* bdst = reinterpret_cast<uint4*>(p.bcw) + ((int64_t)bh * (CP / 8) + (ck_base + k16) / 8) * N + n_loc;
+        if (ok && row_valid && (CP == 128 || wg == 0)) {  // copies for the key-side kernel (exponentials as bf16)
+          const int64_t chunk = ((int64_t)bh * (CP / 8) + (ck_base + k16) / 8) * N + n_loc;
+          uint4* cdst = reinterpret_cast<uint4*>(p.cblw) + chunk;
+          uint4* bdst = reinterpret_cast<uint4*>(p.bcw) + chunk;
           uint32_t wb[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
             const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&pb[e]));
             wb[e] = pack_bf16(f.x, f.y);
           }
+          cdst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          cdst[N] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
           bdst[0] = make_uint4(wb[0], wb[1], wb[2], wb[3]);
           bdst[N] = make_uint4(wb[4], wb[5], wb[6], wb[7]);
         }
       }
-      tmem_st_wait();
-      {
-        uint32_t w[32];
-        tmem_ld32(lane_base + kQDP + 32 * wg, w);
-        tmem_ld_wait();
-#pragma unroll
-        for (int k2 = 0; k2 < NCH / 2; ++k2) *reinterpret_cast<uint32_t*>(&cbl[k2]) = w[k2];
-        tmem_ld32(lane_base + kQDP + 64 + 32 * wg, w);
-        tmem_ld_wait();
-#pragma unroll
-        for (int k2 = 0; k2 < NCH / 2; ++k2) *reinterpret_cast<uint32_t*>(&bc[k2]) = w[k2];
-      }
+      tmem_st_wait();  // the staged values are read back where they are needed (light phase: bc; dense phase: cbl)
       tc_fence_before();
-      uint4* dst = reinterpret_cast<uint4*>(p.cblw) + ((int64_t)bh * (CP / 8) + ck_base / 8) * N + n_loc;
       const bool store_cbl = ok && row_valid && (CP == 128 || wg == 0);
-      if (store_cbl) {
-#pragma unroll
-        for (int m = 0; m < NCH / 8; ++m)
-          dst[(int64_t)m * N] = make_uint4(*reinterpret_cast<uint32_t*>(&cbl[4 * m]), *reinterpret_cast<uint32_t*>(&cbl[4 * m + 1]),
-                                           *reinterpret_cast<uint32_t*>(&cbl[4 * m + 2]), *reinterpret_cast<uint32_t*>(&cbl[4 * m + 3]));
-      }
       if (store_cbl && wg == 0) p.offw[n_row] = mc - L_i;
       BTRACE(37);
       if (ok) {
@@ -563,8 +552,6 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
         fence_proxy_async_smem();
       }
     }
-    mbar_arrive(&bars[kBarProDone]);
-    BTRACE(2);
 
     // gradient of the channel scores, per channel slot of this thread's columns (summed over time)
     float dcb_acc[NCH];
@@ -585,8 +572,43 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
 
     // sm_scale is folded into the exponent: the loop works with P' = sm_scale * P, so dS = P' (dP - delta)
     const float lscale = log2f(p.sm_scale);
+    // The gathered channel scores (fp16, dense tiles) and their exponentials (light tiles) wait in this
+    // thread's lane of the dP columns, which no MMA touches before the first dense tile.
+    __half2 cbl[NCH / 2];
+    auto load_cbl = [&]() {
+      uint32_t w[32];
+      tmem_ld32(lane_base + kQDP + 32 * wg, w);
+      tmem_ld_wait();
+#pragma unroll
+      for (int k2 = 0; k2 < NCH / 2; ++k2) *reinterpret_cast<uint32_t*>(&cbl[k2]) = w[k2];
+    };
+    // Light tiles: P'[i,k] = a[t_k] bc[c_k] with a = exp2(temporal score + max - L + log2 sm_scale), so
+    //   sum_t dS = bc[c_k] (sum_t a[t] dP[t, c_k] - delta sum_t a[t])        -> two FMAs per element:
+    //   sum_c dS = a[t] (sum_c bc[c] dP[t, c] - delta sum_c bc[c])
+    // dcb_acc holds the inner sums until the transition below scales them.
+    float bcf[NCH];
+    float a_sum = 0.f, bc_sum = 0.f;
+    if (n_light > 0) {
+      uint32_t w[32];
+      tmem_ld32(lane_base + kQDP + 64 + 32 * wg, w);
+      tmem_ld_wait();
+#pragma unroll
+      for (int k2 = 0; k2 < NCH / 2; ++k2) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[k2]));
+        bcf[2 * k2] = f.x;
+        bcf[2 * k2 + 1] = f.y;
+        bc_sum += f.x + f.y;
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < NCH; ++k) bcf[k] = 0.f;
+      load_cbl();
+    }
+    tc_fence_before();
+    mbar_arrive(&bars[kBarProDone]);  // only now may a dP product overwrite the staged values
+    BTRACE(2);
     for (int s = 0; ok && s < n_tiles; ++s) {
-      const bool dense = s < n_dense;
+      const bool dense = is_dense(s);
       const int J = tile_of(s);
       float offs[TPW], wmul[TPW], dtb_acc[TPW];
       int slot[TPW];
@@ -605,7 +627,7 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
         for (int tl = 0; tl < TPW; ++tl) tb_next[tl] = __ldcg(tb_src + (int64_t)tb_slot(s + 1, tl) * N);
       }
       if (dense) {
-        ok = warp_wait(&bars[kBarSFull + (s & 1)], (s >> 1) & 1, p.status, 132);
+        ok = warp_wait(&bars[kBarSFull + (s & 1)], ((s - n_light) >> 1) & 1, p.status, 132);
         if (!ok) break;
       }
       ok = warp_wait(&bars[kBarDpFull + (s & 1)], (s >> 1) & 1, p.status, 133);
@@ -640,10 +662,14 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
         }
         tmem_st_wait();
       } else {
-        // outside the content window P' = a[t_k] bc[c_k]: one exponential per key time step
-        __half2 a2[TPW];
+        float a[TPW], w0[TPW], w1[TPW];
 #pragma unroll
-        for (int tl = 0; tl < TPW; ++tl) a2[tl] = __float2half2_rn(ex2(offs[tl]));
+        for (int tl = 0; tl < TPW; ++tl) {
+          a[tl] = ex2(offs[tl]);  // 0 where the time step is not visible
+          a_sum += a[tl];
+          w0[tl] = 0.f;
+          w1[tl] = 0.f;
+        }
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           uint32_t dp[32];
@@ -652,13 +678,21 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
 #pragma unroll
           for (int jj = 0; jj < 32; jj += 2) {
             const int lc = 32 * half + jj, tl = lc / CP, k = lc % NCH;
-            const float2 pp = __half22float2(__hmul2(bc[k / 2], a2[tl]));
-            const float ds0 = pp.x * (__uint_as_float(dp[jj]) - delta_i);
-            const float ds1 = pp.y * (__uint_as_float(dp[jj + 1]) - delta_i);
-            dcb_acc[k] += ds0;
-            dcb_acc[k + 1] += ds1;
-            dtb_acc[tl] += ds0 + ds1;
+            const float d0 = __uint_as_float(dp[jj]), d1 = __uint_as_float(dp[jj + 1]);
+            dcb_acc[k] = fmaf(a[tl], d0, dcb_acc[k]);
+            dcb_acc[k + 1] = fmaf(a[tl], d1, dcb_acc[k + 1]);
+            w0[tl] = fmaf(bcf[k], d0, w0[tl]);
+            w1[tl] = fmaf(bcf[k + 1], d1, w1[tl]);
           }
+        }
+#pragma unroll
+        for (int tl = 0; tl < TPW; ++tl) dtb_acc[tl] = a[tl] * (w0[tl] + w1[tl] - delta_i * bc_sum);
+        if (s == n_light - 1) {
+          // transition: scale the light phase's inner sums, then fetch the scores the dense tiles need
+          // (before the report below lets the first dense dP product overwrite where they wait)
+#pragma unroll
+          for (int k = 0; k < NCH; ++k) dcb_acc[k] = bcf[k] * (dcb_acc[k] - delta_i * a_sum);
+          load_cbl();
         }
       }
       tc_fence_before();
