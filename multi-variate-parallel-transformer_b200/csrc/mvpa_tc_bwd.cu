@@ -1246,9 +1246,14 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
     // The row's data of pair l+1 is requested while pair l is processed: with nothing else to wait for,
     // the latency of these loads would otherwise be the whole cost of a light pair.
     if (ok && n_light > 0) ok = warp_wait(&bars[kPairDone], (n_dense - 1) & 1, p.status, 235);  // P / dS areas are free
-    uint4 nbc[NCH / 8];
-    float ntb[TPW], noff = 0.f;
-    auto light_fetch = [&](int l) {
+    // Two register stages: the row's data of pair l+2 is requested while pair l is processed (one pair
+    // ahead does not cover the latency of these loads once a pair takes about a thousand cycles).
+    struct RowData {
+      uint4 bc[NCH / 8];
+      float tb[TPW];
+      float off;
+    };
+    auto light_fetch = [&](int l, RowData& r) {
       int h, i;
       light_pair(l, h, i);
       const int ti_abs = i * TPB + ti_loc;
@@ -1257,16 +1262,16 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
       const int64_t bhq = (int64_t)b * p.H + h;
       const uint4* src = reinterpret_cast<const uint4*>(p.bcw) + (bhq * (CP / 8) + ck_base / 8) * N + n_loc;
 #pragma unroll
-      for (int m = 0; m < NCH / 8; ++m) nbc[m] = src[(int64_t)m * N];
-      noff = p.offw[bhq * N + n_loc];
+      for (int m = 0; m < NCH / 8; ++m) r.bc[m] = src[(int64_t)m * N];
+      r.off = p.offw[bhq * N + n_loc];
 #pragma unroll
       for (int tl = 0; tl < TPW; ++tl) {
         const int dt = min(max(ti_abs - (J * TPB + tt_base + tl), 0), T - 1);
-        ntb[tl] = p.tbw[(bhq * T + (T - 1 - dt)) * N + n_loc];
+        r.tb[tl] = p.tbw[(bhq * T + (T - 1 - dt)) * N + n_loc];
       }
     };
-    if (ok && n_light > 0) light_fetch(0);
-    for (int l = 0; ok && l < n_light; ++l) {
+    auto light_body = [&](int l, RowData& r) {
+      if (l >= 4 && l < 8) BTRACE(20 + 4 * (l - 4));
       int h, i;
       light_pair(l, h, i);
       const int bsel = l & 1;
@@ -1276,19 +1281,21 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
       uint32_t a2[TPW];
 #pragma unroll
       for (int m = 0; m < NCH / 8; ++m) {
-        bcr[4 * m] = nbc[m].x; bcr[4 * m + 1] = nbc[m].y; bcr[4 * m + 2] = nbc[m].z; bcr[4 * m + 3] = nbc[m].w;
+        bcr[4 * m] = r.bc[m].x; bcr[4 * m + 1] = r.bc[m].y; bcr[4 * m + 2] = r.bc[m].z; bcr[4 * m + 3] = r.bc[m].w;
       }
 #pragma unroll
       for (int tl = 0; tl < TPW; ++tl) {
         const int tk_abs = J * TPB + tt_base + tl;  // (t_i - t_k > window > 0 here)
-        const float a = (row_valid && tk_abs < T) ? ex2(ntb[tl] + noff) : 0.f;
+        const float a = (row_valid && tk_abs < T) ? ex2(r.tb[tl] + r.off) : 0.f;
         a2[tl] = pack_bf16(a, a);
       }
-      if (l + 1 < n_light) light_fetch(l + 1);
+      if (l >= 4 && l < 8) BTRACE(21 + 4 * (l - 4));
+      if (l + 2 < n_light) light_fetch(l + 2, r);  // this stage's registers are free again
       if (l >= 2) {
         ok = warp_wait(&bars[kLFree + bsel], ((l >> 1) - 1) & 1, p.status, 236);
-        if (!ok) break;
+        if (!ok) return;
       }
+      if (l >= 4 && l < 8) BTRACE(22 + 4 * (l - 4));
       uint8_t* dstP = bsel == 0 ? sP : sDS;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {  // 16-byte chunk c = key columns 8c .. 8c+7 of this warpgroup's 64
@@ -1303,6 +1310,13 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
       fence_proxy_async_smem();
       mbar_arrive(&bars[kLpFull + bsel]);
       if (l < 16) BTRACE(40 + l);
+    };
+    RowData r0, r1;
+    if (ok && n_light > 0) light_fetch(0, r0);
+    if (ok && n_light > 1) light_fetch(1, r1);
+    for (int l = 0; ok && l < n_light; l += 2) {
+      light_body(l, r0);
+      if (ok && l + 1 < n_light) light_body(l + 1, r1);
     }
     BTRACE(2);
     // ---- epilogue: lane = key row now ----
