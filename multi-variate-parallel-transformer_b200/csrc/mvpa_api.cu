@@ -193,8 +193,7 @@ int mvpa_bwd(const mvpa_problem* p, const mvpa_tensor* q, const mvpa_tensor* k, 
   b.dk = dk->ptr; b.dk_sb = dk->stride_b; b.dk_sh = dk->stride_h; b.dk_sn = dk->stride_n;
   b.dv = dv->ptr; b.dv_sb = dv->stride_b; b.dv_sh = dv->stride_h; b.dv_sn = dv->stride_n;
   b.du = du; b.dvt = dvt; b.dz = dz; b.drt = dr_time; b.drc = dr_chan;
-  simt_bwd_carve(b, (float*)workspace);
-  if (!(p->dtype == MVPA_BF16 && tc_bwd_q_supported(b.a))) b.tc_extra = nullptr;
+  simt_bwd_carve(b, (float*)workspace, p->dtype);
   return simt_bwd(b, p->dtype, (cudaStream_t)cuda_stream);
 }
 

@@ -53,7 +53,7 @@ void count_launch(int n = 1);
 int simt_fwd(const Args& a, int dtype, cudaStream_t s);
 int simt_bwd(const BwdArgs& b, int dtype, cudaStream_t s);
 size_t simt_bwd_workspace_floats(const mvpa_problem* p);
-void simt_bwd_carve(BwdArgs& b, float* ws);
+void simt_bwd_carve(BwdArgs& b, float* ws, int dtype);
 
 // tcgen05 / TMEM / TMA forward for bf16 (mvpa_tc_fwd.cu).
 bool tc_fwd_supported(const Args& a);

@@ -765,19 +765,42 @@ int simt_bwd(const BwdArgs& b, int dtype, cudaStream_t s) {
   return dtype == MVPA_F32 ? dispatch_bwd<float>(b, s) : dispatch_bwd<__nv_bfloat16>(b, s);
 }
 
+namespace {
+// bf16 problems the tensor-core backward takes need only delta and (when two threads own a temporal
+// slot) the temporal-score gradients from this file's areas; everything else lives in tc_extra.
+bool tc_path(int dtype, int D, int C, int T) {
+  Args a{};
+  a.D = D; a.C = C; a.T = T;
+  return dtype == MVPA_BF16 && tc_bwd_q_supported(a);
+}
+bool tc_needs_dtb(int D, int C) { return !(D == 64 && C <= 64); }
+}  // namespace
+
 size_t simt_bwd_workspace_floats(const mvpa_problem* p) {
   const size_t BH = (size_t)p->B * p->H, N = (size_t)p->T * p->C;
+  if (tc_path(p->dtype, p->D, p->C, p->T)) {
+    size_t n = BH * N + (tc_needs_dtb(p->D, p->C) ? BH * N * p->T : 0);
+    n = (n + 63) & ~(size_t)63;
+    return n + tc_bwd_q_workspace_floats(p);
+  }
   const size_t n_qt = (N + kBM - 1) / kBM;
   size_t n = 2 * BH * N * (p->T + p->C) + BH * N + BH * n_qt * 3 * p->D +
              (size_t)kDrelSplit * p->Hkv * (p->T + p->C) * p->D;
-  n = (n + 63) & ~(size_t)63;  // keep what follows 256-byte aligned
-  if (p->dtype == MVPA_BF16) n += tc_bwd_q_workspace_floats(p);
-  return n;
+  return (n + 63) & ~(size_t)63;
 }
 
-void simt_bwd_carve(BwdArgs& b, float* ws) {
+void simt_bwd_carve(BwdArgs& b, float* ws, int dtype) {
   const Args& a = b.a;
   const size_t BH = (size_t)a.B * a.H, N = a.N;
+  if (tc_path(dtype, a.D, a.C, a.T)) {
+    b.tbg = b.cbg = b.dcbg = b.partial = b.drel_part = nullptr;
+    b.delta = ws;
+    b.dtbg = ws + BH * N;  // (B*H, T, N) scratch of the tensor-core kernels, when they need it
+    size_t used = BH * N + (tc_needs_dtb(a.D, a.C) ? BH * N * a.T : 0);
+    used = (used + 63) & ~(size_t)63;
+    b.tc_extra = ws + used;
+    return;
+  }
   const size_t n_qt = (N + kBM - 1) / kBM;
   b.tbg = ws;
   b.cbg = b.tbg + BH * N * a.T;
@@ -786,9 +809,7 @@ void simt_bwd_carve(BwdArgs& b, float* ws) {
   b.delta = b.dcbg + BH * N * a.C;
   b.partial = b.delta + BH * N;
   b.drel_part = b.partial + BH * n_qt * 3 * a.D;
-  size_t used = (size_t)(b.drel_part - ws) + (size_t)kDrelSplit * a.Hkv * (a.T + a.C) * a.D;
-  used = (used + 63) & ~(size_t)63;
-  b.tc_extra = ws + used;  // only meaningful for bf16 problems; the caller clears it otherwise
+  b.tc_extra = nullptr;
 }
 
 }  // namespace mvpa
