@@ -1500,8 +1500,8 @@ int launch(const BwdArgs& bw, float* cs_dq, int* status, float* relc, float* rac
   {
     const size_t rows = (size_t)a.B * a.H * a.N;
     t.cblw = reinterpret_cast<__half*>(rows_ws + rows * (D / 2));
-    t.bcw = reinterpret_cast<__nv_bfloat16*>(rows_ws + rows * (D / 2) + rows * 64);
-    t.offw = rows_ws + rows * (D / 2) + rows * 128;
+    t.bcw = reinterpret_cast<__nv_bfloat16*>(rows_ws + rows * (D / 2) + rows * (CP / 2));
+    t.offw = rows_ws + rows * (D / 2) + rows * CP;
     t.tbw = t.offw + ((rows + 3) & ~(size_t)3);
   }
   t.B = a.B; t.H = a.H; t.Hkv = a.Hkv; t.T = a.T; t.C = a.C; t.g = a.g; t.window = a.window;
@@ -1547,10 +1547,11 @@ size_t cs_dq_floats(int B, int H, int T, int D) { return (((size_t)B * H * T * D
 // extra fp32 workspace elements of the tensor-core backward
 size_t tc_bwd_q_workspace_floats(const mvpa_problem* p) {
   const size_t rows = (size_t)p->B * p->H * p->T * p->C;
+  const size_t cp = p->C <= 32 ? 32 : (p->C <= 64 ? 64 : 128);  // channel slots per row (two 16-bit copies)
   // column sums + status + constants + per-row data for the key side (Q' bf16, channel scores fp16
   // padded to 128 slots, offset, temporal scores)
   size_t n = cs_dq_floats(p->B, p->H, p->T, p->D) + 64 + (size_t)p->Hkv * 256 +
-             (size_t)p->Hkv * (2 * p->D * 128 + 256) + rows * (p->D / 2) + rows * 128 +
+             (size_t)p->Hkv * (2 * p->D * 128 + 256) + rows * (p->D / 2) + rows * cp +
              ((rows + 3) & ~(size_t)3) + rows * p->T + 64;
 #ifdef MVPA_TC_TRACE
   n = ((n + 63) & ~(size_t)63) + (size_t)p->B * p->H * p->T * 256;  // the timelines (query side, key side) sit at the very end
