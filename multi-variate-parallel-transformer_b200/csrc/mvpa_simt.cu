@@ -268,20 +268,29 @@ __global__ void __launch_bounds__(kThreads) simt_rel_kernel(BwdArgs bw) {
                      bw.cbg + ((int64_t)bh * p.N + m0) * p.C, p.C, valid);
 }
 
-// delta[bh][i] = sum_d dO[i][d] * O[i][d]   (`attentions/attn.py:1213`); one warp per row.
-template <typename Tin>
+// delta[bh][i] = sum_d dO[i][d] * O[i][d]   (`attentions/attn.py:1213`).  HBM-bound: a thread reads 16
+// bytes of each tensor at a time, D / VEC threads share a row (VEC = elements per 16 bytes) and
+// combine with shuffles; D is a power of two >= 16, so a row never straddles warps.
+template <typename Tin, int D>
 __global__ void __launch_bounds__(kThreads) simt_delta_kernel(BwdArgs bw) {
+  constexpr int VEC = 16 / sizeof(Tin), TPR = D / VEC;  // threads per row: 4 .. 32
   const Args& p = bw.a;
-  const int warp = (blockIdx.x * kThreads + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int gid = blockIdx.x * kThreads + threadIdx.x;
+  const int rowi = gid / TPR, part = gid % TPR;
   const int bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
-  if (warp >= p.N) return;
-  const Tin* o = (const Tin*)p.o + b * p.o_sb + h * p.o_sh + (int64_t)warp * p.o_sn;
-  const Tin* g = (const Tin*)bw.d_o + b * bw.do_sb + h * bw.do_sh + (int64_t)warp * bw.do_sn;
   float acc = 0.f;
-  for (int d = lane; d < p.D; d += 32) acc += to_f32<Tin>(o[d]) * to_f32<Tin>(g[d]);
+  if (rowi < p.N) {
+    const Tin* o = (const Tin*)p.o + b * p.o_sb + h * p.o_sh + (int64_t)rowi * p.o_sn + part * VEC;
+    const Tin* g = (const Tin*)bw.d_o + b * bw.do_sb + h * bw.do_sh + (int64_t)rowi * bw.do_sn + part * VEC;
+    const uint4 ov = *reinterpret_cast<const uint4*>(o), gv = *reinterpret_cast<const uint4*>(g);
+    const Tin* oe = reinterpret_cast<const Tin*>(&ov);
+    const Tin* ge = reinterpret_cast<const Tin*>(&gv);
 #pragma unroll
-  for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
-  if (lane == 0) bw.delta[(int64_t)bh * p.N + warp] = acc;
+    for (int e = 0; e < VEC; ++e) acc += to_f32<Tin>(oe[e]) * to_f32<Tin>(ge[e]);
+  }
+#pragma unroll
+  for (int s = TPR / 2; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+  if (part == 0 && rowi < p.N) bw.delta[(int64_t)bh * p.N + rowi] = acc;
 }
 
 // dQ side: one CTA per (32 query rows, b, h).  Walks the causal key tiles, recomputes
@@ -684,8 +693,9 @@ int launch_bwd(const BwdArgs& b, cudaStream_t s) {
     count_launch();
   }
   {
-    dim3 grid((a.N * 32 + kThreads - 1) / kThreads, a.B * a.H);
-    simt_delta_kernel<Tin><<<grid, kThreads, 0, s>>>(b);
+    constexpr int kRowThreads = D / (16 / (int)sizeof(Tin));
+    dim3 grid((a.N * kRowThreads + kThreads - 1) / kThreads, a.B * a.H);
+    simt_delta_kernel<Tin, D><<<grid, kThreads, 0, s>>>(b);
     count_launch();
   }
   if (b.tc_extra != nullptr) {
