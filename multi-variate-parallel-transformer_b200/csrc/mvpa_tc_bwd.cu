@@ -449,11 +449,7 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
       // temporal scores of the row, for the key-side kernel (each warpgroup dumps half of the columns)
       {
         float* dst = p.tbw + ((int64_t)bh * T + 64 * wg) * N + (row_valid ? n_loc : 0);
-#pragma unroll 1
-        for (int c8 = 0; c8 < 64; c8 += 8) {
-          uint32_t v[8];
-          tmem_ld8(lane_base + kQDQ + 64 * wg + c8, v);
-          tmem_ld_wait();
+        auto put8 = [&](const uint32_t (&v)[8], int c8) {
           if (row_valid) {
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
@@ -461,6 +457,17 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
               if (j < T) dst[(int64_t)(c8 + e) * N] = p.c2 * (__uint_as_float(v[e]) + s_vr[j]);
             }
           }
+        };
+        uint32_t va[8], vb[8];  // the next 8 columns are in flight while 8 are stored
+        tmem_ld8(lane_base + kQDQ + 64 * wg, va);
+#pragma unroll 1
+        for (int c8 = 0; c8 < 64; c8 += 16) {
+          tmem_ld_wait();
+          tmem_ld8(lane_base + kQDQ + 64 * wg + c8 + 8, vb);
+          put8(va, c8);
+          tmem_ld_wait();
+          if (c8 + 16 < 64) tmem_ld8(lane_base + kQDQ + 64 * wg + c8 + 16, va);
+          put8(vb, c8 + 8);
         }
       }
       BTRACE(32);
@@ -718,29 +725,37 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
     BTRACE(4);
     // du = sum over rows of dq's content part (`attentions/attn.py:1305-1306`: q + q_bias feeds the content
     // term only): column sums of the accumulator before the relative terms are added to it
-    float* cs = reinterpret_cast<float*>(ring);  // [2 wg][128 rows][DW], columns rotated by the row
+    // (32 rows of a warp are summed with a shuffle butterfly that halves the values per lane each round and
+    // leaves column c0 + lane in lane `lane`; the four warps of a warpgroup meet in shared memory)
+    float* cs = reinterpret_cast<float*>(ring);  // [2 wg][4 warps][DW]
     if (ok) {
       tc_fence_after();
-#pragma unroll 1
-      for (int c8 = 0; c8 < DW; c8 += 8) {
-        uint32_t v[8];
-        tmem_ld8(lane_base + kQDQ + wg * DW + c8, v);
-        tmem_ld_wait();
 #pragma unroll
-        for (int e = 0; e < 8; ++e)
-          cs[(wg * 128 + row) * DW + ((c8 + e + row) & (DW - 1))] = row_valid ? __uint_as_float(v[e]) : 0.f;
+      for (int c0 = 0; c0 < DW; c0 += 32) {
+        uint32_t raw[32];
+        tmem_ld32(lane_base + kQDQ + wg * DW + c0, raw);
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) v[e] = row_valid ? __uint_as_float(raw[e]) : 0.f;
+#pragma unroll
+        for (int step = 16; step >= 1; step >>= 1) {
+          const bool upper = (lane & step) != 0;
+#pragma unroll
+          for (int j = 0; j < step; ++j) {
+            const float keep = upper ? v[j + step] : v[j];
+            const float send = upper ? v[j] : v[j + step];
+            v[j] = keep + __shfl_xor_sync(0xffffffffu, send, step);
+          }
+        }
+        cs[(wg * 4 + (warp & 3)) * DW + c0 + lane] = v[0];
       }
     }
     BTRACE(5);
     softmax_bar();
-    if (row < DW) {  // fixed summation order: deterministic; four chains hide the shared-memory latency
-      float s4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 2
-      for (int r = 0; r < 128; r += 4) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) s4[e] += cs[(wg * 128 + r + e) * DW + ((row + r + e) & (DW - 1))];
-      }
-      p.cs_dq[(size_t)blockIdx.x * D + wg * DW + row] = (s4[0] + s4[1]) + (s4[2] + s4[3]);
+    if (row < DW) {  // fixed summation order: deterministic
+      const float* c4 = cs + wg * 4 * DW + row;
+      p.cs_dq[(size_t)blockIdx.x * D + wg * DW + row] = (c4[0] + c4[DW]) + (c4[2 * DW] + c4[3 * DW]);
     }
     softmax_bar();
     BTRACE(6);
