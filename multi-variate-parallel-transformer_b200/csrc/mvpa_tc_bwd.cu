@@ -779,23 +779,31 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
     uint8_t* s_cbt = D == 128 ? sDO : ring + 98304;  // dO is dead by now; at head_dim 64 the ring has room
     if (ok) {
       const int jb = wg * (CP / 2);
-#pragma unroll 2
-      for (int m = 0; m < CP / 4; ++m) {
-        float vv[2];
+      constexpr int G = CP / 4 < 8 ? CP / 4 : 8;  // packed pairs per TMEM store (CP = 32 has 8 per warpgroup)
+#pragma unroll 1
+      for (int m0 = 0; m0 < CP / 4; m0 += G) {
+        uint32_t pkv[8];
 #pragma unroll
-        for (int t2 = 0; t2 < 2; ++t2) {
-          const int j = jb + 2 * m + t2, e = C - 1 - j;
-          // both candidates are read from wrapped (always valid) positions and masked: no divergence
-          const float lo = sc[row * CP + ((c_i - e + 2 * row) & (CP - 1))];
-          const float hi = sc[row * CP + ((c_i + e + 2 * row) & (CP - 1))];
-          const bool on = row_valid && e >= 0;
-          vv[t2] = ((on && c_i - e >= 0) ? lo : 0.f) + ((on && e > 0 && c_i + e < C) ? hi : 0.f);
+        for (int mi = 0; mi < G; ++mi) {
+          const int m = m0 + mi;
+          float vv[2];
+#pragma unroll
+          for (int t2 = 0; t2 < 2; ++t2) {
+            const int j = jb + 2 * m + t2, e = C - 1 - j;
+            // both candidates are read from wrapped (always valid) positions and masked: no divergence
+            const float lo = sc[row * CP + ((c_i - e + 2 * row) & (CP - 1))];
+            const float hi = sc[row * CP + ((c_i + e + 2 * row) & (CP - 1))];
+            const bool on = row_valid && e >= 0;
+            vv[t2] = ((on && c_i - e >= 0) ? lo : 0.f) + ((on && e > 0 && c_i + e < C) ? hi : 0.f);
+          }
+          pkv[mi] = pack_bf16(vv[0], vv[1]);
+          const int j = jb + 2 * m;
+          *reinterpret_cast<uint32_t*>(s_cbt + (j >> 6) * HALF + row * 128 + ((((j & 63) >> 3) ^ (row & 7)) << 4) +
+                                       (j & 7) * 2) = pkv[mi];
         }
-        const uint32_t pk2 = pack_bf16(vv[0], vv[1]);
-        tmem_st1(lane_base + kQDP + jb / 2 + m, pk2);
-        const int j = jb + 2 * m;
-        *reinterpret_cast<uint32_t*>(s_cbt + (j >> 6) * HALF + row * 128 + ((((j & 63) >> 3) ^ (row & 7)) << 4) +
-                                     (j & 7) * 2) = pk2;
+#pragma unroll
+        for (int mi = G; mi < 8; ++mi) pkv[mi] = 0u;
+        tmem_st8(lane_base + kQDP + jb / 2 + m0, pkv);
       }
     }
     BTRACE(43);
