@@ -91,7 +91,12 @@ def test_oracle_on_rows_of_config2(cuda):
 
 BWD_CASES = [(1, 16, 16, 128, 32, 64),   # config 3's shape, one batch element: several CTAs per SM in a row
              (1, 4, 2, 128, 128, 128),   # 16k tokens, grouped heads, head_dim 128
-             (2, 4, 4, 64, 64, 64)]      # config 2's shape, two batch elements
+             (2, 4, 4, 64, 64, 64),      # config 2's shape, two batch elements
+             # ragged channel / segment counts with many tiles outside the window, one per kernel variant:
+             (2, 4, 2, 50, 22, 64),      # 32 channel slots, head_dim 64, grouped heads
+             (1, 4, 4, 40, 100, 64),     # 128 channel slots at head_dim 64
+             (1, 2, 1, 30, 60, 128),     # 64 channel slots at head_dim 128
+             (1, 2, 2, 128, 7, 128)]     # 32 channel slots at head_dim 128
 
 
 @pytest.mark.parametrize("cfg", BWD_CASES)
