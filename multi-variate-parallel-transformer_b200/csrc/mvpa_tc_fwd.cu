@@ -169,6 +169,10 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
   // scheduler are in different phases (one in its exponentials, the other loading or reducing)
   // and no barrier is needed inside a tile; the accumulators are merged before the light tiles.
   constexpr bool ALT = (D == 64) && (CP <= 64);
+  // With at most 64 channel slots the prologue's scratch rows are padded instead of rotated, and each
+  // thread's columns hold every channel slot (no maximum exchange between the warpgroups).
+  constexpr bool PAD = CP <= 64;
+  constexpr int LDP = PAD ? CP + 2 : CP;
   static_assert(CP >= 32 && CP <= 128 && (CP & (CP - 1)) == 0, "CP in {32,64,128}");
 
   extern __shared__ uint8_t smem_raw[];
@@ -442,7 +446,9 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const int jj = j4 * 4 + e;
-              scratch[row * CP + ((ci * 32 + jj + 2 * row) & (CP - 1))] = p.c2 * (__uint_as_float(v[jj]) + zz[e]);
+              const float val = p.c2 * (__uint_as_float(v[jj]) + zz[e]);
+              if constexpr (PAD) scratch[row * LDP + ci * 32 + jj] = val;
+              else scratch[row * CP + ((ci * 32 + jj + 2 * row) & (CP - 1))] = val;
             }
           }
         }
@@ -460,19 +466,35 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
       float g[NCH];
       float mx = -INFINITY;
       if (ok) {
+        if constexpr (PAD) {
+          // slot C-1-|c_i - c_k| runs up through the row for c_k <= c_i and down for c_k > c_i: two base
+          // pointers with constant offsets (rows padded by two floats: no bank conflicts on either diagonal;
+          // positions of channels that do not exist may lie outside the row, their values are dropped)
+          const float* up = scratch + row * LDP + (C - 1 - c_i);
+          const float* down = scratch + row * LDP + (C - 1 + c_i);
+          const int climit = c_i < C ? C : 0;
 #pragma unroll
-        for (int k = 0; k < NCH; ++k) {
-          const int ck = ck_base + k;
-          const int jc = min(max(C - 1 - abs(c_i - ck), 0), CP - 1);
-          const float val = scratch[row * CP + ((jc + 2 * row) & (CP - 1))];  // rows rotated: no bank conflicts on the (anti)diagonal
-          g[k] = (c_i < C && ck < C) ? val : -INFINITY;
-          mx = fmaxf(mx, g[k]);
+          for (int k = 0; k < NCH; ++k) {
+            const float val = k <= c_i ? up[k] : down[-k];
+            g[k] = k < climit ? val : -INFINITY;
+            mx = fmaxf(mx, g[k]);
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < NCH; ++k) {
+            const int ck = ck_base + k;
+            const int jc = min(max(C - 1 - abs(c_i - ck), 0), CP - 1);
+            const float val = scratch[row * CP + ((jc + 2 * row) & (CP - 1))];  // rows rotated: no bank conflicts on the (anti)diagonal
+            g[k] = (c_i < C && ck < C) ? val : -INFINITY;
+            mx = fmaxf(mx, g[k]);
+          }
         }
       }
-      // the row maximum spans both warpgroups' columns when CP = 128
-      s_max[wg * 128 + row] = mx;
-      softmax_bar();
-      mx = fmaxf(mx, s_max[(wg ^ 1) * 128 + row]);
+      if constexpr (!PAD) {  // the row maximum spans both warpgroups' columns when CP = 128
+        s_max[wg * 128 + row] = mx;
+        softmax_bar();
+        mx = fmaxf(mx, s_max[(wg ^ 1) * 128 + row]);
+      }
       mc = (mx == -INFINITY) ? 0.f : mx;
       if (ok) {
 #pragma unroll
