@@ -161,6 +161,9 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
   // dS has one owner and goes straight into a shared-memory tile; otherwise the two owners add into the
   // workspace with atomics and the tile is rebuilt from there after the loop.
   constexpr bool TBS = (D == 64) && (CP <= 64);
+  // The prologue's scratch rows are padded instead of rotated when that fits (<= 64 channel slots).
+  constexpr bool PAD = CP <= 64;
+  constexpr int LDP = PAD ? CP + 2 : CP;
   static_assert(CP >= 32 && CP <= 128 && (CP & (CP - 1)) == 0, "CP in {32,64,128}");
 
   extern __shared__ uint8_t smem_raw[];
@@ -478,8 +481,11 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
         tmem_ld8(lane_base + kQS + c8, v);
         tmem_ld_wait();
 #pragma unroll
-        for (int e = 0; e < 8; ++e)
-          scratch[row * CP + ((c8 + e + 2 * row) & (CP - 1))] = p.c2 * (__uint_as_float(v[e]) + s_zc[c8 + e]);
+        for (int e = 0; e < 8; ++e) {
+          const float val = p.c2 * (__uint_as_float(v[e]) + s_zc[c8 + e]);
+          if constexpr (PAD) scratch[row * LDP + c8 + e] = val;
+          else scratch[row * CP + ((c8 + e + 2 * row) & (CP - 1))] = val;
+        }
       }
       tc_fence_before();
     }
@@ -490,20 +496,33 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
     {
       // gather by key channel slot: g_k = CB[i, C-1-|c_i - c_k|]; first the row maximum, then fp16 values
       // relative to it, staged in this thread's own row of s_cbl (16-byte chunks swizzled by the row)
+      // (up to 64 channel slots: padded rows, slot C-1-|c_i - c_k| runs up through the row for c_k <= c_i
+      // and down for c_k > c_i; positions of channels that do not exist may lie outside the row and
+      // are dropped.  128 slots: rotated rows.)
+      const float* up = scratch + row * LDP + (C - 1 - c_i);
+      const float* down = scratch + row * LDP + (C - 1 + c_i);
+      const int climit = c_i < C ? C : 0;
       auto gathered = [&](int k) {
-        const int ck = ck_base + k;
-        const int jc = min(max(C - 1 - abs(c_i - ck), 0), CP - 1);
-        const float val = ok ? scratch[row * CP + ((jc + 2 * row) & (CP - 1))] : 0.f;
-        return (c_i < C && ck < C) ? val : -INFINITY;
+        if constexpr (PAD) {
+          const float val = ok ? (k <= c_i ? up[k] : down[-k]) : 0.f;
+          return k < climit ? val : -INFINITY;
+        } else {
+          const int ck = ck_base + k;
+          const int jc = min(max(C - 1 - abs(c_i - ck), 0), CP - 1);
+          const float val = ok ? scratch[row * CP + ((jc + 2 * row) & (CP - 1))] : 0.f;
+          return (c_i < C && ck < C) ? val : -INFINITY;
+        }
       };
       float mx = -INFINITY;
 #pragma unroll 4
       for (int k = 0; k < NCH; ++k) mx = fmaxf(mx, gathered(k));
-      s_max[wg * 128 + row] = mx;
-      BTRACE(35);
-      softmax_bar();
-      BTRACE(36);
-      mx = fmaxf(mx, s_max[(wg ^ 1) * 128 + row]);
+      if constexpr (!PAD) {  // the row maximum spans both warpgroups' columns
+        s_max[wg * 128 + row] = mx;
+        BTRACE(35);
+        softmax_bar();
+        BTRACE(36);
+        mx = fmaxf(mx, s_max[(wg ^ 1) * 128 + row]);
+      }
       mc = (mx == -INFINITY) ? 0.f : mx;
       // fp16 pairs relative to the maximum, staged in this thread's lane of idle TMEM columns so that the
       // loop stays short and the values still end up in registers

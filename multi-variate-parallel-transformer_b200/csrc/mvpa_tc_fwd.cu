@@ -498,11 +498,16 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
       mc = (mx == -INFINITY) ? 0.f : mx;
       if (ok) {
 #pragma unroll
-        for (int k2 = 0; k2 < NCH / 2; ++k2) {
-          const float x0 = g[2 * k2] - mc, x1 = g[2 * k2 + 1] - mc;
-          cbl[k2] = __floats2half2_rn(x0, x1);
-          bc[k2] = pack_bf16(ex2(x0), ex2(x1));
-          sum_bc += __uint_as_float(bc[k2] << 16) + __uint_as_float(bc[k2] & 0xffff0000u);
+        for (int k2 = 0; k2 < NCH / 2; ++k2) cbl[k2] = __floats2half2_rn(g[2 * k2] - mc, g[2 * k2 + 1] - mc);
+        if (n_light > 0) {  // (the exponentials are only used by light tiles)
+#pragma unroll
+          for (int k2 = 0; k2 < NCH / 2; ++k2) {
+            bc[k2] = pack_bf16(ex2(g[2 * k2] - mc), ex2(g[2 * k2 + 1] - mc));
+            sum_bc += __uint_as_float(bc[k2] << 16) + __uint_as_float(bc[k2] & 0xffff0000u);
+          }
+        } else {
+#pragma unroll
+          for (int k2 = 0; k2 < NCH / 2; ++k2) bc[k2] = 0u;
         }
         // Q' = (q+u) c2 in place (`attentions/attn.py:180-183`); each warpgroup converts half of the chunks
         const float4* u4 = reinterpret_cast<const float4*>(s_bias);
