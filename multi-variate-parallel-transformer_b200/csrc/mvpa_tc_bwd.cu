@@ -201,8 +201,9 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
   auto q_of_v = [&](int s) { return s < n_light ? s : n_light + 2 * (s - n_light) + 1; };
   const int T = p.T, C = p.C;
 
+  // One barrier at entry: thread 0 initialises the mbarriers, another warp fetches the status word (an
+  // earlier CTA may have given up), warp 9 allocates the tensor memory - all at the same time.
   if (tid == 0) {
-    *s_abort = *p.status;
     mbar_init(&bars[kBarProFull], 1);
     mbar_init(&bars[kBarProMma], 1);
     mbar_init(&bars[kBarProDone], kSoftmaxThreads);
@@ -222,9 +223,9 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
       mbar_init(&slot_free[i], 1);
     }
     mbar_fence_init();
+  } else if (tid == 64) {
+    *s_abort = *p.status;
   }
-  __syncthreads();
-  if (*s_abort != 0) return;
   if (warp == 9) {
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
@@ -233,6 +234,10 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  if (*s_abort != 0) {  // do nothing, but give the columns back
+    if (warp == 9) tmem_dealloc(tmem, kTmemCols);
+    return;
+  }
 
   if (warp >= 8) {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
@@ -1041,8 +1046,9 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
     i = J + dl + l % n_light_i;
   };
 
+  // One barrier at entry: thread 0 initialises the mbarriers, another warp fetches the status word (an
+  // earlier CTA may have given up), warp 9 allocates the tensor memory - all at the same time.
   if (tid == 0) {
-    *s_abort = *p.status;
     mbar_init(&bars[kKvFull], 1);
     mbar_init(&bars[kQdoFull], 1);
     mbar_init(&bars[kQdoFull + 1], 1);
@@ -1059,9 +1065,9 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
       mbar_init(&bars[kLFree + i], 1);
     }
     mbar_fence_init();
+  } else if (tid == 64) {
+    *s_abort = *p.status;
   }
-  __syncthreads();
-  if (*s_abort != 0) return;
   if (warp == 9) {
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
@@ -1070,6 +1076,10 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  if (*s_abort != 0) {  // do nothing, but give the columns back
+    if (warp == 9) tmem_dealloc(tmem, kTmemCols);
+    return;
+  }
 
   if (warp >= 8) {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");

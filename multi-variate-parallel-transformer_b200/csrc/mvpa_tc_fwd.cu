@@ -221,8 +221,9 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
   auto q_of_v = [&](int s) { return s < n_dense ? 2 * s + 1 : n_dense + s; };
   const int T = p.T, C = p.C;
 
+  // One barrier at entry: thread 0 initialises the mbarriers, another warp fetches the status word (an
+  // earlier CTA may have given up), warp 9 allocates the tensor memory - all at the same time.
   if (tid == 0) {
-    *s_abort = *p.status;  // an earlier CTA already gave up: do nothing
     *s_giveup = 0;
     mbar_init(&bars[kBarProFull], 1);
     mbar_init(&bars[kBarProMma], 1);
@@ -238,9 +239,9 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
       mbar_init(&slot_free[i], 1);
     }
     mbar_fence_init();
+  } else if (tid == 64) {
+    *s_abort = *p.status;
   }
-  __syncthreads();
-  if (*s_abort != 0) return;
   if (warp == 9) {
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
@@ -249,6 +250,10 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  if (*s_abort != 0) {  // do nothing, but give the columns back
+    if (warp == 9) tmem_dealloc(tmem, kTmemCols);
+    return;
+  }
   // Register re-balancing between warpgroups: the producer / MMA warpgroup keeps 40 registers
   // per thread, the two softmax warpgroups grow to 232.
   if (warp >= 8) {
