@@ -66,6 +66,7 @@ constexpr float kRescaleThreshold = 8.f;  // log2 units: P stays below 2^8
 
 struct TcMaps {
   CUtensorMap q, k, v, rt, rc;
+  CUtensorMap o;  // store
 };
 
 struct TcArgs {
@@ -923,24 +924,33 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
       tc_fence_after();
       const float inv = 1.f / l_sum;
       const int64_t n = (int64_t)(ti_abs - p.q_t0) * C + c_i;  // row inside this call's q / o / lse
-      __nv_bfloat16* orow = p.o + b * p.o_sb + h * p.o_sh + n * p.o_sn + wg * DW;
+      // O / l as bf16 into the Q tile's place (laid out like it: 128-byte swizzled rows), then one TMA
+      // store per 64-column half; rows and channels outside the tensor are not written.
 #pragma unroll
       for (int c0 = 0; c0 < DW; c0 += 32) {
         uint32_t v[32];
         tmem_ld32(lane_base + kColO + wg * DW + c0, v);
         tmem_ld_wait();
-        if (row_valid) {
 #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            uint32_t w[4];
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint32_t w[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
-              w[e] = pack_bf16(__uint_as_float(v[q4 * 8 + 2 * e]) * inv, __uint_as_float(v[q4 * 8 + 2 * e + 1]) * inv);
-            *reinterpret_cast<uint4*>(orow + c0 + q4 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
-          }
+          for (int e = 0; e < 4; ++e)
+            w[e] = pack_bf16(__uint_as_float(v[q4 * 8 + 2 * e]) * inv, __uint_as_float(v[q4 * 8 + 2 * e + 1]) * inv);
+          const int col = wg * DW + c0 + q4 * 8, hh = col / 64, c = (col % 64) / 8;
+          *reinterpret_cast<uint4*>(sQ + hh * HALF + row * 128 + ((c ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
+      fence_proxy_async_smem();
       if (wg == 0 && row_valid && p.lse != nullptr) p.lse[(int64_t)bh * p.q_tn * C + n] = m_used + log2f(l_sum);
+    }
+    if (!ok) *s_giveup = 1;
+    softmax_bar();
+    if (*s_giveup == 0 && tid == 0) {
+#pragma unroll
+      for (int hh = 0; hh < NH; ++hh) tma_store_5d(&maps.o, sQ + hh * HALF, hh * 64, 0, I_loc * TPB, h, b);
+      tma_store_commit();
+      tma_store_wait_all();
     }
     TRACE(6);
     tc_fence_before();
@@ -970,6 +980,9 @@ int make_maps(TcMaps& m, const Args& a, int CP) {
                              (uint64_t)a.q_sb * es};
     const uint32_t box[5] = {64, (uint32_t)CP, (uint32_t)TPB, 1, 1};
     if ((rc = encode_bf16_sw128(&m.q, a.q, 5, dims, str, box))) return rc;
+    const uint64_t stro[4] = {(uint64_t)a.o_sn * es, (uint64_t)a.o_sn * a.C * es, (uint64_t)a.o_sh * es,
+                              (uint64_t)a.o_sb * es};
+    if ((rc = encode_bf16_sw128(&m.o, a.o, 5, dims, stro, box))) return rc;
   }
   {
     const uint64_t dims[5] = {(uint64_t)a.D, (uint64_t)a.C, (uint64_t)a.T, (uint64_t)a.Hkv, (uint64_t)a.B};
