@@ -117,3 +117,21 @@ def test_backward_tensor_core_vs_fp32_path_full_size(cuda, cfg):
         a, b = grads[0][n], grads[1][n]
         assert torch.isfinite(a).all(), n
         assert (a - b).abs().max() <= 3e-2 * b.abs().max() + 1e-6, (n, float((a - b).abs().max()), float(b.abs().max()))
+
+
+@pytest.mark.parametrize("gain", [4.0, 40.0])
+def test_forward_with_score_jumps_between_key_tiles(cuda, gain):
+    """The temporal keys of the most recent lags are scaled up, so the row maximum jumps from one key
+    tile to the next (tiles are visited oldest first), by about ten or by more than sixty binary orders
+    of magnitude: the running reference of the online softmax has to follow.  (The temporal products
+    use the raw bf16 q, so both paths see identical scores up to fp32 summation order.)  bf16
+    tensor-core result vs the fp32 CUDA-core kernels on the same values; 2e-2 of the largest |o|."""
+    B, H, Hkv, T, C, D = 1, 2, 2, 16, 64, 64
+    t = make(cuda, 7, B, H, Hkv, T, C, D)
+    rt = t["rt"].clone()
+    rt[:, :, T - 4:] *= gain                # slots T-1-dt of the lags dt = 0 .. 3
+    t = dict(t, rt=rt)
+    a = run(t).float()
+    b = run({n: x.float().contiguous() for n, x in t.items()})
+    assert torch.isfinite(a).all()
+    assert (a - b).abs().max() <= 2e-2 * b.abs().max(), float((a - b).abs().max())
