@@ -1305,9 +1305,19 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
       float tb[TPW];
       float off;
     };
-    auto light_fetch = [&](int l, RowData& r) {
+    // (head, query tile) of a light pair advance as running cursors: no integer division in the loop
+    struct Cursor {
       int h, i;
-      light_pair(l, h, i);
+    };
+    auto advance = [&](Cursor& c, int by) {
+      c.i += by;
+      while (c.i >= J + dl + n_light_i) {
+        c.i -= n_light_i;
+        ++c.h;
+      }
+    };
+    auto light_fetch = [&](Cursor c, RowData& r) {
+      const int h = c.h, i = c.i;
       const int ti_abs = i * TPB + ti_loc;
       const bool row_valid = c_i < C && ti_abs < T;
       const int N = T * C, n_loc = row_valid ? ti_abs * C + c_i : 0;
@@ -1322,10 +1332,11 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
         r.tb[tl] = p.tbw[(bhq * T + (T - 1 - dt)) * N + n_loc];
       }
     };
+    Cursor cur{hk * p.g, J + dl}, nxt{hk * p.g, J + dl};  // pair l, pair l + 2 (the one to fetch)
     auto light_body = [&](int l, RowData& r) {
       if (l >= 4 && l < 8) BTRACE(20 + 4 * (l - 4));
-      int h, i;
-      light_pair(l, h, i);
+      const int i = cur.i;
+      advance(cur, 1);
       const int bsel = l & 1;
       const int ti_abs = i * TPB + ti_loc;
       const bool row_valid = c_i < C && ti_abs < T;
@@ -1342,7 +1353,10 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
         a2[tl] = pack_bf16(a, a);
       }
       if (l >= 4 && l < 8) BTRACE(21 + 4 * (l - 4));
-      if (l + 2 < n_light) light_fetch(l + 2, r);  // this stage's registers are free again
+      if (l + 2 < n_light) {  // this stage's registers are free again
+        light_fetch(nxt, r);
+        advance(nxt, 1);
+      }
       if (l >= 2) {
         ok = warp_wait(&bars[kLFree + bsel], ((l >> 1) - 1) & 1, p.status, 236);
         if (!ok) return;
@@ -1364,8 +1378,14 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
       if (l < 16) BTRACE(40 + l);
     };
     RowData r0, r1;
-    if (ok && n_light > 0) light_fetch(0, r0);
-    if (ok && n_light > 1) light_fetch(1, r1);
+    if (ok && n_light > 0) {
+      light_fetch(nxt, r0);
+      advance(nxt, 1);
+    }
+    if (ok && n_light > 1) {
+      light_fetch(nxt, r1);
+      advance(nxt, 1);
+    }
     for (int l = 0; ok && l < n_light; l += 2) {
       light_body(l, r0);
       if (ok && l + 1 < n_light) light_body(l + 1, r1);
