@@ -457,19 +457,24 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
       // temporal scores of the row, for the key-side kernel (each warpgroup dumps half of the columns)
       {
         float* dst = p.tbw + ((int64_t)bh * T + 64 * wg) * N + (row_valid ? n_loc : 0);
+        // Only the slots of keys a row can see (t_k <= t_i: slot >= T-1-t_i) are ever read, by this
+        // kernel's loop and by the key-side kernel: early query tiles skip most of the dump.
+        const int j_row = T - 1 - min(ti_abs, T - 1);
         auto put8 = [&](const uint32_t (&v)[8], int c8) {
           if (row_valid) {
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
               const int j = 64 * wg + c8 + e;
-              if (j < T) dst[(int64_t)(c8 + e) * N] = p.c2 * (__uint_as_float(v[e]) + s_vr[j]);
+              if (j >= j_row && j < T) dst[(int64_t)(c8 + e) * N] = p.c2 * (__uint_as_float(v[e]) + s_vr[j]);
             }
           }
         };
+        const int j_tile = max(T - 1 - (I * TPB + TPB - 1), 0) - 64 * wg;  // first slot any row of the tile can see
+        const int c_first = j_tile <= 0 ? 0 : (j_tile & ~15);
         uint32_t va[8], vb[8];  // the next 8 columns are in flight while 8 are stored
-        tmem_ld8(lane_base + kQDQ + 64 * wg, va);
+        if (c_first < 64) tmem_ld8(lane_base + kQDQ + 64 * wg + c_first, va);
 #pragma unroll 1
-        for (int c8 = 0; c8 < 64; c8 += 16) {
+        for (int c8 = c_first; c8 < 64; c8 += 16) {
           tmem_ld_wait();
           tmem_ld8(lane_base + kQDQ + 64 * wg + c8 + 8, vb);
           put8(va, c8);
