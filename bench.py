@@ -223,6 +223,53 @@ def time_kernel(torch, attentions, t, w, steps, warmup, flush, gout=None):
     return [a.elapsed_time(b) for a, b in ev]
 
 
+def time_layer(torch, dev, flush, reps=10, warm=3):
+    """The layer module (`layers/mvpa.py:341-409` in the reference) at one sample of BASELINE config 5:
+    projections (cuBLAS) + the attention kernel on strided head views + `c_proj`.  Also times, on the same
+    tensors, the head split / merge copies the reference layer makes (`layers/mvpa.py:383-390,398-399`)
+    and this one does not."""
+    from types import SimpleNamespace as NS
+    import layers
+    H, Hkv, D, T, C = 16, 8, 128, 128, 128
+    E, N = H * D, T * C
+    cfg = NS(max_position_embeddings=T, hidden_size=E, num_attention_heads=H, n_head_kv=Hkv, n_inner=5632,
+             global_att=True, scale_attn_weights=True, scale_attn_by_inverse_layer_idx=False,
+             reorder_and_upcast_attn=False, lora=False, attn_pdrop=0.0, resid_pdrop=0.0)
+    torch.manual_seed(4)
+    m = layers.MVPFormerGQAFlashAttention(cfg, layer_idx=0).eval().to(dev).to(torch.bfloat16)
+    x = torch.randn(1, T, C, E, device=dev, dtype=torch.bfloat16)
+    pos = torch.randn(1, T, E, device=dev, dtype=torch.bfloat16)
+    chan = torch.randn(1, C, E, device=dev, dtype=torch.bfloat16)
+
+    def timed(fn):
+        ms = []
+        for i in range(warm + reps):
+            flush.add_(1)  # writes 256 MiB: evicts the L2
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= warm:
+                ms.append(e0.elapsed_time(e1))
+        return statistics.mean(ms)
+
+    with torch.no_grad():
+        layer_ms = timed(lambda: m(x, pos, chan))
+        q = torch.randn(1, N, H, D, device=dev, dtype=torch.bfloat16)
+        kv = torch.randn(1, N, 2 * Hkv, D, device=dev, dtype=torch.bfloat16)
+        o = torch.randn(1, H, N, D, device=dev, dtype=torch.bfloat16)
+
+        def copies():
+            q.permute(0, 2, 1, 3).contiguous()
+            kv[:, :, :Hkv].permute(0, 2, 1, 3).contiguous()
+            kv[:, :, Hkv:].permute(0, 2, 1, 3).contiguous()
+            o.permute(0, 2, 1, 3).contiguous()
+        copies_ms = timed(copies)
+    return {"ms": layer_ms, "tokens_per_s": N / (layer_ms * 1e-3),
+            "head_split_merge_copies_avoided_ms": copies_ms}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -391,6 +438,7 @@ def main():
                 f3 = flops(**ww)["f_alg"] + flops_bwd(**ww)
                 extra[name] = {"ms": m3, "tflops_f_alg": f3 / m3 / 1e9, "frac_of_peak_f_alg": f3 / m3 / 1e9 / peak}
                 del tt, g2
+            extra["layer_fwd_16k_tokens_E2048_H16_Hkv8"] = time_layer(torch, dev, flush)
             out["extra"] = extra
         if not args.no_cpu and world == 1:  # the CPU leg belongs to the single-GPU run (torchrun pins OMP threads to 1)
             sample = dict(w, B=1)
