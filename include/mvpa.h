@@ -44,6 +44,7 @@ extern "C" {
 /* Element type of q, k, v, u, vt, z, r_time, r_chan, o, dO, dq, dk, dv. */
 #define MVPA_F32 0  /* fp32 I/O, fp32 arithmetic on CUDA cores                      */
 #define MVPA_BF16 1 /* bf16 I/O, tcgen05 tensor cores with fp32 accumulation in TMEM */
+#define MVPA_F16 2  /* fp16 I/O (the reference op takes it too), fp32 arithmetic on CUDA cores */
 
 /* Problem description.  Mirrors the constexpr arguments of the reference launch
  * (`attentions/attn.py:1103-1120`: Z, H_Q, H_KV, N_CTX, TIME_CTX, CHANNEL_CTX,
@@ -56,7 +57,7 @@ typedef struct mvpa_problem {
   int32_t C;      /* channels       (rows of r_chan)                              */
   int32_t D;      /* head dim: 16, 32, 64 or 128 (`attentions/attn.py:1043`)      */
   int32_t window; /* content-window half width in time steps; <= 0: no window     */
-  int32_t dtype;  /* MVPA_F32 or MVPA_BF16                                        */
+  int32_t dtype;  /* MVPA_F32, MVPA_BF16, MVPA_F16                                       */
   float sm_scale; /* applied to the sum of the three score terms                  */
   int32_t flags;  /* reserved, must be 0                                          */
   /* Query time range (forward only).  q, o and lse then hold the tokens of time steps

@@ -27,7 +27,9 @@ def _dtype_code(t: torch.Tensor) -> int:
         return _nat.MVPA_BF16
     if t.dtype == torch.float32:
         return _nat.MVPA_F32
-    raise RuntimeError(f"flash_mvpa: dtype {t.dtype} not supported (bfloat16 or float32)")
+    if t.dtype == torch.float16:
+        return _nat.MVPA_F16
+    raise RuntimeError(f"flash_mvpa: dtype {t.dtype} not supported (bfloat16, float16 or float32)")
 
 
 def _tensor(t: torch.Tensor) -> _nat.Tensor:

@@ -30,8 +30,8 @@ int check_problem(const mvpa_problem* p) {
     set_error("problem pointer is NULL");
     return MVPA_ERR_SHAPE;
   }
-  if (p->dtype != MVPA_F32 && p->dtype != MVPA_BF16) {
-    set_error("unknown dtype %d (MVPA_F32=0, MVPA_BF16=1)", p->dtype);
+  if (p->dtype != MVPA_F32 && p->dtype != MVPA_BF16 && p->dtype != MVPA_F16) {
+    set_error("unknown dtype %d (MVPA_F32=0, MVPA_BF16=1, MVPA_F16=2)", p->dtype);
     return MVPA_ERR_DTYPE;
   }
   if (p->B <= 0 || p->H <= 0 || p->Hkv <= 0 || p->T <= 0 || p->C <= 0) {

@@ -768,11 +768,13 @@ int dispatch_bwd(const BwdArgs& b, cudaStream_t s) {
 }  // namespace
 
 int simt_fwd(const Args& a, int dtype, cudaStream_t s) {
-  return dtype == MVPA_F32 ? dispatch_fwd<float>(a, s) : dispatch_fwd<__nv_bfloat16>(a, s);
+  return dtype == MVPA_F32 ? dispatch_fwd<float>(a, s)
+         : dtype == MVPA_F16 ? dispatch_fwd<__half>(a, s) : dispatch_fwd<__nv_bfloat16>(a, s);
 }
 
 int simt_bwd(const BwdArgs& b, int dtype, cudaStream_t s) {
-  return dtype == MVPA_F32 ? dispatch_bwd<float>(b, s) : dispatch_bwd<__nv_bfloat16>(b, s);
+  return dtype == MVPA_F32 ? dispatch_bwd<float>(b, s)
+         : dtype == MVPA_F16 ? dispatch_bwd<__half>(b, s) : dispatch_bwd<__nv_bfloat16>(b, s);
 }
 
 namespace {

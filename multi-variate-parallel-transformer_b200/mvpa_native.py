@@ -27,7 +27,7 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC", "-shared", "--use_fast_math",
 ]
 
-MVPA_F32, MVPA_BF16 = 0, 1
+MVPA_F32, MVPA_BF16, MVPA_F16 = 0, 1, 2
 
 _lock = threading.Lock()
 _lib = None

@@ -44,6 +44,7 @@ def test_argument_errors_are_reported_without_a_device():
     assert _call_fwd(_prob(D=48)) == -1 and "head dim" in nat.last_error()
     assert _call_fwd(_prob(T=0)) == -1
     assert _call_fwd(_prob(dtype=7)) == -2
+    assert _call_fwd(_prob(dtype=nat.MVPA_F16, H=3)) == -1   # fp16 is a known element type: the shape is what fails
     assert _call_fwd(_prob(), ptr=260) == -3 and "16" in nat.last_error()
     assert _call_fwd(_prob(), stride_n=63) == -3
     assert _call_fwd(_prob(flags=1)) == -1
@@ -58,3 +59,7 @@ def test_workspace_queries():
     assert need >= 4 * (2 * n * (8 + 4) + n)
     assert lib.mvpa_fwd_workspace_bytes(ctypes.byref(p)) == 0  # fp32 forward needs no scratch
     assert lib.mvpa_bwd_workspace_bytes(ctypes.byref(_prob(D=48))) == 0
+    # fp16 runs on the same fp32-arithmetic kernels: same scratch as fp32
+    p16 = _prob(B=2, H=4, Hkv=2, T=8, C=4, D=64, dtype=nat.MVPA_F16)
+    assert lib.mvpa_fwd_workspace_bytes(ctypes.byref(p16)) == 0
+    assert lib.mvpa_bwd_workspace_bytes(ctypes.byref(p16)) == need

@@ -3,6 +3,7 @@
 Tolerances (against the fp32/fp64 oracle on the same inputs):
   fp32 I/O : max-abs error <= 1e-4 * max|reference|
   bf16 I/O : max-abs error <= 2e-2   (inputs rounded to bf16 first, oracle fed the rounded values)
+  fp16 I/O : max-abs error <= 4e-3 * max(1, max|reference|)   (same, rounded to fp16; fp32 arithmetic inside)
 """
 import numpy as np
 import pytest
@@ -16,6 +17,7 @@ pytestmark = pytest.mark.gpu
 GRADS = ("dq", "du", "dv", "dz", "dk", "dr_time", "dr_chan", "dval")
 F32_REL = 1e-4
 BF16_ABS = 2e-2
+F16_ABS = 4e-3
 
 
 def _op(dev, g, dtype, grads=False, window=10):
@@ -35,12 +37,12 @@ def _np(x):
     return x.detach().float().cpu().numpy()
 
 
-def _rounded(g):
-    """Copy of a case with every input rounded to bf16 (what the bf16 kernels actually see)."""
+def _rounded(g, dtype=torch.bfloat16):
+    """Copy of a case with every input rounded to bf16 / fp16 (what those kernels actually see)."""
     r = dict(g)
     for k in ("q", "u", "v", "z", "k", "r_time", "r_chan", "val", "do"):
         if k in r:
-            r[k] = torch.tensor(r[k]).to(torch.bfloat16).float().numpy()
+            r[k] = torch.tensor(r[k]).to(dtype).float().numpy()
     return r
 
 
@@ -136,6 +138,25 @@ def test_backward_random_shapes_vs_oracle(cuda, shape, dtype):
         r = ref[gk]
         err = np.abs(_np(t[key].grad).reshape(r.shape) - r).max()
         assert err <= tol * max(1.0, np.abs(r).max()), (gk, err)
+
+
+@pytest.mark.parametrize("shape", [(1, 2, 1, 13, 16, 64), (2, 2, 2, 5, 33, 128), (1, 3, 1, 12, 32, 32),
+                                   (1, 1, 1, 14, 128, 64)])
+def test_fp16_forward_and_backward_vs_oracle(cuda, shape):
+    """The reference operator takes fp16 as well as bf16 / fp32 (`attn.py:1013-1138` has no dtype check
+    beyond "all equal"); here fp16 runs on the fp32-arithmetic kernels, so only I/O rounding shows."""
+    g = _rounded(random_case(300 + sum(shape), *shape), torch.float16)
+    ref_o, _ = mo.mvpa_forward(*_oracle_args(g), float(g["sm_scale"]))
+    ref = mo.mvpa_backward(*_oracle_args(g), g["do"], float(g["sm_scale"]))
+    o, t = _op(cuda, g, torch.float16, grads=True)
+    assert o.dtype == torch.float16
+    assert np.abs(_np(o) - ref_o).max() <= F16_ABS * max(1.0, np.abs(ref_o).max())
+    o.backward(torch.tensor(g["do"], device=cuda, dtype=torch.float16))
+    for key, gk in zip(("q", "u", "v", "z", "k", "r_time", "r_chan", "val"), GRADS):
+        r = ref[gk]
+        assert t[key].grad.dtype == torch.float16
+        err = np.abs(_np(t[key].grad).reshape(r.shape) - r).max()
+        assert err <= F16_ABS * max(1.0, np.abs(r).max()), (gk, err)
 
 
 def test_no_window_flag(cuda):
