@@ -442,9 +442,10 @@ def main():
             out["extra"] = extra
         if not args.no_cpu and world == 1:  # the CPU leg belongs to the single-GPU run (torchrun pins OMP threads to 1)
             sample = dict(w, B=1)
-            sec, cores = cpu_port_time(sample)
+            cpu_port_time(dict(sample, H=1, Hkv=1))  # warm-up: thread pool, allocator
+            sec, cores = cpu_port_time(sample, reps=10)  # about 10 s of CPU work
             out["cpu_baseline"] = {"value": flops(**sample)["f_alg"] / sec / 1e12, "unit": UNIT, "cores": cores,
-                                   "kind": "port", "sample": "1 of the 4 batch elements (16 heads, 4096 tokens), fp32, 1 pass",
+                                   "kind": "port", "sample": "1 of the 4 batch elements (16 heads, 4096 tokens), fp32, median of 10 passes",
                                    "seconds": sec}
         print(json.dumps(out))
     if world > 1:
