@@ -109,7 +109,7 @@ struct Cfg {
   static constexpr int SMEM_BYTES = SMEM_TAIL + TAIL_BYTES + 1024;  // + alignment slack
 };
 
-// Bounded wait whose verdict is uniform across the warp (warp-collective TMEM ops follow it).
+// Bounded wait whose outcome is uniform across the warp (warp-collective TMEM ops follow it).
 __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
   return __all_sync(0xffffffffu, mbar_wait(bar, parity, status, code));
 }
