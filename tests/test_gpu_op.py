@@ -183,3 +183,43 @@ def test_strided_inputs_match_contiguous(cuda):
     o2 = attentions.flashmvpa(qs, *bias, ks, *rel, vs, **kw)
     assert o2.stride() == qs.stride()
     assert torch.equal(o1, o2)
+
+
+@pytest.mark.parametrize("shape", [(2, 4, 2, 12, 32, 64), (1, 2, 1, 13, 128, 128)])
+def test_bf16_backward_strided_inputs_match_contiguous(cuda, shape):
+    """The layer hands the tensor-core kernels strided head views of (B, N, heads, D) projection
+    buffers and autograd hands back a strided dO: gradients must equal those of the contiguous call
+    (dq, dk, dv bit for bit; the relative-key and bias gradients are summed with atomics, so to 1e-2)."""
+    import attentions
+    g = random_case(11, *shape)
+    B, H, Hkv, T, C, D = shape
+    kw = dict(causal=True, sm_scale=float(g["sm_scale"]), window_size=10)
+    bf = lambda a: torch.tensor(a, device=cuda, dtype=torch.bfloat16)
+
+    def run(strided):
+        small = {k: bf(g[k]).requires_grad_(True) for k in ("u", "v", "z", "r_time", "r_chan")}
+        big = {}
+        for k in ("q", "k", "val"):
+            x = bf(g[k])
+            big[k] = (x.permute(0, 2, 1, 3).contiguous() if strided else x).requires_grad_(True)
+        view = (lambda x: x.permute(0, 2, 1, 3)) if strided else (lambda x: x)
+        do = bf(g["do"])
+        if strided:
+            do = do.permute(0, 2, 1, 3).contiguous().permute(0, 2, 1, 3)
+            assert not view(big["q"]).is_contiguous() and not do.is_contiguous()
+        o = attentions.flashmvpa(view(big["q"]), *[small[k].view(1, Hkv, 1, D) for k in ("u", "v", "z")],
+                                 view(big["k"]), small["r_time"].view(1, Hkv, T, D),
+                                 small["r_chan"].view(1, Hkv, C, D), view(big["val"]), **kw)
+        o.backward(do)
+        grads = {k: view(big[k].grad) for k in big}
+        grads.update({k: small[k].grad for k in small})
+        return o, grads
+
+    o1, g1 = run(False)
+    o2, g2 = run(True)
+    assert torch.equal(o1, o2)
+    for k in ("q", "k", "val"):
+        assert torch.equal(g1[k], g2[k]), k
+    for k in ("u", "v", "z", "r_time", "r_chan"):
+        a, b = g1[k].float(), g2[k].float()
+        assert (a - b).abs().max() <= 1e-2 * max(1.0, a.abs().max().item()), k
