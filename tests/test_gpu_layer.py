@@ -51,3 +51,27 @@ def test_layer_bf16_tensor_core_path(cuda):
         out, _ = m(x, pos, chan)
     assert out.dtype == torch.bfloat16 and out.is_contiguous()
     assert np.abs(out.float().cpu().numpy() - g["out"]).max() <= 2e-2 * max(1.0, np.abs(g["out"]).max())
+
+
+def test_layer_bf16_backward_through_tensor_core_kernels(cuda):
+    """Training path of the layer in bf16-true: the strided head views and the strided dO go through the
+    tcgen05 backward; input and parameter gradients within 3e-2 * max|reference| (measured <= 1.1e-2) of the fp32 reference
+    layer's (bf16 projections and bf16 gradient tensors set the error, not the attention kernels)."""
+    import layers
+    g = load_golden("e128_mha", "layer")
+    B, H, Hkv, T, C, D = (int(x) for x in g["dims"])
+    m = layers.MVPFormerGQAFlashAttention(_cfg(H, Hkv, D, T), layer_idx=0).eval().to(cuda)
+    m.load_state_dict({k[3:]: torch.tensor(v) for k, v in g.items() if k.startswith("sd.")}, strict=True)
+    m = m.to(torch.bfloat16)
+    x, pos, chan = (torch.tensor(g[k], device=cuda, dtype=torch.bfloat16).requires_grad_(True)
+                    for k in ("x", "pos", "chan"))
+    out, _ = m(x, pos, chan)
+    out.backward(torch.tensor(g["gout"], device=cuda, dtype=torch.bfloat16))
+    worst = {}
+    for t, k in ((x, "dx"), (pos, "dpos"), (chan, "dchan")):
+        worst[k] = np.abs(t.grad.float().cpu().numpy() - g[k]).max() / max(1.0, np.abs(g[k]).max())
+    for k, p in m.named_parameters():
+        ref = g["grad." + k]
+        worst[k] = np.abs(p.grad.float().cpu().numpy() - ref).max() / max(1.0, np.abs(ref).max())
+    print("bf16 layer gradient errors / max|ref|:", {k: round(float(v), 4) for k, v in worst.items()})
+    assert max(worst.values()) <= 3e-2, worst
