@@ -266,8 +266,12 @@ def time_layer(torch, dev, flush, reps=10, warm=3):
             kv[:, :, Hkv:].permute(0, 2, 1, 3).contiguous()
             o.permute(0, 2, 1, 3).contiguous()
         copies_ms = timed(copies)
+    # training step of the layer: forward + backward (parameter and input gradients; gradients accumulate)
+    xg, gout = x.clone().requires_grad_(True), torch.randn_like(x)
+    train_ms = timed(lambda: m(xg, pos, chan)[0].backward(gout))
     return {"ms": layer_ms, "tokens_per_s": N / (layer_ms * 1e-3),
-            "head_split_merge_copies_avoided_ms": copies_ms}
+            "head_split_merge_copies_avoided_ms": copies_ms,
+            "fwd_bwd_ms": train_ms, "fwd_bwd_tokens_per_s": N / (train_ms * 1e-3)}
 
 
 def main():
