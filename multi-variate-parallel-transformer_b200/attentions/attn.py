@@ -122,14 +122,22 @@ def flash_mvpa(q, q_bias, q_btime, q_bchan, k_glob, k_time, k_chan, v, causal, s
     (`attentions/attn.py:1335-1336`) and the same shape checks raise
     (`:1339, 1344`).  `sequence_parallel` only chose a launch geometry in the
     reference (`:1165-1172`) and is accepted and ignored.  Structured attention dropout
-    (`:1052-1062`) and runs without the relative terms are not implemented: they raise.
+    (`:1052-1062`) and runs with both relative terms off are not implemented: they raise.
 
     `q_time_range=(t0, n)` (an extension, forward only): `q` holds only the tokens of time steps
     [t0, t0+n) while the keys, values and relative keys describe the whole sequence — what one
     rank computes when a long sample is sharded by query time blocks (`mvpa_shard`).
     """
-    if not (rel_bias_time and rel_bias_chan):
-        raise NotImplementedError("flash_mvpa: both relative terms are required (as the layer uses it)")
+    if not (rel_bias_time or rel_bias_chan):
+        raise NotImplementedError("flash_mvpa: at least one relative term is required (without them the "
+                                  "reference runs a plain windowed attention, which these kernels are not)")
+    # One term switched off: the reference kernels skip it and change nothing else
+    # (`attentions/attn.py:187-216, 241-308`), which is the same attention with that term's relative key
+    # at zero; its key and its query bias then receive zero gradients, as in the reference.
+    if not rel_bias_time:
+        k_time = k_time * 0
+    if not rel_bias_chan:
+        k_chan = k_chan * 0
     if p_drop and p_drop > 0:
         raise NotImplementedError("flash_mvpa: attention dropout is not implemented; use p_drop=0")
     q_heads, kv_heads = q.shape[1], v.shape[1]

@@ -223,3 +223,39 @@ def test_bf16_backward_strided_inputs_match_contiguous(cuda, shape):
     for k in ("u", "v", "z", "r_time", "r_chan"):
         a, b = g1[k].float(), g2[k].float()
         assert (a - b).abs().max() <= 1e-2 * max(1.0, a.abs().max().item()), k
+
+
+@pytest.mark.parametrize("off", ["time", "chan"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_one_relative_term_switched_off(cuda, off, dtype):
+    """`rel_bias_time=False` / `rel_bias_chan=False`: the reference kernels skip that term only
+    (`attn.py:187-216`); oracle = the same attention with that term's relative key at zero."""
+    import attentions
+    shape = (1, 2, 1, 13, 32, 64)
+    B, H, Hkv, T, C, D = shape
+    dt = getattr(torch, dtype)
+    g = random_case(400, *shape)
+    if dt == torch.bfloat16:
+        g = _rounded(g)
+    gz = dict(g)
+    gz["r_time" if off == "time" else "r_chan"] = np.zeros_like(g["r_time" if off == "time" else "r_chan"])
+    ref_o, _ = mo.mvpa_forward(*_oracle_args(gz), float(g["sm_scale"]))
+    ref = mo.mvpa_backward(*_oracle_args(gz), g["do"], float(g["sm_scale"]))
+    t = {k: torch.tensor(g[k], device=cuda, dtype=dt, requires_grad=True)
+         for k in ("q", "u", "v", "z", "k", "r_time", "r_chan", "val")}
+    o = attentions.flashmvpa(
+        t["q"], t["u"].view(1, Hkv, 1, D), t["v"].view(1, Hkv, 1, D), t["z"].view(1, Hkv, 1, D),
+        t["k"], t["r_time"].view(1, Hkv, T, D), t["r_chan"].view(1, Hkv, C, D), t["val"],
+        causal=True, sm_scale=float(g["sm_scale"]), window_size=10, p_drop=0,
+        rel_bias_time=off != "time", rel_bias_chan=off != "chan")
+    tol = BF16_ABS if dt == torch.bfloat16 else F32_REL
+    assert np.abs(_np(o) - ref_o).max() <= tol * max(1.0, np.abs(ref_o).max())
+    o.backward(torch.tensor(g["do"], device=cuda, dtype=dt))
+    dead = ("r_time", "v") if off == "time" else ("r_chan", "z")   # the skipped term's key and query bias
+    for key, gk in zip(("q", "u", "v", "z", "k", "r_time", "r_chan", "val"), GRADS):
+        if key in dead:
+            assert float(t[key].grad.abs().max()) == 0.0, key
+            continue
+        r = ref[gk]
+        err = np.abs(_np(t[key].grad).reshape(r.shape) - r).max()
+        assert err <= tol * max(1.0, np.abs(r).max()), (gk, err)
