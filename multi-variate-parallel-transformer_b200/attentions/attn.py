@@ -11,6 +11,7 @@ autograd.  There is no CPU path: tensors must live on a CUDA device.
 from __future__ import annotations
 
 import ctypes
+import math
 import os
 
 import torch
@@ -122,7 +123,8 @@ def flash_mvpa(q, q_bias, q_btime, q_bchan, k_glob, k_time, k_chan, v, causal, s
     (`attentions/attn.py:1335-1336`) and the same shape checks raise
     (`:1339, 1344`).  `sequence_parallel` only chose a launch geometry in the
     reference (`:1165-1172`) and is accepted and ignored.  Structured attention dropout
-    (`:1052-1062`) and runs with both relative terms off are not implemented: they raise.
+    (`:1052-1062`) is applied to V on the way in (see below); runs with both relative terms off are
+    not implemented and raise.
 
     `q_time_range=(t0, n)` (an extension, forward only): `q` holds only the tokens of time steps
     [t0, t0+n) while the keys, values and relative keys describe the whole sequence — what one
@@ -138,8 +140,8 @@ def flash_mvpa(q, q_bias, q_btime, q_bchan, k_glob, k_time, k_chan, v, causal, s
         k_time = k_time * 0
     if not rel_bias_chan:
         k_chan = k_chan * 0
-    if p_drop and p_drop > 0:
-        raise NotImplementedError("flash_mvpa: attention dropout is not implemented; use p_drop=0")
+    if p_drop and not 0 < p_drop < 1:
+        raise ValueError(f"flash_mvpa: p_drop must be in [0, 1), got {p_drop}")
     q_heads, kv_heads = q.shape[1], v.shape[1]
     assert q_heads % kv_heads == 0, "Q heads must be divisible by KV heads."
     n_ctx, time_ctx, chan_ctx = k_glob.shape[2], k_time.shape[2], k_chan.shape[2]
@@ -153,6 +155,18 @@ def flash_mvpa(q, q_bias, q_btime, q_bchan, k_glob, k_time, k_chan, v, causal, s
     assert q.shape[-1] == k_glob.shape[-1] == v.shape[-1]
     assert q.shape[-1] in {16, 32, 64, 128}
     D = q.shape[-1]
+    if p_drop and p_drop > 0:
+        # Structured dropout of the reference (`attentions/attn.py:1052-1062, 316-321`): whole key time
+        # steps and key channels are dropped, each with probability 1 - sqrt(1 - p_drop), and the kept
+        # probabilities are divided by 1 - p_drop after the softmax denominator is taken.  The mask depends
+        # on the key alone, so P_dropped V = P (mask V / (1 - p_drop)): one elementwise pass over V, and
+        # autograd carries the mask into dV.  Same draws in the same order as the reference (channels, then
+        # time steps), so a generator seeded alike gives the same mask.
+        p_per_dim = 1 - math.sqrt(1 - p_drop)
+        chan_keep = torch.rand(chan_ctx, device=q.device, generator=generator) > p_per_dim
+        time_keep = torch.rand(time_ctx, device=q.device, generator=generator) > p_per_dim
+        keep = (time_keep[:, None] & chan_keep[None, :]).reshape(1, 1, n_ctx, 1)
+        v = v * (keep.to(v.dtype) / (1 - p_drop))
     u, vt, z = (x.reshape(kv_heads, D) for x in (q_bias, q_btime, q_bchan))
     return FlashMVPA.apply(q, u, vt, z, k_glob, k_time.reshape(kv_heads, time_ctx, D),
                            k_chan.reshape(kv_heads, chan_ctx, D), v, sm_scale, window_size, q_time)

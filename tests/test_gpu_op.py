@@ -259,3 +259,46 @@ def test_one_relative_term_switched_off(cuda, off, dtype):
         r = ref[gk]
         err = np.abs(_np(t[key].grad).reshape(r.shape) - r).max()
         assert err <= tol * max(1.0, np.abs(r).max()), (gk, err)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_structured_dropout_is_a_key_mask_on_v(cuda, dtype):
+    """`p_drop > 0` (`attn.py:1052-1062, 316-321`): key time steps and key channels are dropped with
+    probability 1 - sqrt(1 - p) each, kept probabilities divided by 1 - p after the softmax sum.
+    Oracle: the same draws from a generator seeded alike (channels first, then time steps), applied
+    to V.  Forward and all gradients."""
+    import math
+    import attentions
+    shape = (1, 2, 1, 13, 32, 64)
+    B, H, Hkv, T, C, D = shape
+    p_drop = 0.3
+    dt = getattr(torch, dtype)
+    g = random_case(500, *shape)
+    if dt == torch.bfloat16:
+        g = _rounded(g)
+    gen = torch.Generator(device=cuda).manual_seed(1234)
+    p_dim = 1 - math.sqrt(1 - p_drop)
+    chan_keep = (torch.rand(C, device=cuda, generator=gen) > p_dim).cpu().numpy()
+    time_keep = (torch.rand(T, device=cuda, generator=gen) > p_dim).cpu().numpy()
+    keep = (time_keep[:, None] & chan_keep[None, :]).reshape(1, 1, T * C, 1)
+    assert 0 < keep.sum() < keep.size                      # the seed drops something and keeps something
+    scale = keep.astype(np.float32) / (1 - p_drop)
+    gd = dict(g)
+    gd["val"] = g["val"] * scale
+    ref_o, _ = mo.mvpa_forward(*_oracle_args(gd), float(g["sm_scale"]))
+    ref = dict(mo.mvpa_backward(*_oracle_args(gd), g["do"], float(g["sm_scale"])))
+    ref["dval"] = ref["dval"] * scale                        # chain rule through the mask
+    t = {k: torch.tensor(g[k], device=cuda, dtype=dt, requires_grad=True)
+         for k in ("q", "u", "v", "z", "k", "r_time", "r_chan", "val")}
+    o = attentions.flashmvpa(
+        t["q"], t["u"].view(1, Hkv, 1, D), t["v"].view(1, Hkv, 1, D), t["z"].view(1, Hkv, 1, D),
+        t["k"], t["r_time"].view(1, Hkv, T, D), t["r_chan"].view(1, Hkv, C, D), t["val"],
+        causal=True, sm_scale=float(g["sm_scale"]), window_size=10, p_drop=p_drop,
+        generator=torch.Generator(device=cuda).manual_seed(1234))
+    tol = 3e-2 if dt == torch.bfloat16 else F32_REL           # bf16: V / (1 - p) is rounded once more
+    assert np.abs(_np(o) - ref_o).max() <= tol * max(1.0, np.abs(ref_o).max())
+    o.backward(torch.tensor(g["do"], device=cuda, dtype=dt))
+    for key, gk in zip(("q", "u", "v", "z", "k", "r_time", "r_chan", "val"), GRADS):
+        r = ref[gk]
+        err = np.abs(_np(t[key].grad).reshape(r.shape) - r).max()
+        assert err <= tol * max(1.0, np.abs(r).max()), (gk, err)

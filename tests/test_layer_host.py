@@ -56,9 +56,13 @@ def test_operator_refuses_cpu_tensors():
     with pytest.raises(RuntimeError, match="CUDA"):
         attentions.flashmvpa(q, b, b, b, q, torch.zeros(1, 2, 2, 16), torch.zeros(1, 2, 2, 16), q,
                              causal=True, sm_scale=0.25, window_size=10)
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(NotImplementedError):   # both relative terms off: a plain windowed attention
         attentions.flashmvpa(q, b, b, b, q, torch.zeros(1, 2, 2, 16), torch.zeros(1, 2, 2, 16), q,
-                             causal=True, sm_scale=0.25, window_size=10, p_drop=0.1)
+                             causal=True, sm_scale=0.25, window_size=10, rel_bias_time=False,
+                             rel_bias_chan=False)
+    with pytest.raises(ValueError):
+        attentions.flashmvpa(q, b, b, b, q, torch.zeros(1, 2, 2, 16), torch.zeros(1, 2, 2, 16), q,
+                             causal=True, sm_scale=0.25, window_size=10, p_drop=1.0)
     with pytest.raises(AssertionError):
         attentions.flashmvpa(q, b, b, b, q, torch.zeros(1, 2, 3, 16), torch.zeros(1, 2, 2, 16), q,
                              causal=True, sm_scale=0.25)
