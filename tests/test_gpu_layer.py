@@ -75,3 +75,25 @@ def test_layer_bf16_backward_through_tensor_core_kernels(cuda):
         worst[k] = np.abs(p.grad.float().cpu().numpy() - ref).max() / max(1.0, np.abs(ref).max())
     print("bf16 layer gradient errors / max|ref|:", {k: round(float(v), 4) for k, v in worst.items()})
     assert max(worst.values()) <= 3e-2, worst
+
+
+def test_layer_training_mode_with_attention_dropout(cuda):
+    """`model.train()` with `attn_pdrop > 0` (the shipped configs train that way): the layer passes
+    `p_drop` to the operator as the reference Flash layer does (`layers/mvpa.py:391-397`); the step runs,
+    gradients are finite, and the output differs from the eval-mode one."""
+    import layers
+    g = load_golden("e128_mha", "layer")
+    B, H, Hkv, T, C, D = (int(x) for x in g["dims"])
+    m = layers.MVPFormerGQAFlashAttention(_cfg(H, Hkv, D, T), layer_idx=0).to(cuda).to(torch.bfloat16)
+    x, pos, chan = (torch.tensor(g[k], device=cuda, dtype=torch.bfloat16).requires_grad_(True)
+                    for k in ("x", "pos", "chan"))
+    m.eval()
+    with torch.no_grad():
+        ref, _ = m(x, pos, chan)
+    m.train()
+    torch.manual_seed(0)
+    out, _ = m(x, pos, chan)
+    out.float().square().mean().backward()
+    assert torch.isfinite(out).all() and not torch.equal(out, ref)
+    for t in (x, pos, chan, *m.parameters()):
+        assert t.grad is not None and torch.isfinite(t.grad).all()
