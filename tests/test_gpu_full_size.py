@@ -135,3 +135,31 @@ def test_forward_with_score_jumps_between_key_tiles(cuda, gain):
     b = run({n: x.float().contiguous() for n, x in t.items()})
     assert torch.isfinite(a).all()
     assert (a - b).abs().max() <= 2e-2 * b.abs().max(), float((a - b).abs().max())
+
+
+def test_config5_full_batch_last_element_equals_single_sample_run(cuda):
+    """The largest configuration BASELINE names (config 5: B 32 x 16 heads / 8 kv heads x 16384 tokens,
+    D 128, bf16; q alone is 2.1 GB, byte offsets pass 2^31): forward and backward of the whole batch,
+    then the last and a middle batch element again as single-sample calls on the same data — O, dq, dk,
+    dv must be bit-identical (batch elements do not interact; any 32-bit offset overflow would show)."""
+    import attentions
+    B, H, Hkv, T, C, D = 32, 16, 8, 128, 128, 128
+    N = T * C
+    g = torch.Generator(device=cuda).manual_seed(5)
+    r = lambda *s: torch.randn(*s, generator=g, device=cuda, dtype=torch.bfloat16)
+    q, k, v, do = r(B, H, N, D), r(B, Hkv, N, D), r(B, Hkv, N, D), r(B, H, N, D)
+    small = [r(1, Hkv, 1, D) for _ in range(3)] + [r(1, Hkv, T, D), r(1, Hkv, C, D)]
+    kw = dict(causal=True, sm_scale=D ** -0.5, window_size=10)
+
+    def step(qq, kk, vv, dd):
+        qq, kk, vv = (x.detach().requires_grad_(True) for x in (qq, kk, vv))
+        o = attentions.flashmvpa(qq, small[0], small[1], small[2], kk, small[3], small[4], vv, **kw)
+        o.backward(dd)
+        return o.detach(), qq.grad, kk.grad, vv.grad
+
+    full = step(q, k, v, do)
+    assert all(torch.isfinite(x).all() for x in full)
+    for b in (B - 1, B // 2):
+        one = step(q[b:b + 1], k[b:b + 1], v[b:b + 1], do[b:b + 1])
+        for name, a, c in zip(("o", "dq", "dk", "dv"), full, one):
+            assert torch.equal(a[b:b + 1], c), (b, name)
