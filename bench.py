@@ -38,6 +38,9 @@ WORKLOADS = {
     # one sample-layer of BASELINE config 5 (the 16k-token target of the north star)
     "16k": (dict(B=1, H=16, Hkv=8, T=128, C=128, D=128, window=10),
             "16k tokens: bf16 fwd, B1 x 16 heads / 8 kv heads x 16384 tokens (128 ch x 128 seg), head_dim 128"),
+    # one layer of BASELINE config 5 at its full batch (4.3 GB of q, k, v per step)
+    "cfg5": (dict(B=32, H=16, Hkv=8, T=128, C=128, D=128, window=10),
+             "cfg5 layer: bf16 fwd, B32 x 16 heads / 8 kv heads x 16384 tokens (128 ch x 128 seg), head_dim 128"),
 }
 WORKLOAD, NAME = WORKLOADS["cfg2"]
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the forward kernel, from the ncu
@@ -63,12 +66,18 @@ def flops_bwd(B, H, T, C, D, window=10, **_):
     return B * H * (2 * D * (2 * p_c + 3 * p_w) + 6 * D * N * (T + C))
 
 
-def peaks():
+def peaks(sustained=False):
+    """Burst figure for kernels of under a millisecond timed alone; the sustained one for steps of tens of
+    milliseconds, which run under the power cap (the config-5 workload)."""
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
             m = json.load(f)
+        if sustained:
+            return float(m["bf16_tflops_sustained"]), "measured (MEASURED_PEAKS.json bf16_tflops_sustained)"
         return float(m["bf16_tflops"]), "measured (MEASURED_PEAKS.json bf16_tflops, burst)"
     except Exception:
+        if sustained:
+            return 1400.0, "fallback (1.4 PFLOP/s sustained, earlier pool measurement)"
         return 1590.0, "fallback (1.59 PFLOP/s, earlier pool measurement)"
 
 
@@ -403,7 +412,7 @@ def main():
     e2e_val = world * f["f_alg"] * args.steps / (float(e2e_ms.item()) * 1e-3) / 1e12
 
     if rank == 0:
-        peak, peak_src = peaks()
+        peak, peak_src = peaks(sustained=args.workload == "cfg5")
         kernel_ms = statistics.mean(ms)
         achieved = f["f_alg"] / (kernel_ms * 1e-3) / 1e12
         out = {
