@@ -63,3 +63,12 @@ def test_workspace_queries():
     p16 = _prob(B=2, H=4, Hkv=2, T=8, C=4, D=64, dtype=nat.MVPA_F16)
     assert lib.mvpa_fwd_workspace_bytes(ctypes.byref(p16)) == 0
     assert lib.mvpa_bwd_workspace_bytes(ctypes.byref(p16)) == need
+
+
+def test_python_constants_match_the_header():
+    """Element-type codes of the ctypes shim are the header's `#define`s."""
+    text = open(os.path.join(ROOT, "include", "mvpa.h")).read()
+    defs = {m.group(1): int(m.group(2)) for m in re.finditer(r"#define\s+(MVPA_[A-Z0-9_]+)\s+\(?(-?\d+)\)?", text)}
+    for name in ("MVPA_F32", "MVPA_BF16", "MVPA_F16"):
+        assert defs[name] == getattr(nat, name), name
+    assert defs["MVPA_OK"] == 0 and defs["MVPA_ERR_DTYPE"] == -2 and defs["MVPA_ERR_SHAPE"] == -1
