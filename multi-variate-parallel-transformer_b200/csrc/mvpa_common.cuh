@@ -51,6 +51,18 @@ void set_error(const char* fmt, ...);
 void count_launch(int n = 1);
 
 // fp32 CUDA-core kernels (any T, C; D in {16,32,64,128}); element type float or bf16.
+// Order in which the tensor-core kernels' CTAs take their work.  Tile-major (all batch x head pairs of the
+// heaviest tile first) balances best, but the CTAs resident together then stream the K/V (or Q'/dO) of up
+// to 148/g different kv heads: once that set is several times the L2, every CTA reads from DRAM.  Past
+// 256 MB the kernels switch to kv-head-major: the CTAs of one kv head (all its query tiles and group heads)
+// are adjacent, so the operands they share stay in the L2 (tiles still heaviest first inside a head).
+// Measured: at 592 MB (B 32 x 8 kv heads x 16k tokens, D 128) kv-head-major is 15 % (forward) and 32 %
+// (forward + backward) faster; at 128 MB (B 8 x 16 heads x 4k tokens, D 64) tile-major is 6-13 % faster.
+inline int kv_major_order(int B, int Hkv, int g, int N, int D) {
+  const int64_t heads = (int64_t)B * Hkv < (148 + g - 1) / g ? (int64_t)B * Hkv : (148 + g - 1) / g;
+  return heads * 2 * N * D * 2 > (int64_t)256 * 1024 * 1024 ? 1 : 0;
+}
+
 int simt_fwd(const Args& a, int dtype, cudaStream_t s);
 int simt_bwd(const BwdArgs& b, int dtype, cudaStream_t s);
 size_t simt_bwd_workspace_floats(const mvpa_problem* p);

@@ -70,6 +70,7 @@ struct BqArgs {
   float* offw;         // (B*H, N)     that max minus L
   float* tbw;          // (B*H, T, N)  temporal scores, log2 units
   int B, H, Hkv, T, C, g, window, n_qt;
+  int kv_major;  // CTA order: see kv_major_order()
   float c2, sm_scale;
   int* status;
   long long* trace;
@@ -187,8 +188,17 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int BH = p.B * p.H;
-  const int I = p.n_qt - 1 - (int)(blockIdx.x / BH);
-  const int bh = blockIdx.x % BH, b = bh / p.H, h = bh % p.H, hk = h / p.g;
+  int I, bh;
+  if (p.kv_major) {
+    const int per = p.n_qt * p.g, grp = (int)(blockIdx.x / per), r = (int)(blockIdx.x % per);
+    I = p.n_qt - 1 - r / p.g;
+    bh = grp * p.g + r % p.g;  // grp = b * Hkv + hk
+  } else {
+    I = p.n_qt - 1 - (int)(blockIdx.x / BH);
+    bh = blockIdx.x % BH;
+  }
+  const int b = bh / p.H, h = bh % p.H, hk = h / p.g;
+  const int cta_slot = (p.n_qt - 1 - I) * BH + bh;  // index of this CTA's per-CTA outputs, whatever the order
   const int n_tiles = I + 1;
   const int n_light = light_tiles(I, TPB, p.window, p.n_qt);
   // Visit order: the light tiles 0 .. n_light-1 first, then the dense ones (natural key order).  In the
@@ -784,7 +794,7 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
     softmax_bar();
     if (row < DW) {  // fixed summation order: deterministic
       const float* c4 = cs + wg * 4 * DW + row;
-      p.cs_dq[(size_t)blockIdx.x * D + wg * DW + row] = (c4[0] + c4[DW]) + (c4[2 * DW] + c4[3 * DW]);
+      p.cs_dq[(size_t)cta_slot * D + wg * DW + row] = (c4[0] + c4[DW]) + (c4[2 * DW] + c4[3 * DW]);
     }
     softmax_bar();
     BTRACE(6);
@@ -974,6 +984,7 @@ struct BkArgs {
   __nv_bfloat16 *dk, *dv;
   int64_t dk_sb, dk_sh, dk_sn, dv_sb, dv_sh, dv_sn;
   int B, H, Hkv, T, C, g, window, n_qt;
+  int kv_major;  // CTA order: see kv_major_order()
   float c2, sm_scale;
   int* status;
   long long* trace;
@@ -1027,8 +1038,10 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int BK = p.B * p.Hkv;
-  const int J = (int)(blockIdx.x / BK);  // earliest key tiles (seen by the most query tiles) first
-  const int bk = blockIdx.x % BK, b = bk / p.Hkv, hk = bk % p.Hkv;
+  // earliest key tiles (seen by the most query tiles) first, over all kv heads or inside one
+  const int J = p.kv_major ? (int)(blockIdx.x % p.n_qt) : (int)(blockIdx.x / BK);
+  const int bk = p.kv_major ? (int)(blockIdx.x / p.n_qt) : (int)(blockIdx.x % BK);
+  const int b = bk / p.Hkv, hk = bk % p.Hkv;
   const int n_i = p.n_qt - J;            // query tiles J .. n_qt-1
   const int T = p.T, C = p.C;
   // Query tile i is "light" for this key tile when every pair lies outside the content window:
@@ -1463,6 +1476,7 @@ int launch_kv(const BwdArgs& bw, const BqArgs& q, const void* qp, cudaStream_t s
   t.dv_sb = bw.dv_sb; t.dv_sh = bw.dv_sh; t.dv_sn = bw.dv_sn;
   t.B = a.B; t.H = a.H; t.Hkv = a.Hkv; t.T = a.T; t.C = a.C; t.g = a.g; t.window = a.window;
   t.n_qt = q.n_qt; t.c2 = a.c2; t.sm_scale = a.sm_scale; t.status = q.status;
+  t.kv_major = kv_major_order(a.B, a.Hkv, a.g, a.N, D);
   t.trace = q.trace == nullptr ? nullptr : q.trace + (size_t)64 * a.B * a.H * a.T;
   constexpr int smem = BkCfg<D>::SMEM_BYTES;
   static_assert(smem <= 232448, "shared memory budget");
@@ -1584,6 +1598,7 @@ int launch(const BwdArgs& bw, float* cs_dq, int* status, float* relc, float* rac
   t.B = a.B; t.H = a.H; t.Hkv = a.Hkv; t.T = a.T; t.C = a.C; t.g = a.g; t.window = a.window;
   constexpr int TPB = 128 / CP;
   t.n_qt = (a.T + TPB - 1) / TPB;
+  t.kv_major = kv_major_order(a.B, a.Hkv, a.g, a.N, D);
   t.c2 = a.c2; t.sm_scale = a.sm_scale;
   t.status = status;
   t.trace = nullptr;

@@ -76,6 +76,7 @@ struct TcArgs {
   int64_t o_sb, o_sh, o_sn;
   int B, H, Hkv, T, C, g, window, n_qt;
   int q_t0, q_tn, q_tiles;  // query time range of this call and its number of query tiles
+  int kv_major;             // CTA order: see kv_major_order()
   float c2;
   int* status;
   const float* relc;  // (Hkv, 256): vt.r_time[j] at [0,128), z.r_chan[j] at [128,256)
@@ -209,9 +210,17 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
   }
 #endif
   const int BH = p.B * p.H;
-  const int I_loc = p.q_tiles - 1 - (int)(blockIdx.x / BH);  // latest (heaviest) query tiles first
+  int I_loc, bh;  // latest (heaviest) query tiles first, over all heads or inside one kv head
+  if (p.kv_major) {
+    const int per = p.q_tiles * p.g, grp = (int)(blockIdx.x / per), r = (int)(blockIdx.x % per);
+    I_loc = p.q_tiles - 1 - r / p.g;
+    bh = grp * p.g + r % p.g;  // grp = b * Hkv + hk
+  } else {
+    I_loc = p.q_tiles - 1 - (int)(blockIdx.x / BH);
+    bh = blockIdx.x % BH;
+  }
   const int I = p.q_t0 / TPB + I_loc;                         // tile index in the whole sequence
-  const int bh = blockIdx.x % BH, b = bh / p.H, h = bh % p.H, hk = h / p.g;
+  const int b = bh / p.H, h = bh % p.H, hk = h / p.g;
   const int n_tiles = I + 1;
   const int n_light = light_tiles(I, TPB, p.window, p.n_qt);
   const int n_dense = n_tiles - n_light;
@@ -1025,6 +1034,7 @@ int launch(const Args& a, int* status, cudaStream_t s) {
   t.n_qt = (a.T + TPB - 1) / TPB;
   t.q_t0 = a.q_t0; t.q_tn = a.q_tn;
   t.q_tiles = (a.q_tn + TPB - 1) / TPB;
+  t.kv_major = kv_major_order(a.B, a.Hkv, a.g, a.N, D);
   if (a.q_t0 % TPB != 0) {
     set_error("query time range must start on a tile boundary: q_time_begin %d is not a multiple of %d", a.q_t0, TPB);
     return MVPA_ERR_ALIGNMENT;

@@ -141,7 +141,9 @@ def test_config5_full_batch_last_element_equals_single_sample_run(cuda):
     """The largest configuration BASELINE names (config 5: B 32 x 16 heads / 8 kv heads x 16384 tokens,
     D 128, bf16; q alone is 2.1 GB, byte offsets pass 2^31): forward and backward of the whole batch,
     then the last and a middle batch element again as single-sample calls on the same data — O, dq, dk,
-    dv must be bit-identical (batch elements do not interact; any 32-bit offset overflow would show)."""
+    dv must be bit-identical (batch elements do not interact; any 32-bit offset overflow would show).
+    At this size the kernels take their CTAs kv-head-major instead of tile-major, so this also checks that
+    order, including the per-CTA partial sums behind the bias gradients."""
     import attentions
     B, H, Hkv, T, C, D = 32, 16, 8, 128, 128, 128
     N = T * C
@@ -153,13 +155,22 @@ def test_config5_full_batch_last_element_equals_single_sample_run(cuda):
 
     def step(qq, kk, vv, dd):
         qq, kk, vv = (x.detach().requires_grad_(True) for x in (qq, kk, vv))
-        o = attentions.flashmvpa(qq, small[0], small[1], small[2], kk, small[3], small[4], vv, **kw)
+        sm = [x.detach().requires_grad_(True) for x in small]
+        o = attentions.flashmvpa(qq, sm[0], sm[1], sm[2], kk, sm[3], sm[4], vv, **kw)
         o.backward(dd)
-        return o.detach(), qq.grad, kk.grad, vv.grad
+        return (o.detach(), qq.grad, kk.grad, vv.grad), [x.grad.float() for x in sm]
 
-    full = step(q, k, v, do)
+    full, full_small = step(q, k, v, do)
     assert all(torch.isfinite(x).all() for x in full)
-    for b in (B - 1, B // 2):
-        one = step(q[b:b + 1], k[b:b + 1], v[b:b + 1], do[b:b + 1])
-        for name, a, c in zip(("o", "dq", "dk", "dv"), full, one):
-            assert torch.equal(a[b:b + 1], c), (b, name)
+    acc = [torch.zeros_like(x) for x in full_small]
+    for b in range(B):
+        one, one_small = step(q[b:b + 1], k[b:b + 1], v[b:b + 1], do[b:b + 1])
+        for a, x in zip(acc, one_small):
+            a += x
+        if b in (B - 1, B // 2):
+            for name, a, c in zip(("o", "dq", "dk", "dv"), full, one):
+                assert torch.equal(a[b:b + 1], c), (b, name)
+    # bias and relative-key gradients are sums over the batch: whole-batch call vs the sum of the
+    # single-sample calls (each rounded to bf16 once, hence the tolerance)
+    for name, a, c in zip(("du", "dv_bias", "dz", "dr_time", "dr_chan"), full_small, acc):
+        assert (a - c).abs().max() <= 2e-2 * max(1.0, c.abs().max().item()), name
