@@ -113,9 +113,8 @@ int mvpa_bwd(const mvpa_problem* p, const mvpa_tensor* q, const mvpa_tensor* k,
 /*
  * Forward for callers that must not allocate.  (No counterpart in the reference, which allocates
  * freely through torch.)  Some hosts of this library cannot call cudaMalloc on the path that runs
- * attention: a serving process that handed all device memory to its own pool at start-up, a
- * plugin whose host forbids allocator calls inside its execute hook, code running between
- * cudaStreamBeginCapture and cudaStreamEndCapture.  mvpa_fwd leaves the scratch to the caller;
+ * attention: a serving process that handed all device memory to its own pool at start-up, or a
+ * plugin whose host forbids allocator calls inside its execute hook.  mvpa_fwd leaves the scratch to the caller;
  * this variant of the bf16 tensor-core forward keeps its scratch (status word + per-kv-head
  * constants, 65 792 bytes) in a fixed array that is part of the library's device image, so each
  * GPU that loads the library holds those bytes until the process ends.
@@ -137,10 +136,31 @@ int mvpa_fwd_noalloc(const mvpa_problem* p, const mvpa_tensor* q, const mvpa_ten
                      void* cuda_stream);
 
 /* Reads back the status word the kernels of the last mvpa_fwd call left at the start of
- * `workspace` (every device-side wait is bounded; one that runs out records a code there and
- * the kernel returns instead of hanging).  Synchronises `cuda_stream`.  Returns MVPA_OK, or
+ * `workspace` (every device-side wait is bounded by a deadline on the GPU's nanosecond timer;
+ * one that runs out records a code there and the kernel returns instead of hanging).  Synchronises `cuda_stream`.  Returns MVPA_OK, or
  * MVPA_ERR_DEVICE with the code in the error text.  Has no counterpart in the reference. */
 int mvpa_workspace_status(const void* workspace, size_t workspace_bytes, void* cuda_stream);
+
+/* The same for mvpa_bwd: its kernels keep their status word inside the workspace, at an offset that
+ * depends on the problem.  `p`, `workspace`, `workspace_bytes` are the ones given to mvpa_bwd.
+ * Problems that run on the CUDA-core kernels (no device-side waits) always return MVPA_OK.
+ * Synchronises `cuda_stream`.  Has no counterpart in the reference. */
+int mvpa_bwd_status(const mvpa_problem* p, const void* workspace, size_t workspace_bytes,
+                    void* cuda_stream);
+
+/* The same for mvpa_fwd_noalloc: reads the status word of the built-in array on the current
+ * device (MVPA_OK if mvpa_fwd_noalloc has not run there yet).  Synchronises `cuda_stream`.
+ * Allocates nothing.  Has no counterpart in the reference. */
+int mvpa_noalloc_status(void* cuda_stream);
+
+/* Self-test of the bounded waits: launches a one-warp kernel that waits, with a deadline of
+ * `limit_us` microseconds (1 .. 1 000 000), on an mbarrier nothing arrives at.  The wait runs out,
+ * the kernel records its code in the status word at the start of `workspace` (>= 256 bytes) and
+ * returns; mvpa_workspace_status(workspace, ...) must then report MVPA_ERR_DEVICE.  Nothing
+ * faults or hangs; the product kernels' own deadline (two seconds) is not changed.
+ * Has no counterpart in the reference. */
+int mvpa_selftest_wait_timeout(void* workspace, size_t workspace_bytes, uint32_t limit_us,
+                               void* cuda_stream);
 
 /* Text of the last error raised on this host thread ("" if none).
  * Stands where the reference raises RuntimeError / assert

@@ -19,7 +19,7 @@ import torch
 import mvpa_native as _nat
 
 
-# MVPA_CHECK_STATUS=1: read the kernels' status word back after every forward (synchronises).
+# MVPA_CHECK_STATUS=1: read the kernels' status word back after every forward and backward (synchronises).
 _CHECK_STATUS = os.environ.get("MVPA_CHECK_STATUS", "0") == "1"
 
 
@@ -107,6 +107,8 @@ class FlashMVPA(torch.autograd.Function):
                               r[4], r[5], r[6], r[7], du.data_ptr(), dvt.data_ptr(), dz.data_ptr(),
                               drt.data_ptr(), drc.data_ptr(), ws.data_ptr(), nbytes, _stream())
         _nat.check(st, "mvpa_bwd")
+        if _CHECK_STATUS:  # debugging aid: synchronises the stream
+            _nat.check(lib.mvpa_bwd_status(ctypes.byref(prob), ws.data_ptr(), nbytes, _stream()), "mvpa_bwd kernels")
         dt = q.dtype
         return (dq, du.to(dt), dvt.to(dt), dz.to(dt), dk, drt.to(dt), drc.to(dt), dv, None, None, None)
 

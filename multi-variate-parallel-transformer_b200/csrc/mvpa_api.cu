@@ -21,6 +21,19 @@ void set_error(const char* fmt, ...) {
 
 void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
 
+int device_sm_count() {
+  constexpr int kMaxDevices = 64;
+  static std::atomic<int> cache[kMaxDevices];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+  int n = cache[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cache[dev].store(n, std::memory_order_relaxed);
+  }
+  return n;
+}
+
 namespace {
 
 size_t elem_size(int dtype) { return dtype == MVPA_F32 ? 4 : 2; }
@@ -211,11 +224,10 @@ int mvpa_fwd_noalloc(const mvpa_problem* p, const mvpa_tensor* q, const mvpa_ten
   return tc_fwd_static(a, (cudaStream_t)cuda_stream);
 }
 
-int mvpa_workspace_status(const void* workspace, size_t workspace_bytes, void* cuda_stream) {
-  if (workspace == nullptr || workspace_bytes < sizeof(int)) return MVPA_OK;  // nothing was recorded
+static int read_status_word(const int* word, cudaStream_t s) {
+  if (word == nullptr) return MVPA_OK;  // nothing was recorded
   int code = 0;
-  cudaStream_t s = (cudaStream_t)cuda_stream;
-  MVPA_CUDA_CHECK(cudaMemcpyAsync(&code, workspace, sizeof(int), cudaMemcpyDeviceToHost, s));
+  MVPA_CUDA_CHECK(cudaMemcpyAsync(&code, word, sizeof(int), cudaMemcpyDeviceToHost, s));
   MVPA_CUDA_CHECK(cudaStreamSynchronize(s));
   if (code != 0) {
     set_error("a kernel gave up a bounded wait (code %d) and returned early; outputs are invalid", code);
@@ -224,10 +236,41 @@ int mvpa_workspace_status(const void* workspace, size_t workspace_bytes, void* c
   return MVPA_OK;
 }
 
+int mvpa_workspace_status(const void* workspace, size_t workspace_bytes, void* cuda_stream) {
+  if (workspace == nullptr || workspace_bytes < sizeof(int)) return MVPA_OK;
+  return read_status_word(static_cast<const int*>(workspace), (cudaStream_t)cuda_stream);
+}
+
+int mvpa_bwd_status(const mvpa_problem* p, const void* workspace, size_t workspace_bytes, void* cuda_stream) {
+  if (check_problem(p) != MVPA_OK) return MVPA_ERR_SHAPE;
+  if (workspace == nullptr || workspace_bytes < mvpa_bwd_workspace_bytes(p)) {
+    set_error("mvpa_bwd_status: the workspace handed to mvpa_bwd (%zu bytes) is required",
+              mvpa_bwd_workspace_bytes(p));
+    return MVPA_ERR_WORKSPACE;
+  }
+  return read_status_word(bwd_status_word(p, workspace), (cudaStream_t)cuda_stream);
+}
+
+int mvpa_noalloc_status(void* cuda_stream) {
+  return read_status_word(tc_fwd_static_status_word(), (cudaStream_t)cuda_stream);
+}
+
+int mvpa_selftest_wait_timeout(void* workspace, size_t workspace_bytes, uint32_t limit_us, void* cuda_stream) {
+  if (workspace == nullptr || workspace_bytes < 256 || ((uintptr_t)workspace & 15) != 0) {
+    set_error("mvpa_selftest_wait_timeout: a 16-byte aligned workspace of at least 256 bytes is required");
+    return MVPA_ERR_WORKSPACE;
+  }
+  if (limit_us == 0 || limit_us > 1000000u) {
+    set_error("mvpa_selftest_wait_timeout: limit_us must be in [1, 1000000]");
+    return MVPA_ERR_SHAPE;
+  }
+  return selftest_wait_timeout(static_cast<int*>(workspace), limit_us, (cudaStream_t)cuda_stream);
+}
+
 const char* mvpa_last_error_string(void) { return g_error; }
 
 uint64_t mvpa_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
-int mvpa_abi_version(void) { return 2; }
+int mvpa_abi_version(void) { return 3; }
 
 }  // extern "C"

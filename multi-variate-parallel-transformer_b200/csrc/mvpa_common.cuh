@@ -51,15 +51,19 @@ void set_error(const char* fmt, ...);
 void count_launch(int n = 1);
 
 // fp32 CUDA-core kernels (any T, C; D in {16,32,64,128}); element type float or bf16.
+// Multiprocessors of the current device (cudaDevAttrMultiProcessorCount, cached per device; 148 on a B200).
+int device_sm_count();
+
 // Order in which the tensor-core kernels' CTAs take their work.  Tile-major (all batch x head pairs of the
-// heaviest tile first) balances best, but the CTAs resident together then stream the K/V (or Q'/dO) of up
-// to 148/g different kv heads: once that set is several times the L2, every CTA reads from DRAM.  Past
+// heaviest tile first) balances best, but the CTAs resident together (one per multiprocessor) then stream
+// the K/V (or Q'/dO) of up to SMs/g different kv heads: once that set is several times the L2, every CTA reads from DRAM.  Past
 // 256 MB the kernels switch to kv-head-major: the CTAs of one kv head (all its query tiles and group heads)
 // are adjacent, so the operands they share stay in the L2 (tiles still heaviest first inside a head).
 // Measured: at 592 MB (B 32 x 8 kv heads x 16k tokens, D 128) kv-head-major is 15 % (forward) and 32 %
 // (forward + backward) faster; at 128 MB (B 8 x 16 heads x 4k tokens, D 64) tile-major is 6-13 % faster.
 inline int kv_major_order(int B, int Hkv, int g, int N, int D) {
-  const int64_t heads = (int64_t)B * Hkv < (148 + g - 1) / g ? (int64_t)B * Hkv : (148 + g - 1) / g;
+  const int64_t resident = (device_sm_count() + g - 1) / g;
+  const int64_t heads = (int64_t)B * Hkv < resident ? (int64_t)B * Hkv : resident;
   return heads * 2 * N * D * 2 > (int64_t)256 * 1024 * 1024 ? 1 : 0;
 }
 
@@ -73,6 +77,8 @@ bool tc_fwd_supported(const Args& a);
 size_t tc_fwd_workspace_bytes(const mvpa_problem* p);
 int tc_fwd(const Args& a, void* workspace, size_t workspace_bytes, cudaStream_t s);
 int tc_fwd_static(const Args& a, cudaStream_t s);  // same, scratch in a built-in device array
+// Status word of the built-in array on the current device (nullptr before the first tc_fwd_static call there).
+const int* tc_fwd_static_status_word();
 
 // tcgen05 backward for bf16 (mvpa_tc_bwd.cu): dq, dk, dv, and per-kv-head accumulators of the
 // relative-key gradients; tc_bwd_bias turns those into dr_time / dr_chan / du / dvt / dz.
@@ -80,6 +86,12 @@ bool tc_bwd_q_supported(const Args& a);
 size_t tc_bwd_q_workspace_floats(const mvpa_problem* p);
 int tc_bwd_q(const BwdArgs& b, float* extra_workspace, cudaStream_t s);
 int tc_bwd_bias(const BwdArgs& b, float* extra_workspace, cudaStream_t s);
+size_t tc_bwd_status_offset_floats(const mvpa_problem* p);
+// Status word of the backward's kernels inside the caller's workspace (nullptr: this problem runs on
+// kernels without device-side waits).
+const int* bwd_status_word(const mvpa_problem* p, const void* workspace);
+// Wait self-test (mvpa_selftest.cu).
+int selftest_wait_timeout(int* status, unsigned limit_us, cudaStream_t s);
 
 template <typename T>
 __device__ __forceinline__ float to_f32(T x);

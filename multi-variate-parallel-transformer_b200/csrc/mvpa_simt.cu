@@ -801,6 +801,14 @@ size_t simt_bwd_workspace_floats(const mvpa_problem* p) {
   return (n + 63) & ~(size_t)63;
 }
 
+const int* bwd_status_word(const mvpa_problem* p, const void* workspace) {
+  if (!tc_path(p->dtype, p->D, p->C, p->T)) return nullptr;  // the CUDA-core kernels have no device-side waits
+  const size_t BH = (size_t)p->B * p->H, N = (size_t)p->T * p->C;
+  size_t used = BH * N + (tc_needs_dtb(p->D, p->C) ? BH * N * p->T : 0);
+  used = (used + 63) & ~(size_t)63;
+  return reinterpret_cast<const int*>(static_cast<const float*>(workspace) + used + tc_bwd_status_offset_floats(p));
+}
+
 void simt_bwd_carve(BwdArgs& b, float* ws, int dtype) {
   const Args& a = b.a;
   const size_t BH = (size_t)a.B * a.H, N = a.N;

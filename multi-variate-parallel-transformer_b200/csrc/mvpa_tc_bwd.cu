@@ -27,6 +27,7 @@
 #include "mvpa_common.cuh"
 #include "tc_ptx.cuh"
 #include "tc_tma_host.cuh"
+#include "tc_rel_const.cuh"
 
 namespace mvpa {
 namespace {
@@ -38,14 +39,6 @@ constexpr int kThreads = 384;  // warps 10, 11 only donate their registers
 constexpr int kTmemCols = 512;
 constexpr uint32_t kColS = 0;
 constexpr uint32_t kColDP = 128;
-
-// Optional in-kernel timeline of the query-side kernel (build with -DMVPA_TC_TRACE): 64 clock64
-// stamps per CTA behind the regular workspace.
-#ifdef MVPA_TC_TRACE
-#define BTRACE(slot) do { if (trace_on) p.trace[(size_t)blockIdx.x * 64 + (slot)] = clock64(); } while (0)
-#else
-#define BTRACE(slot) do { } while (0)
-#endif
 
 struct BqMaps {
   CUtensorMap q, k, v, dout, rt, rc;
@@ -73,7 +66,6 @@ struct BqArgs {
   int kv_major;  // CTA order: see kv_major_order()
   float c2, sm_scale;
   int* status;
-  long long* trace;
 };
 
 enum BarrierIndex {
@@ -120,27 +112,6 @@ __device__ __forceinline__ int light_tiles(int I, int TPB, int window, int n_qt)
   if (window <= 0 || I == n_qt - 1) return 0;
   const int x = I * TPB - TPB - window;
   return x < 0 ? 0 : x / TPB + 1;
-}
-
-__global__ void __launch_bounds__(256) rel_const_kernel(const __nv_bfloat16* __restrict__ vt,
-                                                        const __nv_bfloat16* __restrict__ z,
-                                                        const __nv_bfloat16* __restrict__ rt,
-                                                        const __nv_bfloat16* __restrict__ rc, float* __restrict__ relc,
-                                                        int T, int C, int D) {
-  const int hk = blockIdx.x, j = threadIdx.x & 127;
-  const bool is_t = threadIdx.x < 128;
-  const int rows = is_t ? T : C;
-  float acc = 0.f;
-  if (j < rows) {
-    const __nv_bfloat16* key = (is_t ? rt : rc) + ((size_t)hk * rows + j) * D;
-    const __nv_bfloat16* bias = (is_t ? vt : z) + (size_t)hk * D;
-    for (int d = 0; d < D; d += 2) {
-      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(key + d));
-      const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(bias + d));
-      acc += a.x * b.x + a.y * b.y;
-    }
-  }
-  relc[hk * 256 + threadIdx.x] = acc;
 }
 
 template <int D, int CP>
@@ -385,13 +356,8 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
       mma_commit(&bars[kBarAllDone]);
       // finish: dQ += dTB r_time + dCB r_chan  (autograd through `_rel_bias`, `attentions/attn.py:1305-1314`);
       // the softmax warps have put dTB / dCB of the tile's rows into TMEM as bf16
-#ifdef MVPA_TC_TRACE
-      const bool trace_on = true;
-#endif
       if (ok) ok = mbar_wait(&bars[kBarFinFull], 0, p.status, 125);
-      BTRACE(28);
       if (ok) ok = mbar_wait(&bars[kBarFinLoaded], 0, p.status, 126);
-      BTRACE(29);
       if (ok) {
         tc_fence_after();
         const DescHalves dfr = make_desc_halves_sw128(smem_u32(ring + 65536), HALF, 1024);
@@ -402,7 +368,6 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
         for (int kk = 0; kk < CP / 16; ++kk) mma_ts_h(tmem + kQDQ, tmem + kQDP + kk * 8, dfc, kk * 2048, idesc_q, 1u);
       }
       mma_commit(&bars[kBarFinDone]);
-      BTRACE(30);
       // Relative-key gradients of this tile's rows (autograd through `_rel_bias`, `attentions/attn.py:1305-1314`):
       //   R_t[j, d] = sum_i dTB[i, j] Q'[i, d],  R_c[j, d] = sum_i dCB[i, j] Q'[i, d]   (A = the bf16 tiles the
       //   softmax warps left in shared memory, keys-of-the-sum = query rows; B = Q' as MN-major operand)
@@ -435,10 +400,6 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
     // ------------------------------ softmax warps ------------------------------
     const int row = tid & 127;
     const int wg = tid >> 7;
-#ifdef MVPA_TC_TRACE
-    const bool trace_on = tid == 0;
-#endif
-    BTRACE(0);
     const int ti_loc = row / CP, c_i = row % CP;
     const int ti_abs = I * TPB + ti_loc;
     const bool row_valid = c_i < C && ti_abs < T;
@@ -459,7 +420,6 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
     const float delta_i = row_valid ? p.delta[n_row] : 0.f;
     softmax_bar();
     bool ok = warp_wait(&bars[kBarProMma], 0, p.status, 131);
-    BTRACE(1);
     if (ok) {
       tc_fence_after();
       // The prologue and the epilogue run once per CTA, so their instructions come from memory rather
@@ -493,7 +453,6 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
           put8(vb, c8 + 8);
         }
       }
-      BTRACE(32);
       // channel scores by |c_i - c_k| slot to shared memory (8-column chunks alternate between the warpgroups)
 #pragma unroll 1
       for (int c8 = 8 * wg; c8 < CP; c8 += 16) {
@@ -509,9 +468,7 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
       }
       tc_fence_before();
     }
-    BTRACE(33);
     softmax_bar();
-    BTRACE(34);
     float mc = 0.f;
     {
       // gather by key channel slot: g_k = CB[i, C-1-|c_i - c_k|]; first the row maximum, then fp16 values
@@ -538,9 +495,7 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
       for (int k = 0; k < NCH; ++k) mx = fmaxf(mx, gathered(k));
       if constexpr (!PAD) {  // the row maximum spans both warpgroups' columns
         s_max[wg * 128 + row] = mx;
-        BTRACE(35);
         softmax_bar();
-        BTRACE(36);
         mx = fmaxf(mx, s_max[(wg ^ 1) * 128 + row]);
       }
       mc = (mx == -INFINITY) ? 0.f : mx;
@@ -579,7 +534,6 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
       tc_fence_before();
       const bool store_cbl = ok && row_valid && (CP == 128 || wg == 0);
       if (store_cbl && wg == 0) p.offw[n_row] = mc - L_i;
-      BTRACE(37);
       if (ok) {
         const float4* u4 = reinterpret_cast<const float4*>(s_bias);
 #pragma unroll 1
@@ -652,7 +606,6 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
     }
     tc_fence_before();
     mbar_arrive(&bars[kBarProDone]);  // only now may a dP product overwrite the staged values
-    BTRACE(2);
     for (int s = 0; ok && s < n_tiles; ++s) {
       const bool dense = is_dense(s);
       const int J = tile_of(s);
@@ -678,7 +631,6 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
       }
       ok = warp_wait(&bars[kBarDpFull + (s & 1)], (s >> 1) & 1, p.status, 133);
       if (!ok) break;
-      if (s < 16) BTRACE(12 + s);
       tc_fence_after();
       if (dense) {
         // P' = exp2(S2 - L + log2 sm_scale), dS = P' (dP - delta)   (`attentions/attn.py:680`)
@@ -759,9 +711,7 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
       }
     }
     // ------------------------------- epilogue ---------------------------------
-    BTRACE(3);
     if (ok) ok = warp_wait(&bars[kBarAllDone], 0, p.status, 134);
-    BTRACE(4);
     // du = sum over rows of dq's content part (`attentions/attn.py:1305-1306`: q + q_bias feeds the content
     // term only): column sums of the accumulator before the relative terms are added to it
     // (32 rows of a warp are summed with a shuffle butterfly that halves the values per lane each round and
@@ -790,28 +740,24 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
         cs[(wg * 4 + (warp & 3)) * DW + c0 + lane] = v[0];
       }
     }
-    BTRACE(5);
     softmax_bar();
     if (row < DW) {  // fixed summation order: deterministic
       const float* c4 = cs + wg * 4 * DW + row;
       p.cs_dq[(size_t)cta_slot * D + wg * DW + row] = (c4[0] + c4[DW]) + (c4[2 * DW] + c4[3 * DW]);
     }
     softmax_bar();
-    BTRACE(6);
     // channel-score gradient: from key-channel slots to |c_i - c_k| slots, through shared memory
     float* sc = reinterpret_cast<float*>(ring);  // [128][CP]; every TMA load has been consumed by now
     if (CP == 128 || wg == 0) {
 #pragma unroll
       for (int k = 0; k < NCH; ++k) sc[row * CP + ((ck_base + k + 2 * row) & (CP - 1))] = dcb_acc[k];
     }
-    BTRACE(40);
     softmax_bar();
     if (CP < 128 && wg == 1) {  // both warpgroups hold sums for the same channel slots (different time steps)
 #pragma unroll
       for (int k = 0; k < NCH; ++k) sc[row * CP + ((k + 2 * row) & (CP - 1))] += dcb_acc[k];
     }
     softmax_bar();
-    BTRACE(42);
     // dCB[i, j], j = C-1-e, e = |c_i - c_k|, as bf16 pairs: into TMEM columns kQDP + j/2 (A operand of
     // dQ += dCB r_chan) and into a shared-memory tile [row][j] (A operand, transposed, of the dr_chan product).
     // Each warpgroup takes half of the slots.
@@ -845,11 +791,8 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
         tmem_st8(lane_base + kQDP + jb / 2 + m0, pkv);
       }
     }
-    BTRACE(43);
-    BTRACE(7);
     if constexpr (!TBS) __threadfence();  // this CTA's atomic row sums in dtb are complete before anyone re-reads them
     softmax_bar();
-    BTRACE(8);
     if (ok) {
       // dTB of the row (this thread's 64 of the 128 r_time rows) as bf16 pairs: A operand of dQ += dTB r_time
       // in TMEM, and the [row][j] tile in shared memory for the dr_time product
@@ -860,7 +803,6 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
           const uint4 w0 = *reinterpret_cast<const uint4*>(my + (((m8 / 4) ^ (row & 7)) << 4));
           const uint4 w1 = *reinterpret_cast<const uint4*>(my + (((m8 / 4 + 1) ^ (row & 7)) << 4));
           const uint32_t pk[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-          if (m8 == 0) BTRACE(46);
           tmem_st8(lane_base + kQS + 32 * wg + m8, pk);
         }
       } else {
@@ -875,25 +817,20 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
           uint32_t pk[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) pk[e] = pack_bf16(a[2 * (m8 + e)] * keep, a[2 * (m8 + e) + 1] * keep);
-          if (m8 == 0) BTRACE(46);
           tmem_st8(lane_base + kQS + 32 * wg + m8, pk);
           const int c0 = m8 / 4;  // 16-byte chunks c0 and c0 + 1 of this row's 128 bytes
           *reinterpret_cast<uint4*>(s_tbt + (((c0) ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
           *reinterpret_cast<uint4*>(s_tbt + (((c0 + 1) ^ (row & 7)) << 4)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
         }
       }
-      BTRACE(47);
       // a [16 x 128] tile of ones (K-major): column sums of dTB / dCB come out of the tensor core too
       *reinterpret_cast<uint4*>(ring + 32768 + tid * 16) = make_uint4(0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u);
       fence_proxy_async_smem();
-      BTRACE(45);
       tmem_st_wait();
     }
     tc_fence_before();
     mbar_arrive(&bars[kBarFinFull]);
-    BTRACE(9);
     if (ok) ok = warp_wait(&bars[kBarFinDone], 0, p.status, 135);
-    BTRACE(10);
     uint8_t* s_out = ring + 65536;  // dq tile as bf16, laid out like a Q tile (the relative keys are dead)
     if (ok) {
       tc_fence_after();
@@ -950,7 +887,6 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
         }
       }
     }
-    BTRACE(11);
     tc_fence_before();
   }
   __syncthreads();
@@ -987,7 +923,6 @@ struct BkArgs {
   int kv_major;  // CTA order: see kv_major_order()
   float c2, sm_scale;
   int* status;
-  long long* trace;
 };
 enum BkBarrier {
   kKvFull = 0, kQdoFull, kQdoFull1, kBkSdpFull, kPdsFull, kPairDone, kBkAllDone,
@@ -1227,14 +1162,9 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
     const int tt_base = (64 * wg) / CP;
     const int ck_base = CP == 128 ? 64 * wg : 0;
     bool ok = true;
-#ifdef MVPA_TC_TRACE
-    const bool trace_on = tid == 0;
-#endif
-    BTRACE(0);
     for (int s = 0; ok && s < n_dense; ++s) {
       int h, i;
       dense_pair(s, h, i);
-      if (s < 8) BTRACE(8 + 4 * s);
       const int ti_abs = i * TPB + ti_loc;
       const bool row_valid = c_i < C && ti_abs < T;
       const int N = T * C, n_loc = ti_abs * C + c_i;
@@ -1269,7 +1199,6 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
       }
       ok = warp_wait(&bars[kBkSdpFull], s & 1, p.status, 232);
       if (!ok) break;
-      if (s < 8) BTRACE(9 + 4 * s);
       tc_fence_after();
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
@@ -1309,9 +1238,7 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(&bars[kPdsFull]);
-      if (s < 8) BTRACE(10 + 4 * s);
     }
-    BTRACE(1);
     // ---- light pairs: P[i, k] = a_i[t_k] bc_i[c_k] straight into the operand layout ----
     // The row's data of pair l+1 is requested while pair l is processed: with nothing else to wait for,
     // the latency of these loads would otherwise be the whole cost of a light pair.
@@ -1352,7 +1279,6 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
     };
     Cursor cur{hk * p.g, J + dl}, nxt{hk * p.g, J + dl};  // pair l, pair l + 2 (the one to fetch)
     auto light_body = [&](int l, RowData& r) {
-      if (l >= 4 && l < 8) BTRACE(20 + 4 * (l - 4));
       const int i = cur.i;
       advance(cur, 1);
       const int bsel = l & 1;
@@ -1370,7 +1296,6 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
         const float a = (row_valid && tk_abs < T) ? ex2(r.tb[tl] + r.off) : 0.f;
         a2[tl] = pack_bf16(a, a);
       }
-      if (l >= 4 && l < 8) BTRACE(21 + 4 * (l - 4));
       if (l + 2 < n_light) {  // this stage's registers are free again
         light_fetch(nxt, r);
         advance(nxt, 1);
@@ -1379,7 +1304,6 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
         ok = warp_wait(&bars[kLFree + bsel], ((l >> 1) - 1) & 1, p.status, 236);
         if (!ok) return;
       }
-      if (l >= 4 && l < 8) BTRACE(22 + 4 * (l - 4));
       uint8_t* dstP = bsel == 0 ? sP : sDS;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {  // 16-byte chunk c = key columns 8c .. 8c+7 of this warpgroup's 64
@@ -1393,7 +1317,6 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
       }
       fence_proxy_async_smem();
       mbar_arrive(&bars[kLpFull + bsel]);
-      if (l < 16) BTRACE(40 + l);
     };
     RowData r0, r1;
     if (ok && n_light > 0) {
@@ -1408,10 +1331,8 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
       light_body(l, r0);
       if (ok && l + 1 < n_light) light_body(l + 1, r1);
     }
-    BTRACE(2);
     // ---- epilogue: lane = key row now ----
     if (ok) ok = warp_wait(&bars[kBkAllDone], 0, p.status, 234);
-    BTRACE(3);
     if (ok) {
       tc_fence_after();
       const int tk_abs = J * TPB + ti_loc;
@@ -1442,7 +1363,6 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
         }
       }
     }
-    BTRACE(4);
     tc_fence_before();
   }
   __syncthreads();
@@ -1477,7 +1397,6 @@ int launch_kv(const BwdArgs& bw, const BqArgs& q, const void* qp, cudaStream_t s
   t.B = a.B; t.H = a.H; t.Hkv = a.Hkv; t.T = a.T; t.C = a.C; t.g = a.g; t.window = a.window;
   t.n_qt = q.n_qt; t.c2 = a.c2; t.sm_scale = a.sm_scale; t.status = q.status;
   t.kv_major = kv_major_order(a.B, a.Hkv, a.g, a.N, D);
-  t.trace = q.trace == nullptr ? nullptr : q.trace + (size_t)64 * a.B * a.H * a.T;
   constexpr int smem = BkCfg<D>::SMEM_BYTES;
   static_assert(smem <= 232448, "shared memory budget");
   MVPA_CUDA_CHECK(cudaFuncSetAttribute(tc_bwd_kv_kernel<D, CP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -1601,15 +1520,6 @@ int launch(const BwdArgs& bw, float* cs_dq, int* status, float* relc, float* rac
   t.kv_major = kv_major_order(a.B, a.Hkv, a.g, a.N, D);
   t.c2 = a.c2; t.sm_scale = a.sm_scale;
   t.status = status;
-  t.trace = nullptr;
-#ifdef MVPA_TC_TRACE
-  {
-    mvpa_problem pr{};
-    pr.B = a.B; pr.H = a.H; pr.Hkv = a.Hkv; pr.T = a.T; pr.C = a.C; pr.D = a.D;
-    t.trace = reinterpret_cast<long long*>(cs_dq + tc_bwd_q_workspace_floats(&pr) - (size_t)a.B * a.H * a.T * 256);
-    MVPA_CUDA_CHECK(cudaMemsetAsync(t.trace, 0, sizeof(long long) * 128 * (size_t)a.B * a.H * a.T, s));
-  }
-#endif
   constexpr int smem = Cfg<D>::SMEM_BYTES;
   static_assert(smem <= 232448, "shared memory budget");
   static_assert(Cfg<D>::EARLY >= 2, "the first tile's K and V load while the prologue runs");
@@ -1636,6 +1546,9 @@ namespace {
 size_t cs_dq_floats(int B, int H, int T, int D) { return (((size_t)B * H * T * D) + 63) & ~(size_t)63; }
 }  // namespace
 
+// where, inside the tensor-core backward's extra workspace, its kernels keep their status word
+size_t tc_bwd_status_offset_floats(const mvpa_problem* p) { return cs_dq_floats(p->B, p->H, p->T, p->D); }
+
 // extra fp32 workspace elements of the tensor-core backward
 size_t tc_bwd_q_workspace_floats(const mvpa_problem* p) {
   const size_t rows = (size_t)p->B * p->H * p->T * p->C;
@@ -1645,9 +1558,6 @@ size_t tc_bwd_q_workspace_floats(const mvpa_problem* p) {
   size_t n = cs_dq_floats(p->B, p->H, p->T, p->D) + 64 + (size_t)p->Hkv * 256 +
              (size_t)p->Hkv * (2 * p->D * 128 + 256) + rows * (p->D / 2) + rows * cp +
              ((rows + 3) & ~(size_t)3) + rows * p->T + 64;
-#ifdef MVPA_TC_TRACE
-  n = ((n + 63) & ~(size_t)63) + (size_t)p->B * p->H * p->T * 256;  // the timelines (query side, key side) sit at the very end
-#endif
   return n;
 }
 

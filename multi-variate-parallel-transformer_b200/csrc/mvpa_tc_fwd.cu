@@ -30,6 +30,7 @@
 #include "mvpa_common.cuh"
 #include "tc_ptx.cuh"
 #include "tc_tma_host.cuh"
+#include "tc_rel_const.cuh"
 
 namespace mvpa {
 namespace {
@@ -43,26 +44,6 @@ constexpr uint32_t kColS = 0;  // + 128 * buf
 constexpr uint32_t kColO = 256;
 constexpr uint32_t kColTB = 384;
 constexpr float kRescaleThreshold = 8.f;  // log2 units: P stays below 2^8
-
-// Optional in-kernel timeline (build with -DMVPA_TC_TRACE): 128 clock64 stamps per CTA, written
-// by one softmax thread and the MMA thread into the workspace after the status word.
-#ifdef MVPA_TC_TRACE
-#define TRACE(slot) do { if (trace_on) p.trace[(size_t)blockIdx.x * 128 + (slot)] = clock64(); } while (0)
-#else
-#define TRACE(slot) do { } while (0)
-#endif
-#ifdef MVPA_TRACE_DENSE
-#define LTRACE_ON false
-#else
-#define LTRACE_ON true
-#endif
-#if defined(MVPA_TC_TRACE) && defined(MVPA_TRACE_DENSE)
-#define DTRACE(s, k) do { if ((s) == 2 || (s) == 3) TRACE(112 + 8 * ((s) - 2) + (k)); } while (0)
-#define ATRACE(s, k) do { if ((s) == 2 || (s) == 4) TRACE(112 + 4 * ((s) - 2) + (k)); } while (0)
-#else
-#define DTRACE(s, k) do { } while (0)
-#define ATRACE(s, k) do { } while (0)
-#endif
 
 struct TcMaps {
   CUtensorMap q, k, v, rt, rc;
@@ -80,7 +61,6 @@ struct TcArgs {
   float c2;
   int* status;
   const float* relc;  // (Hkv, 256): vt.r_time[j] at [0,128), z.r_chan[j] at [128,256)
-  long long* trace;
 };
 
 enum BarrierIndex {
@@ -132,30 +112,6 @@ __device__ __forceinline__ int light_tiles(int I, int TPB, int window, int n_qt)
   return x < 0 ? 0 : x / TPB + 1;
 }
 
-// Per-column constants of the two relative products, once per kv head instead of once per CTA:
-//   relc[hk][j] = vt[hk] . r_time[hk][j]  (j < T),   relc[hk][128 + j] = z[hk] . r_chan[hk][j]  (j < C)
-// (the bias halves of `_rel_bias`, `attentions/attn.py:1308-1313`).
-__global__ void __launch_bounds__(256) rel_const_kernel(const __nv_bfloat16* __restrict__ vt,
-                                                        const __nv_bfloat16* __restrict__ z,
-                                                        const __nv_bfloat16* __restrict__ rt,
-                                                        const __nv_bfloat16* __restrict__ rc, float* __restrict__ relc,
-                                                        int T, int C, int D) {
-  const int hk = blockIdx.x, j = threadIdx.x & 127;
-  const bool is_t = threadIdx.x < 128;
-  const int rows = is_t ? T : C;
-  float acc = 0.f;
-  if (j < rows) {
-    const __nv_bfloat16* key = (is_t ? rt : rc) + ((size_t)hk * rows + j) * D;
-    const __nv_bfloat16* bias = (is_t ? vt : z) + (size_t)hk * D;
-    for (int d = 0; d < D; d += 2) {
-      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(key + d));
-      const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(bias + d));
-      acc += a.x * b.x + a.y * b.y;
-    }
-  }
-  relc[hk * 256 + threadIdx.x] = acc;
-}
-
 template <int D, int CP>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
@@ -198,17 +154,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
   uint64_t* slot_free = slot_full + NS;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-#ifdef MVPA_TC_TRACE
-  if (tid == 0) {  // kernel entry: SM id and the global nanosecond timer, to find the gaps between CTAs of an SM
-    uint32_t smid;
-    unsigned long long gt;
-    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
-    p.trace[(size_t)blockIdx.x * 128 + 124] = clock64();
-    p.trace[(size_t)blockIdx.x * 128 + 125] = smid;
-    p.trace[(size_t)blockIdx.x * 128 + 126] = (long long)gt;
-  }
-#endif
   const int BH = p.B * p.H;
   int I_loc, bh;  // latest (heaviest) query tiles first, over all heads or inside one kv head
   if (p.kv_major) {
@@ -271,9 +216,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
   if (warp == 8) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
-#ifdef MVPA_TC_TRACE
-      const bool trace_on = true;
-#endif
       prefetch_tensormap(&maps.q);
       prefetch_tensormap(&maps.k);
       prefetch_tensormap(&maps.v);
@@ -291,7 +233,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
         const int sl = q % NS;
         if (ok && q >= NS) ok = mbar_wait(&slot_free[sl], ((q / NS) - 1) & 1, p.status, 11);
         if (!ok) return;
-        if (q < 16) TRACE(96 + q);
         uint8_t* dst = ring + sl * TILE;
         mbar_arrive_expect_tx(&slot_full[sl], TILE);
 #pragma unroll
@@ -306,9 +247,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
   } else if (warp == 9) {
     // ------------------------------- MMA issuer -------------------------------
     if (lane == 0) {
-#ifdef MVPA_TC_TRACE
-      const bool trace_on = true;
-#endif
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0);
       constexpr uint32_t idesc_c = make_idesc_bf16(128, CP, 0);
       constexpr uint32_t idesc_o = make_idesc_bf16(128, D, 1);
@@ -381,7 +319,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
       for (int s = 0; ok && s < n_dense; ++s) {
         if (s + 1 < n_dense) issue_qk(s + 1);  // S of the next tile first: its softmax is the long pole
         if (ok && !pre_p) ok = mbar_wait_a(a_pfull + 8 * (s & 1), (s >> 1) & 1, p.status, 23);
-        if (s < 16) TRACE(64 + 2 * s);
         if (!ok) break;
         tc_fence_after();
         // P_s: two 32-column halves at the start of each warpgroup's S columns (stride 64)
@@ -399,13 +336,11 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
         mma_ts_x4(d_o, a0 + (ALT ? 32 : 64), b_lo + 4 * (2048 >> 4), dv0.hi, 2048 >> 4, idesc_o, 1u);
         mma_commit_a(a_free + 8 * v_sl);
         advance_v(dn ? 2 : 1);  // a dense successor's V is two loads on, a light successor's one
-        if (s < 24) TRACE(36 + s);
       }
       // ---- light tiles: P in four contiguous 64-column buffers ----
       uint32_t pb = 0, pb_par = 0;
       for (int l = 0; ok && l < n_light; ++l) {
         if (!pre_p) ok = mbar_wait_a(a_plfull + 8 * pb, pb_par, p.status, 23);
-        if (n_dense + l < 16) TRACE(64 + 2 * (n_dense + l));
         if (!ok) break;
         tc_fence_after();
         const uint32_t a0 = tmem + kColS + 64 * pb;
@@ -417,17 +352,12 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
         mma_ts_x4(tmem + kColO, a0 + 32, b_lo + 4 * (2048 >> 4), dv0.hi, 2048 >> 4, idesc_o, 1u);
         mma_commit_a(a_free + 8 * v_sl);
         advance_v(1);
-        if (n_dense + l < 24) TRACE(36 + n_dense + l);
       }
     }
   }
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
     // ------------------------------ softmax warps ------------------------------
-#ifdef MVPA_TC_TRACE
-    const bool trace_on = tid == 0;
-#endif
-    TRACE(0);
     const int row = tid & 127;               // query row of the tile == TMEM lane
     const int wg = tid >> 7;                 // column half this thread owns
     const int ti_loc = row / CP, c_i = row % CP;
@@ -440,9 +370,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
     s_vr[tid] = p.relc[hk * 256 + tid];  // s_vr and s_zc are adjacent: 256 floats
     softmax_bar();
     bool ok = warp_wait(&bars[kBarProFull], 0, p.status, 30);
-    TRACE(1);
     if (ok) ok = warp_wait(&bars[kBarProMma], 0, p.status, 31);
-    TRACE(2);
     // (the relative-key tiles sR / sC were only read by the two MMAs: the scratch may overwrite them)
     // Channel scores of the row, c2 (q.r_chan[j] + z.r_chan[j]), parked in shared memory in
     // 32-column chunks (split between the warpgroups) for the per-row gather below.
@@ -471,7 +399,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
       tc_fence_before();
     }
     softmax_bar();  // scratch complete; the MMAs no longer need the raw Q tile
-    TRACE(3);
     // Gathered by |c_i - c_k| for this thread's columns:
     //   cbl = cb - max (fp16x2, log2 domain) for dense tiles,  bc = exp2(cbl) (bf16x2) for light tiles.
     __half2 cbl[NCH / 2];
@@ -543,8 +470,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
       }
     }
     mbar_arrive(&bars[kBarProDone]);  // borrowed ring stages, S0 and the rewritten Q are ready
-    TRACE(4);
-
     float m_used = -INFINITY, l_sum = 0.f;
 
     // O and l follow the running maximum only when it moved by more than 2^8.  Needs every PV
@@ -605,14 +530,12 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
         const int J = tile_of(s);
         float tb_all[TPB], wmul[TPB];
         bool valid_all[TPB];
-        ATRACE(s, 0);
         {
           uint32_t tb_raw[TPB];
           int tb_col[TPB];
           tb_issue(J, tb_raw, tb_col, valid_all);
           ok = warp_wait(&bars[kBarSFull + wg], (s >> 1) & 1, p.status, 32);
           tmem_ld_wait();
-          ATRACE(s, 1);
           if (!ok) break;
           tc_fence_after();
           tb_finish(tb_raw, tb_col, tb_all);
@@ -650,7 +573,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
         tmem_ld_wait();
         tmem_ld32(s_addr, va);  // first chunk of pass 2
         max_chunk(vb, 3);
-        ATRACE(s, 2);
         if (!wait_v(s)) { ok = false; break; }  // these warps vouch for V_s when they report P_s
         if (s == wg) {
           m_used = (m_tile == -INFINITY) ? 0.f : m_tile;
@@ -675,7 +597,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
             if (need) m_used = m_tile;
           }
         }
-        ATRACE(s, 3);
         // pass 2: P = exp2(S2 - m) as bf16 over the consumed S columns (chunk c lands in columns 16c..16c+15,
         // always behind the columns still to be read)
         float psum = 0.f, psum1 = 0.f;
@@ -706,13 +627,10 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
         tmem_ld_wait();
         exp_chunk(vb, 3);
         psum += psum1;
-        ATRACE(s, 4);
         l_sum += psum;
         tmem_st_wait();
         tc_fence_before();
         mbar_arrive(&bars[kBarPFull + wg]);
-        if (s < 24) TRACE(8 + s);
-        ATRACE(s, 5);
       }
       // ---- merge the two accumulators: O_even <- O_even 2^(m_e - m) + O_odd 2^(m_o - m) ----
       s_merge[wg * 128 + row] = m_used;
@@ -760,14 +678,12 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
       int tb_col[TPB];
 #pragma unroll
       for (int tt = 0; tt < TPB; ++tt) { tb_all[tt] = 0.f; valid_all[tt] = false; tb_raw[tt] = 0; tb_col[tt] = 0; }
-      DTRACE(s, 0);
       if (ok) tb_issue(J, tb_raw, tb_col, valid_all);
       float tbv[TPW], wmul[TPW];
       bool valid[TPW];
       float sreg[64];
       if (ok && !warp_wait(&bars[kBarSFull + buf], (s >> 1) & 1, p.status, 32)) ok = false;
       float m_part = -INFINITY;
-      DTRACE(s, 1);
       if (ok) {
         tc_fence_after();
         uint32_t v0[32], v1[32];
@@ -775,7 +691,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
         tmem_ld32(s_addr + 32, v1);
         if (!wait_v(s)) ok = false;  // overlaps the TMEM round trips
         tmem_ld_wait();
-        DTRACE(s, 2);
         tb_finish(tb_raw, tb_col, tb_all);
 #pragma unroll
         for (int jj = 0; jj < 32; ++jj) {
@@ -815,9 +730,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
       // the two column halves of a row must agree on the tile maximum
       s_max[(buf * 2 + wg) * 128 + row] = m_part;
       if (!ok) *s_giveup = 1;
-      DTRACE(s, 3);
       softmax_bar();
-      DTRACE(s, 4);
       if (*s_giveup != 0) { ok = false; break; }  // some warp's wait ran out: everyone leaves together
       const float m_tile = fmaxf(m_part, s_max[(buf * 2 + (wg ^ 1)) * 128 + row]);
       if (s == 0) {
@@ -828,7 +741,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
       }
       // (P_s reuses the columns of S_s / P_{s-2}; S_full of this tile already implies PV_{s-2} is done)
       float negmu[TPW];
-      DTRACE(s, 5);
 #pragma unroll
       for (int tl = 0; tl < TPW; ++tl) negmu[tl] = valid[tl] ? tbv[tl] - m_used : -INFINITY;
       float psum = 0.f;
@@ -844,12 +756,9 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
       l_sum += psum;
       tmem_st16(s_addr, lo);  // P (bf16) over this thread's own, already consumed S columns
       tmem_st16(s_addr + 16, hi);
-      DTRACE(s, 6);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bars[kBarPFull + buf]);
-      DTRACE(s, 7);
-      if (s < 24) TRACE(8 + s);
     }
 
     }  // !ALT
@@ -877,7 +786,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
         if (!ok) break;
         tb_finish(tb_raw, tb_col, tb_all);
       }
-      if (LTRACE_ON && s >= 12 && s < 16) TRACE(112 + 4 * (s - 12));
       float m_tile = -INFINITY;
 #pragma unroll
       for (int tt = 0; tt < TPB; ++tt)
@@ -890,7 +798,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
         if (!ok) break;
         tc_fence_after();
       }
-      if (LTRACE_ON && s >= 12 && s < 16) TRACE(113 + 4 * (s - 12));
       uint32_t lo[16], hi[16];
 #pragma unroll
       for (int tl = 0; tl < TPW; ++tl) {
@@ -913,19 +820,15 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
       const uint32_t p_addr = lane_base + kColS + 64 * (l & 3) + 32 * wg;
       tmem_st16(p_addr, lo);
       tmem_st16(p_addr + 16, hi);
-      if (LTRACE_ON && s >= 12 && s < 16) TRACE(114 + 4 * (s - 12));
       tmem_st_wait();
-      if (LTRACE_ON && s >= 12 && s < 16) TRACE(115 + 4 * (s - 12));
       tc_fence_before();
       mbar_arrive(&bars[kBarPlFull + (l & 3)]);
-      if (s < 24) TRACE(8 + s);
     }
     // ------------------------------- epilogue ---------------------------------
     if (ok) {
       const int ql = q_of_v(n_tiles - 1);
       ok = warp_wait(&slot_free[ql % NS], (ql / NS) & 1, p.status, 34);
     }
-    TRACE(5);
     s_lsum[wg * 128 + row] = l_sum;
     softmax_bar();
     l_sum = s_lsum[row] + s_lsum[128 + row];
@@ -961,7 +864,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
       tma_store_commit();
       tma_store_wait_all();
     }
-    TRACE(6);
     tc_fence_before();
   }
   __syncthreads();
@@ -969,14 +871,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
     tc_fence_after();
     tmem_dealloc(tmem, kTmemCols);
   }
-#ifdef MVPA_TC_TRACE
-  if (tid == 0) {
-    unsigned long long gt;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
-    p.trace[(size_t)blockIdx.x * 128 + 127] = (long long)gt;
-    p.trace[(size_t)blockIdx.x * 128 + 7] = clock64();
-  }
-#endif
 }
 
 int make_maps(TcMaps& m, const Args& a, int CP) {
@@ -1043,7 +937,6 @@ int launch(const Args& a, int* status, cudaStream_t s) {
   t.status = status;
   float* relc = reinterpret_cast<float*>(status) + 64;  // workspace + 256 bytes
   t.relc = relc;
-  t.trace = reinterpret_cast<long long*>(relc + (size_t)a.Hkv * 256);  // MVPA_TC_TRACE builds only
   constexpr int smem = Cfg<D>::SMEM_BYTES;
   static_assert(smem <= 232448, "shared memory budget");
   static_assert(Cfg<D>::EARLY >= 2, "the first tile's K and V load while the prologue runs");
@@ -1069,9 +962,6 @@ size_t tc_fwd_workspace_bytes(const mvpa_problem* p) {
   const bool tc = (p->D == 64 || p->D == 128) && p->C <= 128 && p->T <= 128;
   // status word (bounded waits report here) + per-kv-head constants of the relative products
   size_t bytes = 256 + (size_t)p->Hkv * 1024;
-#ifdef MVPA_TC_TRACE
-  bytes += (size_t)p->T * p->B * p->H * 1024;
-#endif
   return tc ? bytes : 0;
 }
 
@@ -1083,39 +973,44 @@ constexpr int kStaticMaxKvHeads = 64;
 constexpr size_t kStaticScratchBytes = 256 + (size_t)kStaticMaxKvHeads * 1024;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
+namespace {
+// In host code `g_static_scratch` only names the symbol; its device address has to be asked for,
+// once per device, while that device is current.
+constexpr int kStaticMaxDevices = 64;
+void* g_static_addr[kStaticMaxDevices] = {};
+std::mutex g_static_mu;
+}  // namespace
+
 int tc_fwd_static(const Args& a, cudaStream_t s) {
-#ifdef MVPA_TC_TRACE
-  set_error("the instrumented build writes its timeline to the caller's workspace: use mvpa_fwd");
-  return MVPA_ERR_UNSUPPORTED;
-#else
   if (a.Hkv > kStaticMaxKvHeads) {
     set_error("mvpa_fwd_noalloc: %d kv heads exceed the built-in scratch (at most %d); use mvpa_fwd with a workspace",
               a.Hkv, kStaticMaxKvHeads);
     return MVPA_ERR_WORKSPACE;
   }
-  // In host code `g_static_scratch` only names the symbol; its device address has to be asked for,
-  // once per device, while that device is current.
-  constexpr int kMaxDevices = 64;
-  static void* addr[kMaxDevices] = {};
-  static std::mutex mu;
   int dev = -1;
   MVPA_CUDA_CHECK(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= kMaxDevices) {
+  if (dev < 0 || dev >= kStaticMaxDevices) {
     set_error("mvpa_fwd_noalloc: device ordinal %d out of range", dev);
     return MVPA_ERR_CUDA;
   }
   void* ptr;
   {
-    std::lock_guard<std::mutex> lock(mu);
-    if (addr[dev] == nullptr) {
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (g_static_addr[dev] == nullptr) {
       void* got = nullptr;
       MVPA_CUDA_CHECK(cudaGetSymbolAddress(&got, g_static_scratch));
-      addr[dev] = got;
+      g_static_addr[dev] = got;
     }
-    ptr = addr[dev];
+    ptr = g_static_addr[dev];
   }
   return tc_fwd(a, ptr, kStaticScratchBytes, s);
-#endif
+}
+
+const int* tc_fwd_static_status_word() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kStaticMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  return static_cast<const int*>(g_static_addr[dev]);
 }
 
 int tc_fwd(const Args& a, void* workspace, size_t workspace_bytes, cudaStream_t s) {

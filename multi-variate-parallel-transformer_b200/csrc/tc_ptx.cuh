@@ -2,8 +2,9 @@
 // mbarrier, TMA (cp.async.bulk.tensor, no cluster multicast anywhere), tcgen05 MMA with
 // TMEM accumulators, tcgen05.ld/st, and the shared-memory / instruction descriptors.
 //
-// Every wait is bounded: after kSpinLimit polls it records a code in a status word and
-// returns false, so a protocol bug surfaces as an error status instead of a hung GPU.
+// Every wait is bounded in time: once a deadline on the %globaltimer clock has passed it records a
+// code in a status word and returns false, so a protocol bug surfaces as an error status instead
+// of a hung GPU.
 #pragma once
 
 #include <cuda.h>
@@ -13,7 +14,27 @@
 namespace mvpa {
 namespace ptx {
 
-constexpr uint32_t kSpinLimit = 1u << 24;  // try_wait polls before giving up (~ a second)
+constexpr uint64_t kDefaultWaitNs = 2000000000ull;  // a wait gives up after two seconds
+constexpr uint32_t kPollsPerClockRead = 32;         // try_wait polls between two looks at the clock
+// Per translation unit: a non-zero value (microseconds) replaces the default deadline.  Only the wait
+// self-test sets it (to make a wait run out quickly); product kernels run with the default.
+static __device__ unsigned int g_wait_limit_us = 0;
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ uint64_t wait_limit_ns() {
+  const unsigned int us = *(volatile unsigned int*)&g_wait_limit_us;
+  return us != 0 ? (uint64_t)us * 1000ull : kDefaultWaitNs;
+}
+__device__ __forceinline__ void record_giveup(int* status, int code) {
+  if (status != nullptr) {
+    atomicCAS(status, 0, code);
+    status[(code % 100) & 63] = code;  // every wait that gave up, for diagnosis (the first word keeps the first)
+  }
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -56,16 +77,20 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  On time-out stores `code` to *status (first writer wins) and returns false.
-// A phase that has already completed is caught by the non-suspending test first.
+// A phase that has already completed is caught by the non-suspending test first; the clock is
+// only consulted once a first batch of polls has failed, so a short wait never reads it.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
   if (mbar_test_wait(bar, parity)) return true;
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+  for (uint32_t i = 0; i < kPollsPerClockRead; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
   }
-  if (status != nullptr) {
-    atomicCAS(status, 0, code);
-    status[(code % 100) & 63] = code;  // every wait that gave up, for diagnosis (the first word keeps the first)
-  }
+  const uint64_t t0 = global_timer_ns(), limit = wait_limit_ns();
+  do {
+    for (uint32_t i = 0; i < kPollsPerClockRead; ++i) {
+      if (mbar_try_wait(bar, parity)) return true;
+    }
+  } while (global_timer_ns() - t0 < limit);
+  record_giveup(status, code);
   return false;
 }
 
@@ -82,23 +107,29 @@ __device__ __forceinline__ bool mbar_test_wait_a(uint32_t bar, uint32_t parity) 
       : "memory");
   return ok != 0;
 }
+__device__ __forceinline__ bool mbar_try_wait_a(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ bool mbar_wait_a(uint32_t bar, uint32_t parity, int* status, int code) {
   if (mbar_test_wait_a(bar, parity)) return true;
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (ok) return true;
+  for (uint32_t i = 0; i < kPollsPerClockRead; ++i) {
+    if (mbar_try_wait_a(bar, parity)) return true;
   }
-  if (status != nullptr) {
-    atomicCAS(status, 0, code);
-    status[(code % 100) & 63] = code;
-  }
+  const uint64_t t0 = global_timer_ns(), limit = wait_limit_ns();
+  do {
+    for (uint32_t i = 0; i < kPollsPerClockRead; ++i) {
+      if (mbar_try_wait_a(bar, parity)) return true;
+    }
+  } while (global_timer_ns() - t0 < limit);
+  record_giveup(status, code);
   return false;
 }
 __device__ __forceinline__ void mma_commit_a(uint32_t bar) {

@@ -17,9 +17,7 @@ import threading
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _CSRC = os.path.join(_HERE, "csrc")
 _INCLUDE = os.path.join(os.path.dirname(_HERE), "include")
-# MVPA_B200_LIB: load a library built elsewhere (e.g. an instrumented build) instead of the in-tree one.
-_OVERRIDE = os.environ.get("MVPA_B200_LIB")
-LIB_PATH = _OVERRIDE or os.path.join(_HERE, "libmvpa_b200.so")
+LIB_PATH = os.path.join(_HERE, "libmvpa_b200.so")
 HASH_PATH = LIB_PATH + ".srchash"
 
 NVCC_FLAGS = [
@@ -49,8 +47,6 @@ def _source_hash() -> str:
 
 
 def _stale() -> bool:
-    if _OVERRIDE:
-        return False
     if not (os.path.exists(LIB_PATH) and os.path.exists(HASH_PATH)):
         return True
     with open(HASH_PATH) as f:
@@ -94,7 +90,9 @@ class Tensor(ctypes.Structure):
 
 EXPORTS = ("mvpa_fwd", "mvpa_bwd", "mvpa_fwd_workspace_bytes", "mvpa_bwd_workspace_bytes",
            "mvpa_last_error_string", "mvpa_launch_count", "mvpa_abi_version",
-           "mvpa_workspace_status", "mvpa_fwd_noalloc")
+           "mvpa_workspace_status", "mvpa_fwd_noalloc", "mvpa_bwd_status", "mvpa_noalloc_status",
+           "mvpa_selftest_wait_timeout")
+ABI_VERSION = 3   # mvpa_abi_version() of the header this shim was written against
 
 
 def lib() -> ctypes.CDLL:
@@ -127,9 +125,18 @@ def lib() -> ctypes.CDLL:
         L.mvpa_fwd_noalloc.argtypes = [P, Tn, Tn, Tn, vp, vp, vp, vp, vp, Tn, vp, vp]
         L.mvpa_workspace_status.restype = ctypes.c_int
         L.mvpa_workspace_status.argtypes = [vp, ctypes.c_size_t, vp]
+        L.mvpa_bwd_status.restype = ctypes.c_int
+        L.mvpa_bwd_status.argtypes = [P, vp, ctypes.c_size_t, vp]
+        L.mvpa_noalloc_status.restype = ctypes.c_int
+        L.mvpa_noalloc_status.argtypes = [vp]
+        L.mvpa_selftest_wait_timeout.restype = ctypes.c_int
+        L.mvpa_selftest_wait_timeout.argtypes = [vp, ctypes.c_size_t, ctypes.c_uint32, vp]
         L.mvpa_last_error_string.restype = ctypes.c_char_p
         L.mvpa_launch_count.restype = ctypes.c_uint64
         L.mvpa_abi_version.restype = ctypes.c_int
+        if L.mvpa_abi_version() != ABI_VERSION:  # e.g. a stale binary kept because the rebuild failed
+            raise ImportError(f"{LIB_PATH} has ABI version {L.mvpa_abi_version()}, this shim needs {ABI_VERSION}: "
+                              "rebuild it (python __graft_entry__.py)")
         _lib = L
         return L
 

@@ -22,7 +22,7 @@ def test_library_exports_every_declared_symbol():
     for n in names:
         assert hasattr(lib, n), n
     assert set(nat.EXPORTS) <= set(names)
-    assert lib.mvpa_abi_version() >= 1
+    assert lib.mvpa_abi_version() == nat.ABI_VERSION
 
 
 def _prob(**kw):
@@ -72,3 +72,63 @@ def test_python_constants_match_the_header():
     for name in ("MVPA_F32", "MVPA_BF16", "MVPA_F16"):
         assert defs[name] == getattr(nat, name), name
     assert defs["MVPA_OK"] == 0 and defs["MVPA_ERR_DTYPE"] == -2 and defs["MVPA_ERR_SHAPE"] == -1
+
+
+_CTYPES = {"int32_t": ctypes.c_int32, "float": ctypes.c_float, "void*": ctypes.c_void_p, "int64_t": ctypes.c_int64}
+
+
+def _header_struct(name):
+    """(field, ctypes type) pairs of `struct <name>` as `include/mvpa.h` declares them."""
+    text = open(os.path.join(ROOT, "include", "mvpa.h")).read()
+    body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (name, name), text, flags=re.S).group(1)
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    fields = []
+    for decl in body.split(";"):
+        decl = decl.strip()
+        if not decl:
+            continue
+        m = re.match(r"(int32_t|int64_t|float|void\s*\*)\s*(.*)", decl)
+        ctype = _CTYPES[m.group(1).replace(" ", "")]
+        fields += [(n.strip(), ctype) for n in m.group(2).split(",")]
+    return fields
+
+
+def _integration_structs():
+    """The `Problem` / `Tensor` classes of the binding shown in INTEGRATION.md, executed as written."""
+    text = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    block = next(b for b in re.findall(r"```python\n(.*?)```", text, flags=re.S) if "class Problem" in b)
+    defs = block[block.index("class Problem"):block.index("lib = ctypes.CDLL")]
+    ns = {"ctypes": ctypes}
+    exec(defs, ns)
+    return ns["Problem"], ns["Tensor"]
+
+
+def test_struct_layouts_match_the_header():
+    """`mvpa_problem` / `mvpa_tensor`: field names, order and types agree between the header, the
+    ctypes shim and the binding printed in INTEGRATION.md (a struct that is short hands the library
+    garbage in its last fields)."""
+    doc_problem, doc_tensor = _integration_structs()
+    for cname, shim, doc in (("mvpa_problem", nat.Problem, doc_problem), ("mvpa_tensor", nat.Tensor, doc_tensor)):
+        want = _header_struct(cname)
+        for cls in (shim, doc):
+            assert [(n, t) for n, t in cls._fields_] == want, (cname, cls)
+            assert ctypes.sizeof(cls) == ctypes.sizeof(shim)
+    assert ctypes.sizeof(nat.Problem) == 48 and ctypes.sizeof(nat.Tensor) == 32
+
+
+def test_integration_binding_passes_every_problem_field():
+    """The `Problem(...)` call in INTEGRATION.md's binding gives one value per struct field."""
+    text = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    call = re.search(r"p = Problem\((.*?)\)[^\n]*\n\s+o = ", text, flags=re.S).group(1)
+    call = re.sub(r"#[^\n]*", "", call)
+    depth, args, cur = 0, [], ""
+    for ch in call:
+        depth += ch in "([{"
+        depth -= ch in ")]}"
+        if ch == "," and depth == 0:
+            args.append(cur)
+            cur = ""
+        else:
+            cur += ch
+    args.append(cur)
+    assert len(args) == len(nat.Problem._fields_)

@@ -46,21 +46,28 @@ def _cpu_op(q, u, vt, z, k, rt, rc, v, causal, sm_scale, window_size, q_time_ran
     return o[:, :, t0 * C:(t0 + n) * C]
 
 
-def _worker(rank, world, port, out_dir):
+def _worker(rank, world, port, out_dir, shape=(1, 4, 2, 13, 5, 16), fused=False):
     for p in (PKG, os.path.join(ROOT, "oracle")):
         sys.path.insert(0, p)
     import mvpa_port_torch as portmod
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        B, H, Hkv, T, C, D = 1, 4, 2, 13, 5, 16
+        B, H, Hkv, T, C, D = shape
         g = torch.Generator().manual_seed(5)
         r = lambda *s: torch.randn(*s, generator=g)
         q, k, v = r(B, T * C, H, D), r(B, T * C, Hkv, D), r(B, T * C, Hkv, D)     # projection layout
         u, vt, z, rt, rc = r(1, Hkv, 1, D), r(1, Hkv, 1, D), r(1, Hkv, 1, D), r(1, Hkv, T, D), r(1, Hkv, C, D)
         plan = ms.zigzag_chunks(T, C, world)
         cut = lambda x: [x[:, t0 * C:(t0 + n) * C].contiguous() if n else None for t0, n in plan[rank]]
-        outs = ms.time_sharded_attention(_cpu_op, cut(q), u, vt, z, cut(k), rt, rc, cut(v), T, C, D ** -0.5, 10)
+        calls = []
+        if fused:   # K and V fused along the head axis, as `c_attn` produces them: one collective per half
+            outs = ms.time_sharded_attention(_cpu_op, cut(q), u, vt, z, cut(torch.cat([k, v], dim=2)), rt, rc, None,
+                                             T, C, D ** -0.5, 10, batch=B, overlap=lambda: calls.append(1))
+            assert calls == [1]
+        else:
+            outs = ms.time_sharded_attention(_cpu_op, cut(q), u, vt, z, cut(k), rt, rc, cut(v), T, C, D ** -0.5, 10,
+                                             batch=B)
         ref = portmod.rel_attn(q.permute(0, 2, 1, 3), u.reshape(Hkv, D), vt.reshape(Hkv, D), z.reshape(Hkv, D),
                                k.permute(0, 2, 1, 3), rt.reshape(Hkv, T, D), rc.reshape(Hkv, C, D),
                                v.permute(0, 2, 1, 3), D ** -0.5, 10).permute(0, 2, 1, 3)
@@ -68,6 +75,8 @@ def _worker(rank, world, port, out_dir):
         for (t0, n), o in zip(plan[rank], outs):
             if n:
                 err = max(err, (o - ref[:, t0 * C:(t0 + n) * C]).abs().max().item())
+            else:
+                assert o is None
         np.save(os.path.join(out_dir, f"err{rank}.npy"), np.array([err]))
     finally:
         dist.destroy_process_group()
@@ -77,6 +86,24 @@ def test_time_sharding_with_two_gloo_ranks(tmp_path):
     port = 29500 + (os.getpid() % 2000)
     mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     errs = [float(np.load(tmp_path / f"err{r}.npy")[0]) for r in range(2)]
+    assert max(errs) < 1e-5, errs
+
+
+@pytest.mark.parametrize("world,shape,fused", [
+    (4, (1, 2, 1, 3, 16, 16), False),    # fewer tiles than chunks: ranks 1 and 2 own nothing, yet join every collective
+    (2, (2, 4, 2, 16, 128, 16), True),   # equal chunks with a batch dimension, K and V fused
+    (2, (1, 4, 2, 16, 128, 16), True),   # equal chunks, one sample: the early half is gathered in place
+])
+def test_time_sharding_gather_variants(tmp_path, world, shape, fused):
+    """Every branch of the gather (in place, reversed half, ragged / batched) reassembles the single-process
+    result, including ranks whose two zig-zag chunks are both empty."""
+    B, H, Hkv, T, C, D = shape
+    plan = ms.zigzag_chunks(T, C, world)
+    if world == 4:
+        assert any(all(n == 0 for _, n in chunks) for chunks in plan)
+    port = 29500 + (os.getpid() % 2000) + 11 * world + int(fused) + B
+    mp.spawn(_worker, args=(world, port, str(tmp_path), shape, fused), nprocs=world, join=True)
+    errs = [float(np.load(tmp_path / f"err{r}.npy")[0]) for r in range(world)]
     assert max(errs) < 1e-5, errs
 
 
