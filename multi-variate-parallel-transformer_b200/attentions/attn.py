@@ -161,14 +161,18 @@ def flash_mvpa(q, q_bias, q_btime, q_bchan, k_glob, k_time, k_chan, v, causal, s
         # Structured dropout of the reference (`attentions/attn.py:1052-1062, 316-321`): whole key time
         # steps and key channels are dropped, each with probability 1 - sqrt(1 - p_drop), and the kept
         # probabilities are divided by 1 - p_drop after the softmax denominator is taken.  The mask depends
-        # on the key alone, so P_dropped V = P (mask V / (1 - p_drop)): one elementwise pass over V, and
-        # autograd carries the mask into dV.  Same draws in the same order as the reference (channels, then
-        # time steps), so a generator seeded alike gives the same mask.
+        # on the key alone, so P_dropped V = (P (mask V)) / (1 - p_drop): one exact 0/1 pass over V before the
+        # kernels and one fp32 scaling of their output (the reference divides P in fp32, `:235`), and autograd
+        # carries both into dV and dO.  Same draws in the same order as the reference (channels, then time
+        # steps), so a generator seeded alike gives the same mask.
         p_per_dim = 1 - math.sqrt(1 - p_drop)
         chan_keep = torch.rand(chan_ctx, device=q.device, generator=generator) > p_per_dim
         time_keep = torch.rand(time_ctx, device=q.device, generator=generator) > p_per_dim
         keep = (time_keep[:, None] & chan_keep[None, :]).reshape(1, 1, n_ctx, 1)
-        v = v * (keep.to(v.dtype) / (1 - p_drop))
+        v = v * keep.to(v.dtype)
     u, vt, z = (x.reshape(kv_heads, D) for x in (q_bias, q_btime, q_bchan))
-    return FlashMVPA.apply(q, u, vt, z, k_glob, k_time.reshape(kv_heads, time_ctx, D),
-                           k_chan.reshape(kv_heads, chan_ctx, D), v, sm_scale, window_size, q_time)
+    o = FlashMVPA.apply(q, u, vt, z, k_glob, k_time.reshape(kv_heads, time_ctx, D),
+                        k_chan.reshape(kv_heads, chan_ctx, D), v, sm_scale, window_size, q_time)
+    if p_drop and p_drop > 0:
+        o = (o.float() * (1.0 / (1 - p_drop))).to(o.dtype)
+    return o
