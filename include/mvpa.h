@@ -162,6 +162,67 @@ int mvpa_noalloc_status(void* cuda_stream);
 int mvpa_selftest_wait_timeout(void* workspace, size_t workspace_bytes, uint32_t limit_us,
                                void* cuda_stream);
 
+/* ---- kernels around the attention: block glue, encoder, heads (HBM-bound) -------------------
+ * Rows are contiguous (`width` elements, a multiple of 16 bytes) unless a leading dimension is
+ * given; element types MVPA_F32 / MVPA_BF16; arithmetic in fp32. */
+
+/*
+ * y = rmsnorm(h) * weight,  h = x (+ add, rounded to the element type as eager PyTorch does);
+ * h is also written to `sum_out` when that is not NULL.  Replaces `ln_1` / `ln_f`
+ * (`models/mvpformer.py:108,133,167,383`; RMSNorm: x * rsqrt(mean(x^2) + eps) * weight) and, with
+ * `add`, the residual sum of the parallel block that precedes the next layer's norm
+ * (`models/mvpformer.py:147`).  width <= 4096 (bf16) / 2048 (fp32).
+ */
+int mvpa_rmsnorm(const void* x, const void* add, const void* weight, void* sum_out, void* y,
+                 int64_t rows, int32_t width, float eps, int32_t dtype, void* cuda_stream);
+
+/*
+ * out = silu(gate) * up, elementwise; gate, up share the leading dimension ld_in (two column blocks
+ * of one fused projection), out has ld_out.  Replaces the activation inside `LlamaMLP`
+ * (`models/mvpformer.py:114,146`: down_proj(act_fn(gate_proj(x)) * up_proj(x))).
+ */
+int mvpa_silu_mul(const void* gate, const void* up, int64_t ld_in, void* out, int64_t ld_out,
+                  int64_t rows, int32_t width, int32_t dtype, void* cuda_stream);
+
+/*
+ * Number of coefficients `WaveEncoder` produces for a segment of `segment_len` samples with an
+ * 8-tap wavelet in periodic mode (`models/fftencoder.py:69-78`: every level floor((n + 7) / 2),
+ * floor(log2(len / 7)) levels, plus the last approximation); 0 if the segment is too short.
+ * `level_sizes` (may be NULL) receives the per-level sizes, finest first.
+ */
+int32_t mvpa_wave_encode_size(int32_t segment_len, int32_t* level_sizes, int32_t max_levels);
+
+/*
+ * Encoder front end: all levels of the periodic 8-tap wavelet transform of each segment,
+ * concatenated [cA_L, cD_L, ..., cD_1], RMS-normalised and scaled by `weight`, written once in
+ * the output element type (columns past the coefficient count, up to ld_out, are zeroed so the
+ * projection can run on a padded K).  Replaces `WaveEncoder.block` + `self.ln`
+ * (`models/fftencoder.py:79-94`; `ptwt.wavedec(..., mode="periodic")` = circular padding + strided
+ * convolution per level).  dec_lo / dec_hi: the eight decomposition taps, HOST pointers.
+ */
+int mvpa_wave_encode(const void* x, int64_t ld_x, int32_t x_dtype, const float* dec_lo,
+                     const float* dec_hi, const void* weight, void* out, int64_t ld_out,
+                     int32_t out_dtype, int64_t rows, int32_t segment_len, float eps,
+                     void* cuda_stream);
+
+/*
+ * Classification readout: out[b] = mean over channels of h[b, T-1] for h (B,T,C,E)
+ * (`models/mvpformer.py:951-953`: `out[:, -1].mean(dim=1)`).
+ */
+int mvpa_channel_mean(const void* h, void* out, int32_t B, int32_t T, int32_t C, int32_t E,
+                      int32_t dtype, void* cuda_stream);
+
+/*
+ * Contrastive next-state logits (`models/mvpformer.py:574-594, 631-660`).  pred, enc (B,T,C,E);
+ * negatives (B,T,C,K) int32 row indices into enc viewed as (B*T*C, E); logits (B*(T-1)*C, 1+K) fp32:
+ * row of target (b, t >= 1, c) holds cos(pred[b,t-1,c], enc[b,t,c]) / temperature, then the same
+ * against each negative, -inf where a negative equals the positive.  The (rows, 1+K, E) target
+ * tensor of the reference is never formed.  E <= 2048 (bf16) / 1024 (fp32).
+ */
+int mvpa_contrastive_logits(const void* pred, const void* enc, const int32_t* negatives,
+                            float* logits, int32_t B, int32_t T, int32_t C, int32_t E, int32_t K,
+                            float temperature, int32_t dtype, void* cuda_stream);
+
 /* Text of the last error raised on this host thread ("" if none).
  * Stands where the reference raises RuntimeError / assert
  * (`attentions/attn.py:1034-1045, 1339, 1344`). */

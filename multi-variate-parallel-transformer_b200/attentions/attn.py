@@ -113,6 +113,33 @@ class FlashMVPA(torch.autograd.Function):
         return (dq, du.to(dt), dvt.to(dt), dz.to(dt), dk, drt.to(dt), drc.to(dt), dv, None, None, None)
 
 
+def flash_mvpa_into(out, q, u, vt, z, k, r_time, r_chan, v, sm_scale, window_size=10):
+    """Inference form of `flash_mvpa`: no autograd record, no log-sum-exp output, and the result goes into
+    `out`, a caller-owned (B,H,N,D) tensor that may be a strided view (e.g. a column block of the buffer the
+    next projection reads).  u, vt, z (Hkv,D); r_time (Hkv,T,D); r_chan (Hkv,C,D).  No counterpart in the
+    reference, whose operator always allocates its output (`attentions/attn.py:1047`)."""
+    if not q.is_cuda:
+        raise RuntimeError("flash_mvpa: tensors must be on a CUDA device (no CPU path)")
+    lib = _nat.lib()
+    q, k, v = _rows(q), _rows(k), _rows(v)
+    u, vt, z, r_time, r_chan = (x.contiguous() for x in (u, vt, z, r_time, r_chan))
+    es = out.element_size()
+    if out.stride(-1) != 1 or any((st * es) % 16 for st in out.stride()[:-1]) or out.data_ptr() % 16 or out.shape != q.shape:
+        raise RuntimeError("flash_mvpa_into: `out` must have q's shape, a contiguous last dimension and 16-byte aligned strides")
+    prob = _problem(q, k, r_time, r_chan, sm_scale, window_size)
+    nbytes = lib.mvpa_fwd_workspace_bytes(ctypes.byref(prob))
+    ws = torch.empty(max(nbytes, 16), device=q.device, dtype=torch.uint8)
+    tq, tk, tv, to = _tensor(q), _tensor(k), _tensor(v), _tensor(out)
+    with torch.cuda.device(q.device):
+        st = lib.mvpa_fwd(ctypes.byref(prob), ctypes.byref(tq), ctypes.byref(tk), ctypes.byref(tv),
+                          u.data_ptr(), vt.data_ptr(), z.data_ptr(), r_time.data_ptr(), r_chan.data_ptr(),
+                          ctypes.byref(to), None, ws.data_ptr(), nbytes, _stream())
+    _nat.check(st, "mvpa_fwd")
+    if _CHECK_STATUS and nbytes:
+        _nat.check(lib.mvpa_workspace_status(ws.data_ptr(), nbytes, _stream()), "mvpa_fwd kernels")
+    return out
+
+
 def flash_mvpa(q, q_bias, q_btime, q_bchan, k_glob, k_time, k_chan, v, causal, sm_scale,
                window_size=0, p_drop=0.0, sequence_parallel=False, rel_bias_time=True,
                rel_bias_chan=True, generator=None, q_time_range=None):

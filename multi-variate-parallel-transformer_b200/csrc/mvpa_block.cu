@@ -1,0 +1,475 @@
+// HBM-bound kernels around the attention of an MVPFormer block, encoder and heads:
+//
+//   rmsnorm / add_rmsnorm   `ln_1`, `ln_f` and the residual sum of the parallel block
+//                           (`models/mvpformer.py:132-147`: h = x + MLP(ln_1 x) + Attn(ln_1 x)),
+//                           one pass over the hidden state instead of three
+//   silu_mul                the SwiGLU gate of the MLP (`LlamaMLP`: down(silu(gate x) * up x)) on a
+//                           strided view of a fused gate|up projection
+//   wave_encode             `WaveEncoder.block` + its RMSNorm (`models/fftencoder.py:79-97`): all levels
+//                           of the periodic db4 wavelet transform of one segment in shared memory,
+//                           concatenated coarse-to-fine, normalised, written once in the model's dtype
+//   channel_mean            the classification readout `out[:, -1].mean(dim=1)` (`models/mvpformer.py:951-953`)
+//   contrastive_logits      cosine similarity of each prediction with its target and K sampled negatives
+//                           (`models/mvpformer.py:574-594`) without materialising the (tokens, 1+K, E) targets
+//
+// Every kernel moves 16 bytes per thread per access, keeps a row in registers (one warp per row)
+// or shared memory (one CTA per segment) and reduces with warp shuffles.
+#include <cuda_bf16.h>
+
+#include "mvpa_common.cuh"
+
+namespace mvpa {
+namespace {
+
+constexpr int kWarpsPerCta = 8;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+template <typename T>
+struct Vec;  // 16 bytes of T
+template <>
+struct Vec<__nv_bfloat16> {
+  static constexpr int N = 8;
+  __device__ static void load(const __nv_bfloat16* p, float (&f)[8]) {
+    const uint4 r = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+  __device__ static void store(__nv_bfloat16* p, const float (&f)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 v = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&v);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  __device__ static float round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+};
+template <>
+struct Vec<float> {
+  static constexpr int N = 4;
+  __device__ static void load(const float* p, float (&f)[4]) {
+    const float4 r = *reinterpret_cast<const float4*>(p);
+    f[0] = r.x; f[1] = r.y; f[2] = r.z; f[3] = r.w;
+  }
+  __device__ static void store(float* p, const float (&f)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+  }
+  __device__ static float round(float x) { return x; }
+};
+
+// y = rmsnorm(h) * w with h = x (+ a), h optionally written out.  One warp per row; the row stays in
+// registers between the sum of squares and the scaling (NV 16-byte vectors per lane).
+template <typename T, int NV>
+__global__ void __launch_bounds__(kWarpsPerCta * 32) rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ a,
+                                                                    const T* __restrict__ w, T* __restrict__ h_out,
+                                                                    T* __restrict__ y, int64_t rows, int E, float eps) {
+  constexpr int N = Vec<T>::N;
+  const int64_t row = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const T* xr = x + row * E;
+  float v[NV][N];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int col = (i * 32 + lane) * N;
+    if (col < E) {
+      Vec<T>::load(xr + col, v[i]);
+      if (a != nullptr) {
+        float b[N];
+        Vec<T>::load(a + row * E + col, b);
+#pragma unroll
+        for (int e = 0; e < N; ++e) v[i][e] = Vec<T>::round(v[i][e] + b[e]);  // the sum lives in T, as in eager PyTorch
+        if (h_out != nullptr) Vec<T>::store(h_out + row * E + col, v[i]);
+      }
+#pragma unroll
+      for (int e = 0; e < N; ++e) ss += v[i][e] * v[i][e];
+    }
+  }
+  const float rstd = rsqrtf(warp_sum(ss) / (float)E + eps);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int col = (i * 32 + lane) * N;
+    if (col < E) {
+      float g[N];
+      Vec<T>::load(w + col, g);
+#pragma unroll
+      for (int e = 0; e < N; ++e) g[e] = v[i][e] * rstd * g[e];
+      Vec<T>::store(y + row * E + col, g);
+    }
+  }
+}
+
+// out = silu(gate) * up, elementwise, rows of `width` elements at independent leading dimensions.
+template <typename T>
+__global__ void __launch_bounds__(256) silu_mul_kernel(const T* __restrict__ gate, const T* __restrict__ up, int64_t ld_in,
+                                                       T* __restrict__ out, int64_t ld_out, int64_t rows, int width) {
+  constexpr int N = Vec<T>::N;
+  const int vec_per_row = width / N;
+  const int64_t total = rows * vec_per_row;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / vec_per_row;
+    const int c = (int)(i % vec_per_row) * N;
+    float g[N], u[N];
+    Vec<T>::load(gate + r * ld_in + c, g);
+    Vec<T>::load(up + r * ld_in + c, u);
+#pragma unroll
+    for (int e = 0; e < N; ++e) g[e] = Vec<T>::round(g[e] / (1.f + __expf(-g[e]))) * u[e];
+    Vec<T>::store(out + r * ld_out + c, g);
+  }
+}
+
+constexpr int kMaxLevels = 16;
+struct WaveLevels {
+  int n_levels;
+  int len[kMaxLevels + 1];  // len[0] = segment length, len[l+1] = coefficients of level l+1
+  int out_off[kMaxLevels];  // where the detail coefficients of level l+1 start in the output row
+  int total;                // sum of all detail lengths + the last approximation
+};
+struct WaveFilters {
+  float lo[8], hi[8];  // decomposition filters (8 taps: db4)
+};
+
+// One CTA per segment: every level of the periodic wavelet transform in shared memory.
+//   cA[k] = sum_m lo[m] x[(2k + 1 - m) mod n],  cD likewise with hi,  k < (n + 7) / 2
+// (periodic extension of the level's own input, even or odd; n_out = floor((n + 8 - 1) / 2)).
+// Output row: [cA_L, cD_L, cD_{L-1}, ..., cD_1], then RMSNorm over the whole row, times `w`.
+template <typename Tin, typename Tout>
+__global__ void __launch_bounds__(256) wave_encode_kernel(const Tin* __restrict__ x, int64_t ld_x, const WaveLevels lv,
+                                                          const WaveFilters flt, const Tout* __restrict__ w,
+                                                          Tout* __restrict__ out, int64_t ld_out, float eps) {
+  extern __shared__ float smem[];
+  float* coef = smem;                        // [total]
+  float* buf0 = coef + ((lv.total + 3) & ~3);  // level input  (at most len[0])
+  float* buf1 = buf0 + ((lv.len[0] + 3) & ~3);  // level output (at most len[1])
+  __shared__ float s_red[8];
+  const int64_t row = blockIdx.x;
+  const Tin* xr = x + row * ld_x;
+  for (int i = threadIdx.x; i < lv.len[0]; i += blockDim.x) buf0[i] = to_f32<Tin>(xr[i]);
+  __syncthreads();
+  float* src = buf0;
+  float* dst = buf1;
+  for (int l = 0; l < lv.n_levels; ++l) {
+    const int n = lv.len[l], m = lv.len[l + 1];
+    const bool last = l == lv.n_levels - 1;
+    float* det = coef + lv.out_off[l];
+    float* app = last ? coef : dst;
+    for (int k = threadIdx.x; k < m; k += blockDim.x) {
+      float a = 0.f, d = 0.f;
+      int idx = (2 * k + 1) % n;  // tap m = 0 reads x[2k+1], tap m reads x[2k+1-m]
+#pragma unroll
+      for (int t = 0; t < 8; ++t) {
+        const float v = src[idx];
+        a = fmaf(flt.lo[t], v, a);
+        d = fmaf(flt.hi[t], v, d);
+        idx = idx == 0 ? n - 1 : idx - 1;
+      }
+      app[k] = a;
+      det[k] = d;
+    }
+    __syncthreads();
+    float* t = src; src = dst; dst = t;
+  }
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < lv.total; i += blockDim.x) ss += coef[i] * coef[i];
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += s_red[i];
+  const float rstd = rsqrtf(tot / (float)lv.total + eps);
+  Tout* orow = out + row * ld_out;
+  for (int i = threadIdx.x; i < (int)ld_out; i += blockDim.x)
+    orow[i] = i < lv.total ? from_f32<Tout>(coef[i] * rstd * to_f32<Tout>(w[i])) : from_f32<Tout>(0.f);
+}
+
+// out[b, :] = mean over channels of h[b, T-1, :, :]   (h is (B, T, C, E), contiguous)
+template <typename T>
+__global__ void __launch_bounds__(256) channel_mean_kernel(const T* __restrict__ h, T* __restrict__ out, int Tn, int C,
+                                                           int E) {
+  const int b = blockIdx.y;
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= E) return;
+  const T* p = h + (((int64_t)b * Tn + (Tn - 1)) * C) * E + e;
+  float acc = 0.f;
+  for (int c = 0; c < C; ++c) acc += to_f32<T>(p[(int64_t)c * E]);
+  out[(int64_t)b * E + e] = from_f32<T>(acc / (float)C);
+}
+
+// Contrastive logits.  pred, enc: (B, T, C, E).  For every target position (b, t >= 1, c):
+//   row n = (b (T-1) + (t-1)) C + c,  p = pred[b, t-1, c],  candidate 0 = enc[b, t, c],
+//   candidate j = enc_flat[neg[b, t, c, j-1]];  logits[n, j] = cos(p, candidate j) / temp,
+//   -inf for a negative that equals the positive (|neg - pos| < 1e-8 + 1e-5 |pos|).
+// One warp per target position; p and the positive stay in registers while the negatives stream by.
+template <typename T, int NV>
+__global__ void __launch_bounds__(kWarpsPerCta * 32) contrastive_kernel(const T* __restrict__ pred, const T* __restrict__ enc,
+                                                                        const int* __restrict__ neg, float* __restrict__ logits,
+                                                                        int B, int Tn, int C, int E, int K, float inv_temp) {
+  constexpr int N = Vec<T>::N;
+  const int64_t n = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int64_t rows = (int64_t)B * (Tn - 1) * C;
+  if (n >= rows) return;
+  const int c = (int)(n % C);
+  const int t = (int)((n / C) % (Tn - 1)) + 1;
+  const int b = (int)(n / ((int64_t)C * (Tn - 1)));
+  const int64_t tok_pos = ((int64_t)b * Tn + t) * C + c, tok_pred = tok_pos - C;
+  float p[NV][N], q[NV][N];
+  float pp = 0.f, qq = 0.f, pq = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int col = (i * 32 + lane) * N;
+    if (col < E) {
+      Vec<T>::load(pred + tok_pred * E + col, p[i]);
+      Vec<T>::load(enc + tok_pos * E + col, q[i]);
+#pragma unroll
+      for (int e = 0; e < N; ++e) {
+        pp += p[i][e] * p[i][e];
+        qq += q[i][e] * q[i][e];
+        pq += p[i][e] * q[i][e];
+      }
+    }
+  }
+  pp = warp_sum(pp); qq = warp_sum(qq); pq = warp_sum(pq);
+  const float np_ = fmaxf(sqrtf(pp), 1e-8f), nq = sqrtf(qq);
+  float* lrow = logits + n * (K + 1);
+  if (lane == 0) lrow[0] = pq / (np_ * fmaxf(nq, 1e-8f)) * inv_temp;
+  for (int j = 0; j < K; ++j) {
+    const int64_t src = neg[tok_pos * K + j];
+    float rr = 0.f, pr = 0.f, dd = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int col = (i * 32 + lane) * N;
+      if (col < E) {
+        float r[N];
+        Vec<T>::load(enc + src * E + col, r);
+#pragma unroll
+        for (int e = 0; e < N; ++e) {
+          rr += r[e] * r[e];
+          pr += p[i][e] * r[e];
+          const float df = Vec<T>::round(r[e] - q[i][e]);
+          dd += df * df;
+        }
+      }
+    }
+    rr = warp_sum(rr); pr = warp_sum(pr); dd = warp_sum(dd);
+    if (lane == 0) {
+      const bool same = sqrtf(dd) < 1e-8f + 1e-5f * nq;
+      lrow[j + 1] = same ? -INFINITY : pr / (np_ * fmaxf(sqrtf(rr), 1e-8f)) * inv_temp;
+    }
+  }
+}
+
+template <typename T>
+int launch_rmsnorm(const void* x, const void* a, const void* w, void* h_out, void* y, int64_t rows, int E, float eps,
+                   cudaStream_t s) {
+  constexpr int N = Vec<T>::N;
+  const unsigned grid = (unsigned)((rows + kWarpsPerCta - 1) / kWarpsPerCta);
+  const int nv = (E / N + 31) / 32;
+#define MVPA_RMS(NV)                                                                                             \
+  rmsnorm_kernel<T, NV><<<grid, kWarpsPerCta * 32, 0, s>>>((const T*)x, (const T*)a, (const T*)w, (T*)h_out, (T*)y, \
+                                                            rows, E, eps)
+  if (nv <= 2) MVPA_RMS(2);
+  else if (nv <= 4) MVPA_RMS(4);
+  else if (nv <= 8) MVPA_RMS(8);
+  else MVPA_RMS(16);
+#undef MVPA_RMS
+  count_launch();
+  MVPA_CUDA_CHECK(cudaGetLastError());
+  return MVPA_OK;
+}
+
+int check_rows(const char* what, int64_t rows, int width, int dtype, int max_vectors) {
+  if (dtype != MVPA_F32 && dtype != MVPA_BF16) {
+    set_error("%s: element type must be MVPA_F32 or MVPA_BF16", what);
+    return MVPA_ERR_DTYPE;
+  }
+  const int n = dtype == MVPA_F32 ? 4 : 8;
+  if (rows <= 0 || width <= 0 || width % n != 0 || (max_vectors > 0 && width / n > 32 * max_vectors)) {
+    set_error("%s: %lld rows of %d elements: the width must be a positive multiple of %d%s", what, (long long)rows, width,
+              n, max_vectors > 0 ? " and at most 512 sixteen-byte vectors" : "");
+    return MVPA_ERR_SHAPE;
+  }
+  if (rows > (int64_t)1 << 31) {
+    set_error("%s: too many rows (%lld)", what, (long long)rows);
+    return MVPA_ERR_SHAPE;
+  }
+  return MVPA_OK;
+}
+
+bool aligned16(const void* p) { return p != nullptr && ((uintptr_t)p & 15) == 0; }
+
+}  // namespace
+}  // namespace mvpa
+
+using namespace mvpa;
+
+extern "C" {
+
+int mvpa_rmsnorm(const void* x, const void* add, const void* weight, void* sum_out, void* y, int64_t rows,
+                 int32_t width, float eps, int32_t dtype, void* cuda_stream) {
+  int rc = check_rows("mvpa_rmsnorm", rows, width, dtype, 16);
+  if (rc) return rc;
+  if (!aligned16(x) || !aligned16(weight) || !aligned16(y) || (add != nullptr && !aligned16(add)) ||
+      (sum_out != nullptr && !aligned16(sum_out))) {
+    set_error("mvpa_rmsnorm: x, weight, y (and add, sum_out when given) must be 16-byte aligned and not NULL");
+    return MVPA_ERR_ALIGNMENT;
+  }
+  cudaStream_t s = (cudaStream_t)cuda_stream;
+  return dtype == MVPA_F32 ? launch_rmsnorm<float>(x, add, weight, sum_out, y, rows, width, eps, s)
+                           : launch_rmsnorm<__nv_bfloat16>(x, add, weight, sum_out, y, rows, width, eps, s);
+}
+
+int mvpa_silu_mul(const void* gate, const void* up, int64_t ld_in, void* out, int64_t ld_out, int64_t rows,
+                  int32_t width, int32_t dtype, void* cuda_stream) {
+  int rc = check_rows("mvpa_silu_mul", rows, width, dtype, 0);
+  if (rc) return rc;
+  const int n = dtype == MVPA_F32 ? 4 : 8;
+  if (!aligned16(gate) || !aligned16(up) || !aligned16(out) || ld_in % n != 0 || ld_out % n != 0 || ld_in < width ||
+      ld_out < width) {
+    set_error("mvpa_silu_mul: pointers must be 16-byte aligned, leading dimensions multiples of %d and >= the width", n);
+    return MVPA_ERR_ALIGNMENT;
+  }
+  cudaStream_t s = (cudaStream_t)cuda_stream;
+  const int64_t total = rows * (width / n);
+  const unsigned grid = (unsigned)((total + 255) / 256 < (int64_t)device_sm_count() * 16 ? (total + 255) / 256
+                                                                                         : (int64_t)device_sm_count() * 16);
+  if (dtype == MVPA_F32)
+    silu_mul_kernel<float><<<grid, 256, 0, s>>>((const float*)gate, (const float*)up, ld_in, (float*)out, ld_out, rows, width);
+  else
+    silu_mul_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, ld_in,
+                                                       (__nv_bfloat16*)out, ld_out, rows, width);
+  count_launch();
+  MVPA_CUDA_CHECK(cudaGetLastError());
+  return MVPA_OK;
+}
+
+int32_t mvpa_wave_encode_size(int32_t segment_len, int32_t* level_sizes, int32_t max_levels) {
+  // db4: 8 taps.  Levels while the input is at least as long as the filter support allows
+  // (floor(log2(len / 7))), each producing floor((n + 7) / 2) coefficients.
+  if (segment_len < 8) return 0;
+  int levels = 0;
+  for (int v = segment_len / 7; v > 1; v >>= 1) ++levels;
+  if (levels > kMaxLevels) levels = kMaxLevels;
+  int n = segment_len, total = 0;
+  for (int l = 0; l < levels; ++l) {
+    n = (n + 7) / 2;
+    if (level_sizes != nullptr && l < max_levels) level_sizes[l] = n;
+    total += n;
+  }
+  return total + n;  // + the last approximation
+}
+
+int mvpa_wave_encode(const void* x, int64_t ld_x, int32_t x_dtype, const float* dec_lo, const float* dec_hi,
+                     const void* weight, void* out, int64_t ld_out, int32_t out_dtype, int64_t rows,
+                     int32_t segment_len, float eps, void* cuda_stream) {
+  const int total = mvpa_wave_encode_size(segment_len, nullptr, 0);
+  if (total == 0 || rows <= 0 || rows > (int64_t)1 << 31 || segment_len > 16384) {
+    set_error("mvpa_wave_encode: %lld segments of %d samples (8 .. 16384 samples per segment)", (long long)rows, segment_len);
+    return MVPA_ERR_SHAPE;
+  }
+  if ((x_dtype != MVPA_F32 && x_dtype != MVPA_BF16) || (out_dtype != MVPA_F32 && out_dtype != MVPA_BF16)) {
+    set_error("mvpa_wave_encode: element types must be MVPA_F32 or MVPA_BF16");
+    return MVPA_ERR_DTYPE;
+  }
+  if (x == nullptr || out == nullptr || weight == nullptr || dec_lo == nullptr || dec_hi == nullptr || ld_x < segment_len ||
+      ld_out < total) {
+    set_error("mvpa_wave_encode: NULL pointer, or a leading dimension shorter than its row (%d in, %d out)", segment_len, total);
+    return MVPA_ERR_SHAPE;
+  }
+  WaveLevels lv;
+  WaveFilters flt;
+  for (int i = 0; i < 8; ++i) { flt.lo[i] = dec_lo[i]; flt.hi[i] = dec_hi[i]; }  // host pointers: eight taps each
+  lv.n_levels = 0;
+  for (int v = segment_len / 7; v > 1; v >>= 1) ++lv.n_levels;
+  if (lv.n_levels > kMaxLevels) lv.n_levels = kMaxLevels;
+  lv.len[0] = segment_len;
+  for (int l = 0; l < lv.n_levels; ++l) lv.len[l + 1] = (lv.len[l] + 7) / 2;
+  lv.total = total;
+  int off = total;
+  for (int l = 0; l < lv.n_levels; ++l) {  // finest details last
+    off -= lv.len[l + 1];
+    lv.out_off[l] = off;
+  }
+  const size_t smem = sizeof(float) * (((total + 3) & ~3) + ((lv.len[0] + 3) & ~3) + ((lv.len[1] + 3) & ~3));
+  cudaStream_t s = (cudaStream_t)cuda_stream;
+#define MVPA_WAVE(TI, TO)                                                                                         \
+  do {                                                                                                            \
+    MVPA_CUDA_CHECK(cudaFuncSetAttribute(wave_encode_kernel<TI, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                         (int)smem));                                                             \
+    wave_encode_kernel<TI, TO><<<(unsigned)rows, 256, smem, s>>>((const TI*)x, ld_x, lv, flt, (const TO*)weight,   \
+                                                                 (TO*)out, ld_out, eps);                          \
+  } while (0)
+  if (x_dtype == MVPA_F32 && out_dtype == MVPA_F32) MVPA_WAVE(float, float);
+  else if (x_dtype == MVPA_F32) MVPA_WAVE(float, __nv_bfloat16);
+  else if (out_dtype == MVPA_F32) MVPA_WAVE(__nv_bfloat16, float);
+  else MVPA_WAVE(__nv_bfloat16, __nv_bfloat16);
+#undef MVPA_WAVE
+  count_launch();
+  MVPA_CUDA_CHECK(cudaGetLastError());
+  return MVPA_OK;
+}
+
+int mvpa_channel_mean(const void* h, void* out, int32_t B, int32_t T, int32_t C, int32_t E, int32_t dtype,
+                      void* cuda_stream) {
+  if (B <= 0 || T <= 0 || C <= 0 || E <= 0 || h == nullptr || out == nullptr) {
+    set_error("mvpa_channel_mean: sizes must be positive and pointers not NULL");
+    return MVPA_ERR_SHAPE;
+  }
+  if (dtype != MVPA_F32 && dtype != MVPA_BF16) {
+    set_error("mvpa_channel_mean: element type must be MVPA_F32 or MVPA_BF16");
+    return MVPA_ERR_DTYPE;
+  }
+  cudaStream_t s = (cudaStream_t)cuda_stream;
+  const dim3 grid((E + 255) / 256, B);
+  if (dtype == MVPA_F32) channel_mean_kernel<float><<<grid, 256, 0, s>>>((const float*)h, (float*)out, T, C, E);
+  else channel_mean_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)h, (__nv_bfloat16*)out, T, C, E);
+  count_launch();
+  MVPA_CUDA_CHECK(cudaGetLastError());
+  return MVPA_OK;
+}
+
+int mvpa_contrastive_logits(const void* pred, const void* enc, const int32_t* negatives, float* logits, int32_t B,
+                            int32_t T, int32_t C, int32_t E, int32_t K, float temperature, int32_t dtype,
+                            void* cuda_stream) {
+  if (B <= 0 || T < 2 || C <= 0 || K < 0 || temperature <= 0.f) {
+    set_error("mvpa_contrastive_logits: B, C > 0, T >= 2, K >= 0 and a positive temperature are required");
+    return MVPA_ERR_SHAPE;
+  }
+  int rc = check_rows("mvpa_contrastive_logits", (int64_t)B * (T - 1) * C, E, dtype, 8);
+  if (rc) return rc;
+  if (!aligned16(pred) || !aligned16(enc) || logits == nullptr || (K > 0 && negatives == nullptr)) {
+    set_error("mvpa_contrastive_logits: pred and enc must be 16-byte aligned; logits (and negatives when K > 0) not NULL");
+    return MVPA_ERR_ALIGNMENT;
+  }
+  cudaStream_t s = (cudaStream_t)cuda_stream;
+  const int64_t rows = (int64_t)B * (T - 1) * C;
+  const unsigned grid = (unsigned)((rows + kWarpsPerCta - 1) / kWarpsPerCta);
+  const int n = dtype == MVPA_F32 ? 4 : 8;
+  const int nv = (E / n + 31) / 32;
+#define MVPA_CL(TT, NV)                                                                                          \
+  contrastive_kernel<TT, NV><<<grid, kWarpsPerCta * 32, 0, s>>>((const TT*)pred, (const TT*)enc, negatives, logits, B, T, \
+                                                                C, E, K, 1.f / temperature)
+  if (dtype == MVPA_F32) {
+    if (nv <= 2) MVPA_CL(float, 2); else if (nv <= 4) MVPA_CL(float, 4); else MVPA_CL(float, 8);
+  } else {
+    if (nv <= 2) MVPA_CL(__nv_bfloat16, 2); else if (nv <= 4) MVPA_CL(__nv_bfloat16, 4); else MVPA_CL(__nv_bfloat16, 8);
+  }
+#undef MVPA_CL
+  count_launch();
+  MVPA_CUDA_CHECK(cudaGetLastError());
+  return MVPA_OK;
+}
+
+}  // extern "C"

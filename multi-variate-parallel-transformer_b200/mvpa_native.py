@@ -91,7 +91,8 @@ class Tensor(ctypes.Structure):
 EXPORTS = ("mvpa_fwd", "mvpa_bwd", "mvpa_fwd_workspace_bytes", "mvpa_bwd_workspace_bytes",
            "mvpa_last_error_string", "mvpa_launch_count", "mvpa_abi_version",
            "mvpa_workspace_status", "mvpa_fwd_noalloc", "mvpa_bwd_status", "mvpa_noalloc_status",
-           "mvpa_selftest_wait_timeout")
+           "mvpa_selftest_wait_timeout", "mvpa_rmsnorm", "mvpa_silu_mul", "mvpa_wave_encode_size",
+           "mvpa_wave_encode", "mvpa_channel_mean", "mvpa_contrastive_logits")
 ABI_VERSION = 3   # mvpa_abi_version() of the header this shim was written against
 
 
@@ -131,6 +132,20 @@ def lib() -> ctypes.CDLL:
         L.mvpa_noalloc_status.argtypes = [vp]
         L.mvpa_selftest_wait_timeout.restype = ctypes.c_int
         L.mvpa_selftest_wait_timeout.argtypes = [vp, ctypes.c_size_t, ctypes.c_uint32, vp]
+        i32, i64, f32 = ctypes.c_int32, ctypes.c_int64, ctypes.c_float
+        L.mvpa_rmsnorm.restype = ctypes.c_int
+        L.mvpa_rmsnorm.argtypes = [vp, vp, vp, vp, vp, i64, i32, f32, i32, vp]
+        L.mvpa_silu_mul.restype = ctypes.c_int
+        L.mvpa_silu_mul.argtypes = [vp, vp, i64, vp, i64, i64, i32, i32, vp]
+        L.mvpa_wave_encode_size.restype = i32
+        L.mvpa_wave_encode_size.argtypes = [i32, ctypes.POINTER(i32), i32]
+        L.mvpa_wave_encode.restype = ctypes.c_int
+        L.mvpa_wave_encode.argtypes = [vp, i64, i32, ctypes.POINTER(f32), ctypes.POINTER(f32), vp, vp, i64, i32, i64,
+                                       i32, f32, vp]
+        L.mvpa_channel_mean.restype = ctypes.c_int
+        L.mvpa_channel_mean.argtypes = [vp, vp, i32, i32, i32, i32, i32, vp]
+        L.mvpa_contrastive_logits.restype = ctypes.c_int
+        L.mvpa_contrastive_logits.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, vp]
         L.mvpa_last_error_string.restype = ctypes.c_char_p
         L.mvpa_launch_count.restype = ctypes.c_uint64
         L.mvpa_abi_version.restype = ctypes.c_int
