@@ -13,8 +13,14 @@ data-path collective: batch elements are independent).
   roofline  dominant kernel vs the measured dense bf16 peak (MEASURED_PEAKS.json, burst figure)
   cpu_baseline  the materialised PyTorch attention (oracle/mvpa_port_torch.py, a port of the
             reference's `_rel_attn`) on the host cores, on a bounded sample of the same workload
+  extra     model_cfg4 / model_cfg5: full-model forward tokens/s on synthetic iEEG, the batch split over the
+            ranks; long_sample_16k (N >= 2): one 16k-token sample with its time axis spread over the ranks and
+            the K/V all-gather overlapped; the 16k-token and config-3 operator points, forward and forward +
+            backward; triton_reference: the reference's own Triton operator on the same GPU; cpu_config1:
+            BASELINE config 1 on the host cores
 
-`--impl reference` times only that CPU port (rank 0), as the reference arm.
+`--impl reference` times only that CPU port (rank 0), as the reference arm; `--impl triton` runs the
+reference's Triton operator staged under baseline/_ref/ (what `extra.triton_reference` calls in a child process).
 """
 import argparse
 import json
@@ -146,9 +152,21 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(sm)}
 
 
+def use_all_host_threads(torch):
+    """`torch.distributed.run` exports OMP_NUM_THREADS=1 to its workers; the CPU legs use every core the
+    process may run on, whatever launched them, so that `cores` is the same at every GPU count."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(1, n))
+    return torch.get_num_threads()
+
+
 def cpu_port_time(sample, reps=1, seed=1):
     """Seconds per pass of the materialised PyTorch attention over `sample` on the host cores."""
     import torch
+    use_all_host_threads(torch)
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import mvpa_port_torch as port
     B, H, Hkv, T, C, D = (sample[k] for k in ("B", "H", "Hkv", "T", "C", "D"))
@@ -164,6 +182,32 @@ def cpu_port_time(sample, reps=1, seed=1):
             port.rel_attn(*args, D ** -0.5, sample["window"])
             ts.append(time.perf_counter() - t0)
     return statistics.median(ts), torch.get_num_threads()
+
+
+def cpu_config1():
+    """BASELINE config 1 exactly: the materialised attention (`layers/mvpa.py:173-278`, here its port) at
+    batch 1, 16 channels x 32 segments, 4 heads, head_dim 64, fp32, seed 0, on the host cores:
+    3 warm-up passes, 20 timed."""
+    import torch
+    threads = use_all_host_threads(torch)
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import mvpa_port_torch as port
+    B, H, Hkv, T, C, D = 1, 4, 4, 32, 16, 64
+    g = torch.Generator().manual_seed(0)
+    N = T * C
+    r = lambda *s: torch.randn(*s, generator=g)
+    a = (r(B, H, N, D), r(Hkv, D), r(Hkv, D), r(Hkv, D), r(B, Hkv, N, D), r(Hkv, T, D), r(Hkv, C, D), r(B, Hkv, N, D))
+    ts = []
+    with torch.no_grad():
+        for i in range(23):
+            t0 = time.perf_counter()
+            port.rel_attn(*a, D ** -0.5, 10)
+            if i >= 3:
+                ts.append(time.perf_counter() - t0)
+    f = flops(B, H, T, C, D)["f_alg"]
+    return {"workload": "config 1: fp32, B1 x 4 heads x 512 tokens (16 ch x 32 seg), head_dim 64", "reps": len(ts),
+            "mean_ms": 1e3 * statistics.mean(ts), "median_ms": 1e3 * statistics.median(ts),
+            "tflops_f_alg": f / statistics.median(ts) / 1e12, "torch_threads": threads, "cpu_count": os.cpu_count()}
 
 
 def run_reference(args):
@@ -283,12 +327,228 @@ def time_layer(torch, dev, flush, reps=10, warm=3):
             "fwd_bwd_ms": train_ms, "fwd_bwd_tokens_per_s": N / (train_ms * 1e-3)}
 
 
+MODELS = {
+    # BASELINE config 4: MVPFormer-S classification (`configs/mvpformer_s_classification.yaml`), batch 8, 64 channels,
+    # 128 segments of 2560 samples; n_positions raised from the YAML's 110 to 128 so that 128 segments have embeddings
+    "cfg4": dict(arch=dict(n_embd=768, n_layer=12, n_head=12, n_head_kv=4, n_inner=1728), B=8, T=128, C=64, task="classify",
+                 seed=3, tflop_per_sample=1.86),
+    # BASELINE config 5: MVPFormer generative next-state forward (`configs/mvpformer_generative.yaml`), batch 32,
+    # 128 channels x 128 segments (16384 tokens per sample)
+    "cfg5": dict(arch=dict(n_embd=2048, n_layer=24, n_head=16, n_head_kv=8, n_inner=5632), B=32, T=128, C=128,
+                 task="generative", seed=4, tflop_per_sample=53.2),
+}
+
+
+def time_model(torch, dist, dev, name, world, rank, flush, steps=2, warm=1):
+    """Full-model forward (encoder -> MVPFormer stack -> head) on synthetic iEEG created on the device, the
+    batch split across the ranks (batch elements are independent; no data-path collective).  Random-init
+    weights of the named architecture, bf16.  Returns whole-job tokens/s (max time over ranks)."""
+    import models
+    from attentions import flash_mvpa_into
+    from eeg_datasets import synthetic_ieeg
+    spec = MODELS[name]
+    a, T, C, n = spec["arch"], spec["T"], spec["C"], 2560
+    B_total = spec["B"]
+    B = B_total // world if B_total % world == 0 else 0
+    if B == 0:
+        return {"skipped": f"batch {B_total} does not split over {world} ranks"}
+    E = a["n_embd"]
+    torch.manual_seed(100 + spec["seed"])
+    with torch.device(dev):
+        cfg = models.MVPFormerConfig(n_positions=128, n_channels=128, **a)
+        gen = spec["task"] == "generative"
+        cls = models.HMVPFormer if gen else models.ClassificationHMVPFormer
+        task = cls(cfg, models.WaveEncoder(n, E), models.MVPFormerHead(E, None if gen else 2), num_negatives=30)
+    task = task.to(dev).to(torch.bfloat16).eval()
+    x = synthetic_ieeg(B, T, C, n, seed=1000 * spec["seed"] + rank, device=dev)   # fp32, in HBM
+    neg = task._negative_indices((B, T, C), torch.Generator(device=dev).manual_seed(7)) if gen and B > 1 else None
+
+    def step():
+        if gen and B > 1:
+            return task.next_state_logits(x, negatives=neg)
+        if gen:                                            # one sample per rank: no other sample to draw negatives from
+            out, _ = task._common_forward(x)
+            return task.head(out)
+        return task.classify(x)
+
+    ms = []
+    for i in range(warm + steps):
+        flush.add_(1)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        y = step()
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= warm:
+            ms.append(e0.elapsed_time(e1))
+    finite = bool(torch.isfinite(y.float()).all())
+    # share of the attention kernels: the same operator call on tensors of the layer's shapes, times the layer count
+    H, Hkv = a["n_head"], a["n_head_kv"]
+    D, N = E // H, T * C
+    r = lambda *sh: torch.randn(*sh, device=dev, dtype=torch.bfloat16)
+    q, k, v, o = r(B, N, H, D), r(B, N, Hkv, D), r(B, N, Hkv, D), r(B, N, H, D)
+    small = (r(Hkv, D), r(Hkv, D), r(Hkv, D))
+    rt, rc = r(Hkv, T, D), r(Hkv, C, D)
+    att = []
+    for i in range(4):
+        flush.add_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        flash_mvpa_into(o.permute(0, 2, 1, 3), q.permute(0, 2, 1, 3), *small, k.permute(0, 2, 1, 3), rt, rc,
+                        v.permute(0, 2, 1, 3), D ** -0.5, 10)
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= 1:
+            att.append(e0.elapsed_time(e1))
+    t = torch.tensor([statistics.mean(ms)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    step_ms = float(t.item())
+    del task, x
+    torch.cuda.empty_cache()
+    return {"ms": step_ms, "tokens_per_s": B_total * N / (step_ms * 1e-3), "global_batch": B_total, "per_gpu_batch": B,
+            "tokens_per_sample": N, "share_of_attention": a["n_layer"] * statistics.mean(att) / statistics.mean(ms),
+            "model_tflops_f_alg": spec["tflop_per_sample"] * B_total / (step_ms * 1e-3), "finite": finite,
+            "input": "synthetic 1/f iEEG + 3-8 Hz bursts, fp32, generated on the device", "task": spec["task"]}
+
+
+def time_long_sample(torch, dist, dev, world, rank, flush, one_gpu_ms):
+    """One 16k-token sample (D 128, 16 heads / 8 kv heads) with its time axis spread over the ranks: every rank
+    holds the q / k|v rows of its two zig-zag chunks, K and V are all-gathered over NVLink (NCCL) on a
+    communication stream in two halves, and the rank's two query ranges run against the gathered K/V; the early
+    range starts when the early half has landed.  Strong scaling against the single-GPU forward of the sample."""
+    import attentions
+    import mvpa_shard as ms
+    w = WORKLOADS["16k"][0]
+    H, Hkv, T, C, D = (w[k] for k in ("H", "Hkv", "T", "C", "D"))
+    plan = ms.zigzag_chunks(T, C, world)
+    g = torch.Generator(device=dev).manual_seed(50 + rank)
+    r = lambda *sh: torch.randn(*sh, device=dev, dtype=torch.bfloat16, generator=g)
+    q_loc = [r(1, n * C, H, D) for _, n in plan[rank]]
+    kv_loc = [r(1, n * C, 2 * Hkv, D) for _, n in plan[rank]]
+    g2 = torch.Generator(device=dev).manual_seed(49)          # replicated small tensors: same on every rank
+    r2 = lambda *sh: torch.randn(*sh, device=dev, dtype=torch.bfloat16, generator=g2)
+    u, vt, z, rt, rc = r2(1, Hkv, 1, D), r2(1, Hkv, 1, D), r2(1, Hkv, 1, D), r2(1, Hkv, T, D), r2(1, Hkv, C, D)
+    kw = dict(dim=D, dtype=torch.bfloat16, device=dev, batch=1)
+
+    def timed(fn, reps=6, warm=2):
+        out = []
+        for i in range(warm + reps):
+            flush.add_(1)
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= warm:
+                out.append(e0.elapsed_time(e1))
+        t = torch.tensor([statistics.mean(out)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    with torch.no_grad():
+        total = timed(lambda: ms.time_sharded_attention(attentions.flashmvpa, q_loc, u, vt, z, kv_loc, rt, rc, None, T, C,
+                                                        D ** -0.5, 10))
+        gather = timed(lambda: ms.gather_kv(kv_loc, plan, T, C, heads=2 * Hkv, **kw))
+        full = ms.gather_kv(kv_loc, plan, T, C, heads=2 * Hkv, **kw)
+        kf, vf = full[:, :, :Hkv].permute(0, 2, 1, 3), full[:, :, Hkv:].permute(0, 2, 1, 3)
+
+        def attn_only():
+            for (t0, n), ql in zip(plan[rank], q_loc):
+                attentions.flashmvpa(ql.permute(0, 2, 1, 3), u, vt, z, kf, rt, rc, vf, causal=True, sm_scale=D ** -0.5,
+                                     window_size=10, q_time_range=(t0, n))
+        attn = timed(attn_only)
+    return {"ms": total, "tokens_per_s": T * C / (total * 1e-3), "gather_ms": gather, "attention_only_ms": attn,
+            "exposed_gather_ms": max(0.0, total - attn), "speedup_vs_1gpu": one_gpu_ms / total, "one_gpu_ms": one_gpu_ms,
+            "gathered_bytes_per_rank": 2 * Hkv * D * 2 * T * C * (world - 1) // world,
+            "limiter": "the K/V all-gather (2 x 33.5 MB per layer over NVLink): the attention of a rank's shard is shorter"}
+
+
+def run_triton(args):
+    """The reference's own Triton operator (`attentions/attn.py:1317-1366`, unmodified, loaded from
+    baseline/_ref/attentions/) on this GPU: first a small shape checked against this library, then the
+    benchmark workload.  Any failure to compile or launch is reported as text."""
+    import importlib.util
+    import traceback
+    out = {"impl": "triton", "workload": NAME}
+    try:
+        import torch
+        import attentions
+        path = os.path.join(ROOT, "baseline", "_ref", "attentions", "attn.py")
+        if not os.path.exists(path):
+            out["unavailable"] = "baseline/_ref/attentions/attn.py is not staged"
+            print(json.dumps(out))
+            return
+        import triton
+        out["triton_version"] = triton.__version__
+        spec = importlib.util.spec_from_file_location("reference_attentions_attn", path)
+        ref = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(ref)
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(dev)
+        small = dict(B=1, H=2, Hkv=2, T=16, C=16, D=64, window=10)
+        for stage, w in (("small", small), ("workload", WORKLOAD)):
+            _, t = make_inputs(torch, dev, w, seed=1)
+            call = lambda f: f(t["q"], t["u"], t["v"], t["z"], t["k"], t["rt"], t["rc"], t["val"], causal=True,
+                               sm_scale=w["D"] ** -0.5, window_size=w["window"])
+            with torch.no_grad():
+                o_ref = call(ref.flash_mvpa)
+                torch.cuda.synchronize()
+                o_own = call(attentions.flashmvpa)
+                out[stage + "_max_abs_diff_vs_this_library"] = float((o_ref.float() - o_own.float()).abs().max())
+        flush = torch.zeros(64 * 1024 * 1024, dtype=torch.float32, device=dev)
+        ms = []
+        with torch.no_grad():
+            for i in range(3 + args.steps):
+                flush.add_(1)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                call(ref.flash_mvpa)
+                e1.record()
+                torch.cuda.synchronize()
+                if i >= 3:
+                    ms.append(e0.elapsed_time(e1))
+        f = flops(**WORKLOAD)
+        m = statistics.mean(ms)
+        out.update(ms=m, tflops_f_alg=f["f_alg"] / m / 1e9, tflops_f_dense=f["f_dense"] / m / 1e9, steps=len(ms),
+                   includes="_rel_bias (two cuBLAS products into HBM) + _fwd_kernel, as the reference operator runs them")
+    except BaseException as e:  # the error text is the data point
+        out["error"] = f"{type(e).__name__}: {e}"[:1500]
+        out["traceback_tail"] = traceback.format_exc()[-1500:]
+    print(json.dumps(out))
+
+
+def triton_point(args, device_index):
+    """Runs `--impl triton` in a child process (a compiler crash or a long compile must not take the benchmark
+    with it) and returns its JSON."""
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR",
+                                                             "MASTER_PORT", "OMP_NUM_THREADS")}
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    ids = [x for x in vis.split(",") if x.strip()] if vis else None
+    env["CUDA_VISIBLE_DEVICES"] = ids[device_index] if ids and device_index < len(ids) else str(device_index)
+    try:
+        res = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "triton", "--workload", args.workload,
+                              "--steps", "10"], capture_output=True, text=True, timeout=600, env=env)
+        for line in reversed(res.stdout.strip().splitlines()):
+            if line.startswith("{"):
+                return json.loads(line)
+        return {"impl": "triton", "error": "no JSON line", "stderr_tail": res.stderr[-1200:], "returncode": res.returncode}
+    except subprocess.TimeoutExpired:
+        return {"impl": "triton", "error": "child process exceeded 600 s (compile or run); not retried"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference", "triton"],
+                    help="reference: the CPU arm; triton: the reference's Triton operator on this GPU (an extra point)")
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS),
                     help="cfg2 is the benchmark; the others exist for profiling and extra points")
     ap.add_argument("--pass", dest="passes", default="fwd", choices=["fwd", "fwd_bwd"],
@@ -301,6 +561,8 @@ def main():
     WORKLOAD, NAME = WORKLOADS[args.workload]
     if args.impl == "reference":
         return run_reference(args)
+    if args.impl == "triton":
+        return run_triton(args)
 
     import torch
     import torch.distributed as dist
@@ -432,12 +694,28 @@ def main():
                          "flops_per_launch": f["f_alg"],
                          "achieved_dense_convention": f["f_dense"] / (kernel_ms * 1e-3) / 1e12},
         }
+        out["roofline"]["traffic_source"] = "ncu capture summarised under profiles/ (not measured in this run)"
+    extra, ms_16k = {}, None
+    if not args.no_extra:  # points every rank takes part in
+        for name in ("cfg4", "cfg5"):
+            res = time_model(torch, dist, dev, name, world, rank, flush)
+            extra["model_" + name] = res
+        _, tt = make_inputs(torch, dev, WORKLOADS["16k"][0], seed=7)
+        ms_16k = statistics.mean(time_kernel(torch, attentions, tt, WORKLOADS["16k"][0], 10, 3, flush))
+        del tt
+        if world > 1:
+            extra["long_sample_16k"] = time_long_sample(torch, dist, dev, world, rank, flush, ms_16k)
+    if rank == 0:
         if not args.no_extra:
-            extra = {}
+            ff = flops(**WORKLOADS["16k"][0])
+            out["roofline"]["north_star_16k"] = {
+                "workload": WORKLOADS["16k"][1], "ms": ms_16k, "achieved": ff["f_alg"] / ms_16k / 1e9,
+                "frac": ff["f_alg"] / ms_16k / 1e9 / peak, "target_frac": 0.60,
+                "achieved_dense_convention": ff["f_dense"] / ms_16k / 1e9}
             for name, ww in (("16k_tokens_D128_H16_Hkv8_B1", WORKLOADS["16k"][0]),
                              ("cfg3_fwd_B8_T128_C32_D64", WORKLOADS["cfg3"][0])):
                 _, tt = make_inputs(torch, dev, ww, seed=7)
-                m2 = statistics.mean(time_kernel(torch, attentions, tt, ww, 10, 3, flush))
+                m2 = ms_16k if ww is WORKLOADS["16k"][0] else statistics.mean(time_kernel(torch, attentions, tt, ww, 10, 3, flush))
                 ff = flops(**ww)
                 extra[name] = {"ms": m2, "tflops_f_alg": ff["f_alg"] / m2 / 1e9, "tflops_f_dense": ff["f_dense"] / m2 / 1e9,
                                "frac_of_peak_f_alg": ff["f_alg"] / m2 / 1e9 / peak}
@@ -452,8 +730,12 @@ def main():
                 extra[name] = {"ms": m3, "tflops_f_alg": f3 / m3 / 1e9, "frac_of_peak_f_alg": f3 / m3 / 1e9 / peak}
                 del tt, g2
             extra["layer_fwd_16k_tokens_E2048_H16_Hkv8"] = time_layer(torch, dev, flush)
+            if world == 1:  # the reference's Triton operator on this GPU, in a child process
+                extra["triton_reference"] = triton_point(args, local)
+                if not args.no_cpu:
+                    extra["cpu_config1"] = cpu_config1()
             out["extra"] = extra
-        if not args.no_cpu and world == 1:  # the CPU leg belongs to the single-GPU run (torchrun pins OMP threads to 1)
+        if not args.no_cpu and world == 1:  # the CPU leg belongs to the single-GPU run
             sample = dict(w, B=1)
             cpu_port_time(dict(sample, H=1, Hkv=1))  # warm-up: thread pool, allocator
             sec, cores = cpu_port_time(sample, reps=10)  # about 10 s of CPU work

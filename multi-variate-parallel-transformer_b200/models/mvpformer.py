@@ -261,7 +261,7 @@ class HMVPFormer(torch.nn.Module):
         """The draws of `_get_negative_samples` (`:631-660`): for every token, `num_negatives` rows of the
         flattened batch other than the token itself.  (B,T,C,K) int32."""
         bsz, seg_n, ch = shape
-        dev = self.seizure_embeddings.device
+        dev = generator.device if generator is not None else self.head.head.weight.device
         n = bsz * seg_n * ch
         idx = torch.randint((bsz - 1) * (ch * seg_n), (n * self.num_negatives,), device=dev, dtype=torch.int,
                             generator=generator)

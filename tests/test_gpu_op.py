@@ -204,7 +204,13 @@ def test_bf16_single_time_step_or_channel_on_the_tensor_cores(cuda, shape):
     for key, gk in zip(("q", "u", "v", "z", "k", "r_time", "r_chan", "val"), GRADS):
         r = ref[gk]
         err = np.abs(_np(t[key].grad).reshape(r.shape) - r).max()
-        assert err <= BF16_ABS * max(1.0, np.abs(r).max()), (gk, err)
+        # With a single time step (or channel) that relative score is the same for every key of a row, so its
+        # gradient is a row sum of dS, exactly zero: what the kernels return there is the bf16 rounding of dS
+        # (delta is taken from the bf16-rounded O, so sum_k P (dP - delta) is off by ~0.4 % of delta per row)
+        # summed over all rows, which does not scale with the (zero) reference; the fp32 goldens pin the zero.
+        cancels = (gk in ("dr_time", "dv") and shape[3] == 1) or (gk in ("dr_chan", "dz") and shape[4] == 1)
+        tol = 0.25 if cancels else BF16_ABS * max(1.0, np.abs(r).max())
+        assert err <= tol, (gk, err)
 
 
 def test_strided_inputs_match_contiguous(cuda):
