@@ -94,9 +94,11 @@ class FlashMVPA(torch.autograd.Function):
         do = _rows(do)
         prob = _problem(q, k, r_time, r_chan, ctx.sm_scale, ctx.window)
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-        f32 = dict(device=q.device, dtype=torch.float32)
-        du, dvt, dz = (torch.empty(u.shape, **f32) for _ in range(3))
-        drt, drc = torch.empty(r_time.shape, **f32), torch.empty(r_chan.shape, **f32)
+        # the five small gradients leave the library as fp32: one buffer, so that one cast serves all of them
+        shapes = (u.shape, vt.shape, z.shape, r_time.shape, r_chan.shape)
+        sizes = [(math.prod(sh) + 3) // 4 * 4 for sh in shapes]             # 16-byte aligned pieces
+        small = torch.empty(sum(sizes), device=q.device, dtype=torch.float32)
+        du, dvt, dz, drt, drc = (piece[:math.prod(sh)].view(sh) for piece, sh in zip(small.split(sizes), shapes))
         nbytes = lib.mvpa_bwd_workspace_bytes(ctypes.byref(prob))
         ws = torch.empty(max(nbytes, 16), device=q.device, dtype=torch.uint8)
         T = [_tensor(x) for x in (q, k, v, o, do, dq, dk, dv)]
@@ -109,8 +111,9 @@ class FlashMVPA(torch.autograd.Function):
         _nat.check(st, "mvpa_bwd")
         if _CHECK_STATUS:  # debugging aid: synchronises the stream
             _nat.check(lib.mvpa_bwd_status(ctypes.byref(prob), ws.data_ptr(), nbytes, _stream()), "mvpa_bwd kernels")
-        dt = q.dtype
-        return (dq, du.to(dt), dvt.to(dt), dz.to(dt), dk, drt.to(dt), drc.to(dt), dv, None, None, None)
+        small = small.to(q.dtype)
+        du, dvt, dz, drt, drc = (piece[:math.prod(sh)].view(sh) for piece, sh in zip(small.split(sizes), shapes))
+        return (dq, du, dvt, dz, dk, drt, drc, dv, None, None, None)
 
 
 def flash_mvpa_into(out, q, u, vt, z, k, r_time, r_chan, v, sm_scale, window_size=10):

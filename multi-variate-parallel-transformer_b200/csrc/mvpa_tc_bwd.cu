@@ -40,6 +40,19 @@ constexpr int kTmemCols = 512;
 constexpr uint32_t kColS = 0;
 constexpr uint32_t kColDP = 128;
 
+// The per-kv-head accumulators receive one partial from every query-side CTA through global atomics.
+// Floating-point atomics would make the sums depend on the order in which CTAs finish; integer addition is
+// associative, so the partials are added as 64-bit fixed-point numbers with 32 fractional bits (resolution
+// 2.3e-10, range +-2.1e9: gradients of bf16 problems sit many orders inside both) and the result is the same
+// bits on every run.  The reference's kernels use relaxed fp32 atomics here (`attentions/attn.py:683-707`).
+constexpr float kFix = 4294967296.f;  // 2^32
+__device__ __forceinline__ void fix_add(unsigned long long* acc, float x) {
+  atomicAdd(acc, (unsigned long long)__float2ll_rn(x * kFix));
+}
+__device__ __forceinline__ float fix_read(unsigned long long v) {
+  return (float)((double)(long long)v * (1.0 / 4294967296.0));
+}
+
 struct BqMaps {
   CUtensorMap q, k, v, dout, rt, rc;
   CUtensorMap qp, dq;  // stores: Q' rows for the key-side kernel, the dq output
@@ -54,8 +67,9 @@ struct BqArgs {
   // Everything a thread (= query row) reads or writes per row is stored row-innermost, so that the 32
   // rows of a warp touch consecutive addresses.
   float* dtb;          // (B*H, T, N) zero-initialised; slot T-1-(t_i-t_k)
-  float* racc;         // (Hkv, 2, D, 128) fp32, zero-initialised: sum over query rows of dTB^T Q' / dCB^T Q'
-  float* cacc;         // (Hkv, 2, 128)    fp32, zero-initialised: column sums of dTB / dCB (as bf16, like racc)
+  // Accumulators over all query-side CTAs of a kv head, zero-initialised, in 64-bit fixed point (see kFix):
+  unsigned long long* racc;  // (Hkv, 2, D, 128): sum over query rows of dTB^T Q' / dCB^T Q'
+  unsigned long long* cacc;  // (Hkv, 2, 128):    column sums of dTB / dCB (as bf16, like racc)
   // per query row, kept for the key-side kernel (which visits every query tile many times):
   //   Q' = (q+u) c2 as (B*H, N, D) bf16, written through the `qp` tensor map
   __half* cblw;        // (B*H, CP/8, N, 8) channel scores gathered by key channel slot, relative to their max
@@ -867,7 +881,7 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
         const bool jv = which == 0 ? j < T : j < C;
-        float* acc = p.racc + (((size_t)hk * 2 + which) * D + wg * DW) * 128 + j;
+        unsigned long long* acc = p.racc + (((size_t)hk * 2 + which) * D + wg * DW) * 128 + j;
         const uint32_t col = which == 0 ? kQS1 : kQS;
 #pragma unroll 1
         for (int c8 = 0; c8 < DW; c8 += 8) {
@@ -876,14 +890,14 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
           tmem_ld_wait();
           if (jv) {
 #pragma unroll
-            for (int e = 0; e < 8; ++e) atomicAdd(acc + (size_t)(c8 + e) * 128, __uint_as_float(v[e]));
+            for (int e = 0; e < 8; ++e) fix_add(acc + (size_t)(c8 + e) * 128, __uint_as_float(v[e]));
           }
         }
         if (wg == which) {  // column sums: one warpgroup each
           uint32_t cs1;
           tmem_ld1(lane_base + kQDP + 16 * which, cs1);
           tmem_ld_wait();
-          if (jv) atomicAdd(p.cacc + ((size_t)hk * 2 + which) * 128 + j, __uint_as_float(cs1));
+          if (jv) fix_add(p.cacc + ((size_t)hk * 2 + which) * 128 + j, __uint_as_float(cs1));
         }
       }
     }
@@ -1442,20 +1456,22 @@ int make_maps(BqMaps& m, const BwdArgs& bw, int CP, const void* qp) {
 // du / dvt / dz of one kv head: du = sum of the query tiles' content column sums; dvt = (column sums
 // of dTB) r_time, dz = (column sums of dCB) r_chan (`_rel_bias` adds q_btime / q_bchan to every row, so
 // their gradients are the row sums of dq's temporal / channel parts).
-__global__ void __launch_bounds__(512) tc_dbias_kernel(const float* __restrict__ cs_dq, const float* __restrict__ cacc,
+__global__ void __launch_bounds__(1024) tc_dbias_kernel(const float* __restrict__ cs_dq,
+                                                       const unsigned long long* __restrict__ cacc,
                                                        const __nv_bfloat16* __restrict__ rt,
                                                        const __nv_bfloat16* __restrict__ rc, float* __restrict__ du,
                                                        float* __restrict__ dvt, float* __restrict__ dz, int B, int H,
                                                        int g, int T, int C, int D, int n_qt) {
   __shared__ float s_cs[256];
-  __shared__ float s_part[3][512];
+  __shared__ float s_part[3][1024];
   const int hk = blockIdx.x;
-  if (threadIdx.x < 256) s_cs[threadIdx.x] = cacc[(size_t)hk * 256 + threadIdx.x];
+  if (threadIdx.x < 256) s_cs[threadIdx.x] = fix_read(cacc[(size_t)hk * 256 + threadIdx.x]);
   __syncthreads();
   const int d = threadIdx.x % D, part = threadIdx.x / D, parts = blockDim.x / D;
   float su = 0.f, st = 0.f, sz = 0.f;
   const int n_items = n_qt * B * g;
-  for (int it = part; it < n_items; it += parts) {
+#pragma unroll 8
+  for (int it = part; it < n_items; it += parts) {  // (independent loads: eight in flight per thread)
     const int tq = it / (B * g), b = (it / g) % B, hh = it % g;
     su += cs_dq[((size_t)tq * B * H + (size_t)b * H + hk * g + hh) * D + d];
   }
@@ -1479,25 +1495,27 @@ __global__ void __launch_bounds__(512) tc_dbias_kernel(const float* __restrict__
 
 // dr_time / dr_chan from the accumulators of the query-side kernel:
 //   dr[j, d] = sum_i dX[i, j] (q[i, d] + bias[d]) = R'[j, d] / c2 + colsum[j] (bias[d] - u[d]),   Q' = (q + u) c2.
-__global__ void __launch_bounds__(256) tc_drel_final_kernel(const float* __restrict__ racc, const float* __restrict__ cacc,
+__global__ void __launch_bounds__(256) tc_drel_final_kernel(const unsigned long long* __restrict__ racc,
+                                                            const unsigned long long* __restrict__ cacc,
                                                             const __nv_bfloat16* __restrict__ u,
                                                             const __nv_bfloat16* __restrict__ vt,
                                                             const __nv_bfloat16* __restrict__ z, float* __restrict__ drt,
                                                             float* __restrict__ drc, int T, int C, int D, float inv_c2) {
   const int hk = blockIdx.x, which = blockIdx.y, S = which == 0 ? T : C;
-  const float* acc = racc + ((size_t)hk * 2 + which) * D * 128;
-  const float* cs = cacc + ((size_t)hk * 2 + which) * 128;
+  const unsigned long long* acc = racc + ((size_t)hk * 2 + which) * D * 128;
+  const unsigned long long* cs = cacc + ((size_t)hk * 2 + which) * 128;
   const __nv_bfloat16* bias = (which == 0 ? vt : z) + (size_t)hk * D;
   float* out = (which == 0 ? drt : drc) + (size_t)hk * S * D;
   for (int idx = threadIdx.x; idx < S * D; idx += blockDim.x) {
     const int j = idx / D, d = idx % D;
-    out[idx] = acc[(size_t)d * 128 + j] * inv_c2 +
-               cs[j] * (__bfloat162float(bias[d]) - __bfloat162float(u[(size_t)hk * D + d]));
+    out[idx] = fix_read(acc[(size_t)d * 128 + j]) * inv_c2 +
+               fix_read(cs[j]) * (__bfloat162float(bias[d]) - __bfloat162float(u[(size_t)hk * D + d]));
   }
 }
 
 template <int D, int CP>
-int launch(const BwdArgs& bw, float* cs_dq, int* status, float* relc, float* racc, float* rows_ws, cudaStream_t s) {
+int launch(const BwdArgs& bw, float* cs_dq, int* status, float* relc, unsigned long long* racc, float* rows_ws,
+           cudaStream_t s) {
   const Args& a = bw.a;
   BqMaps maps;
   int rc = make_maps(maps, bw, CP, rows_ws);
@@ -1525,7 +1543,7 @@ int launch(const BwdArgs& bw, float* cs_dq, int* status, float* relc, float* rac
   static_assert(Cfg<D>::EARLY >= 2, "the first tile's K and V load while the prologue runs");
   MVPA_CUDA_CHECK(cudaFuncSetAttribute(tc_bwd_q_kernel<D, CP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   MVPA_CUDA_CHECK(cudaMemsetAsync(status, 0, 256, s));
-  MVPA_CUDA_CHECK(cudaMemsetAsync(racc, 0, sizeof(float) * (size_t)a.Hkv * (2 * D * 128 + 256), s));
+  MVPA_CUDA_CHECK(cudaMemsetAsync(racc, 0, sizeof(unsigned long long) * (size_t)a.Hkv * (2 * D * 128 + 256), s));
   if (!(D == 64 && CP <= 64))  // (the kernel keeps these sums in shared memory otherwise)
     MVPA_CUDA_CHECK(cudaMemsetAsync(bw.dtbg, 0, sizeof(float) * (size_t)a.B * a.H * a.N * a.T, s));
   rel_const_kernel<<<a.Hkv, 256, 0, s>>>((const __nv_bfloat16*)a.vt, (const __nv_bfloat16*)a.z,
@@ -1556,7 +1574,7 @@ size_t tc_bwd_q_workspace_floats(const mvpa_problem* p) {
   // column sums + status + constants + per-row data for the key side (Q' bf16, channel scores fp16
   // padded to 128 slots, offset, temporal scores)
   size_t n = cs_dq_floats(p->B, p->H, p->T, p->D) + 64 + (size_t)p->Hkv * 256 +
-             (size_t)p->Hkv * (2 * p->D * 128 + 256) + rows * (p->D / 2) + rows * cp +
+             2 * (size_t)p->Hkv * (2 * p->D * 128 + 256) + rows * (p->D / 2) + rows * cp +
              ((rows + 3) & ~(size_t)3) + rows * p->T + 64;
   return n;
 }
@@ -1564,9 +1582,10 @@ size_t tc_bwd_q_workspace_floats(const mvpa_problem* p) {
 int tc_bwd_bias(const BwdArgs& bw, float* extra, cudaStream_t s) {
   const Args& a = bw.a;
   const int CP = a.C <= 32 ? 32 : (a.C <= 64 ? 64 : 128), TPB = 128 / CP;
-  const float* racc = extra + cs_dq_floats(a.B, a.H, a.T, a.D) + 64 + (size_t)a.Hkv * 256;
-  const float* cacc = racc + (size_t)a.Hkv * 2 * a.D * 128;
-  tc_dbias_kernel<<<a.Hkv, 512, 0, s>>>(extra, cacc, (const __nv_bfloat16*)a.rt, (const __nv_bfloat16*)a.rc, bw.du,
+  const unsigned long long* racc =
+      reinterpret_cast<const unsigned long long*>(extra + cs_dq_floats(a.B, a.H, a.T, a.D) + 64 + (size_t)a.Hkv * 256);
+  const unsigned long long* cacc = racc + (size_t)a.Hkv * 2 * a.D * 128;
+  tc_dbias_kernel<<<a.Hkv, 1024, 0, s>>>(extra, cacc, (const __nv_bfloat16*)a.rt, (const __nv_bfloat16*)a.rc, bw.du,
                                        bw.dvt, bw.dz, a.B, a.H, a.g, a.T, a.C, a.D, (a.T + TPB - 1) / TPB);
   tc_drel_final_kernel<<<dim3(a.Hkv, 2), 256, 0, s>>>(racc, cacc, (const __nv_bfloat16*)a.u,
                                                      (const __nv_bfloat16*)a.vt, (const __nv_bfloat16*)a.z, bw.drt,
@@ -1581,8 +1600,8 @@ int tc_bwd_q(const BwdArgs& bw, float* extra, cudaStream_t s) {
   float* dqc = extra;  // column sums of dq's content part, one row of D per query-side CTA
   int* status = reinterpret_cast<int*>(extra + cs_dq_floats(a.B, a.H, a.T, a.D));
   float* relc = reinterpret_cast<float*>(status) + 64;
-  float* racc = relc + (size_t)a.Hkv * 256;
-  float* rows_ws = racc + (size_t)a.Hkv * (2 * a.D * 128 + 256);
+  unsigned long long* racc = reinterpret_cast<unsigned long long*>(relc + (size_t)a.Hkv * 256);  // 8-byte aligned
+  float* rows_ws = reinterpret_cast<float*>(racc + (size_t)a.Hkv * (2 * a.D * 128 + 256));
   const int CP = a.C <= 32 ? 32 : (a.C <= 64 ? 64 : 128);
   if (a.D == 64) {
     if (CP == 32) return launch<64, 32>(bw, dqc, status, relc, racc, rows_ws, s);

@@ -189,6 +189,25 @@ def test_backward_tensor_core_vs_fp32_path_full_size(cuda, cfg):
         assert (a - b).abs().max() <= 3e-2 * b.abs().max() + 1e-6, (n, float((a - b).abs().max()), float(b.abs().max()))
 
 
+@pytest.mark.parametrize("cfg", [(1, 16, 16, 128, 32, 64), (2, 4, 2, 64, 128, 128), (1, 4, 2, 40, 100, 64)])
+def test_backward_is_bit_identical_from_run_to_run(cuda, cfg):
+    """All eight gradients of the bf16 tensor-core backward, twice on the same inputs with thousands of CTAs
+    adding into the per-kv-head accumulators in whatever order they finish: identical bits.  (The partial
+    sums are added in 64-bit fixed point, and integer addition is associative.)"""
+    t = make(cuda, 11, *cfg)
+    gout = torch.randn(t["q"].shape, generator=torch.Generator().manual_seed(12)).to(torch.bfloat16).to(cuda)
+    runs = []
+    for _ in range(2):
+        leaves = {n: x.detach().clone().requires_grad_(True) for n, x in t.items()}
+        run(leaves).backward(gout)
+        torch.cuda.synchronize()
+        runs.append({n: x.grad.clone() for n, x in leaves.items()})
+        # different work on the GPU in between, so that the two backward passes do not meet the same timing
+        torch.randn(1 << 22, device=cuda).sort()
+    for n in runs[0]:
+        assert torch.equal(runs[0][n], runs[1][n]), n
+
+
 @pytest.mark.parametrize("gain", [4.0, 40.0])
 def test_forward_with_score_jumps_between_key_tiles(cuda, gain):
     """The temporal keys of the most recent lags are scaled up, so the row maximum jumps from one key
