@@ -469,6 +469,71 @@ def time_long_sample(torch, dist, dev, world, rank, flush, one_gpu_ms):
             "limiter": "the K/V all-gather (2 x 33.5 MB per layer over NVLink): the attention of a rank's shard is shorter"}
 
 
+def hbm_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    except Exception:
+        return 6650.0, "fallback (6.65 TB/s, earlier pool measurement)"
+
+
+def run_blocks(args):
+    """`--workload blocks`: the HBM-bound kernels around the attention (RMSNorm with and without the residual
+    add, SwiGLU gate, wavelet encoder front end, readouts) at the shapes one rank of BASELINE config 5 on 8 GPUs
+    sees (4 samples x 16384 tokens, E 2048, I 5632, segments of 2560 samples).  Per kernel: device time by CUDA
+    events, algorithmic bytes (every input read once, every output written once), GB/s against the measured copy
+    bandwidth.  One JSON line."""
+    import torch
+    import mvpa_native
+    import mvpa_ops
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    lib = mvpa_native.lib()
+    M, E, I, n, K = args.block_tokens, 2048, 5632, 2560, 30
+    bf = torch.bfloat16
+    g = torch.Generator(device=dev).manual_seed(0)
+    r = lambda *sh, dt=bf: torch.randn(*sh, device=dev, dtype=torch.float32, generator=g).to(dt)
+    flush = torch.zeros(64 * 1024 * 1024, dtype=torch.float32, device=dev)
+    x, a, w = r(M, E), r(M, E), r(E)
+    big = r(M, 2 * I)
+    act = torch.empty(M, I, device=dev, dtype=bf)
+    sig = r(M, n, dt=torch.float32)
+    _, total = mvpa_ops.wave_sizes(n)
+    lnw = r(total)
+    B, T, C = max(2, M // 16384), 128, 128
+    pred, enc = r(B, T, C, E), r(B, T, C, E)
+    neg = torch.randint(0, B * T * C, (B, T, C, K), device=dev, dtype=torch.int32, generator=g)
+    h = x.clone()
+    cases = {
+        "rmsnorm_kernel (ln_1 / ln_f)": (lambda: mvpa_ops.rmsnorm(x, w, 1e-5), 2 * M * E * 2),
+        "rmsnorm_kernel (+ residual add)": (lambda: mvpa_ops.rmsnorm(h, w, 1e-5, add=a, sum_out=h), 4 * M * E * 2),
+        "silu_mul_kernel": (lambda: mvpa_ops.silu_mul(big[:, :I], big[:, I:], act), 3 * M * I * 2),
+        "wave_encode_kernel": (lambda: mvpa_ops.wave_encode(sig, lnw, 1e-5, pad_to=2624), M * (n * 4 + 2624 * 2)),
+        "channel_mean_kernel": (lambda: mvpa_ops.channel_mean(pred), B * C * E * 2 + B * E * 2),
+        "contrastive_kernel (K = 30; negatives mostly from the L2)": (
+            lambda: mvpa_ops.contrastive_logits(pred, enc, neg, 0.1), B * (T - 1) * C * ((K + 2) * E * 2 + (K + 1) * 4)),
+    }
+    peak, src = hbm_peak()
+    n0 = lib.mvpa_launch_count()
+    out = {}
+    for name, (fn, nbytes) in cases.items():
+        ms = []
+        for i in range(3 + args.steps):
+            flush.add_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= 3:
+                ms.append(e0.elapsed_time(e1))
+        m = statistics.mean(ms)
+        out[name] = {"ms": m, "algorithmic_bytes": nbytes, "gb_per_s": nbytes / m / 1e6, "frac_of_hbm_peak": nbytes / m / 1e6 / peak}
+    print(json.dumps({"workload": f"blocks: kernels around the attention at config 5's per-rank shapes (M {M} tokens, E 2048, I 5632)",
+                      "bound": "hbm", "peak_gb_per_s": peak, "peak_source": src, "steps": args.steps,
+                      "gpu_launches": int(lib.mvpa_launch_count() - n0), "kernels": out}))
+
+
 def run_triton(args):
     """The reference's own Triton operator (`attentions/attn.py:1317-1366`, unmodified, loaded from
     baseline/_ref/attentions/) on this GPU: first a small shape checked against this library, then the
@@ -549,14 +614,18 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference", "triton"],
                     help="reference: the CPU arm; triton: the reference's Triton operator on this GPU (an extra point)")
-    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS),
-                    help="cfg2 is the benchmark; the others exist for profiling and extra points")
+    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS) + ["blocks"],
+                    help="cfg2 is the benchmark; the others exist for profiling and extra points "
+                         "(blocks: the HBM-bound kernels around the attention)")
     ap.add_argument("--pass", dest="passes", default="fwd", choices=["fwd", "fwd_bwd"],
                     help="fwd is the benchmark; fwd_bwd times forward + backward (training step of the operator)")
+    ap.add_argument("--block-tokens", type=int, default=65536, help="rows of the `blocks` workload (profiling uses fewer)")
     ap.add_argument("--no-extra", action="store_true", help="skip the extra reported points")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.workload == "blocks":
+        return run_blocks(args)
     global WORKLOAD, NAME
     WORKLOAD, NAME = WORKLOADS[args.workload]
     if args.impl == "reference":
