@@ -43,15 +43,24 @@ struct Vec<__nv_bfloat16> {
       f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
     }
   }
-  __device__ static void store(__nv_bfloat16* p, const float (&f)[8]) {
+  __device__ static void unpack(const uint4& r, float (&f)[8]) {
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+  __device__ static uint4 pack(const float (&f)[8]) {
     uint32_t w[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       __nv_bfloat162 v = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
       w[i] = *reinterpret_cast<uint32_t*>(&v);
     }
-    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+    return make_uint4(w[0], w[1], w[2], w[3]);
   }
+  __device__ static void store(__nv_bfloat16* p, const float (&f)[8]) { *reinterpret_cast<uint4*>(p) = pack(f); }
   __device__ static float round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 };
 template <>
@@ -61,6 +70,12 @@ struct Vec<float> {
     const float4 r = *reinterpret_cast<const float4*>(p);
     f[0] = r.x; f[1] = r.y; f[2] = r.z; f[3] = r.w;
   }
+  __device__ static void unpack(const uint4& r, float (&f)[4]) {
+    f[0] = __uint_as_float(r.x); f[1] = __uint_as_float(r.y); f[2] = __uint_as_float(r.z); f[3] = __uint_as_float(r.w);
+  }
+  __device__ static uint4 pack(const float (&f)[4]) {
+    return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+  }
   __device__ static void store(float* p, const float (&f)[4]) {
     *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
   }
@@ -68,7 +83,8 @@ struct Vec<float> {
 };
 
 // y = rmsnorm(h) * w with h = x (+ a), h optionally written out.  One warp per row; the row stays in
-// registers between the sum of squares and the scaling (NV 16-byte vectors per lane).
+// registers, in its storage format (NV 16-byte vectors per lane: half the registers of an fp32 copy for
+// bf16, which doubles the rows in flight per multiprocessor), between the sum of squares and the scaling.
 template <typename T, int NV>
 __global__ void __launch_bounds__(kWarpsPerCta * 32) rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ a,
                                                                     const T* __restrict__ w, T* __restrict__ h_out,
@@ -78,22 +94,46 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) rmsnorm_kernel(const T* __r
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
   const T* xr = x + row * E;
-  float v[NV][N];
-  float ss = 0.f;
+  uint4 raw[NV];
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     const int col = (i * 32 + lane) * N;
-    if (col < E) {
-      Vec<T>::load(xr + col, v[i]);
-      if (a != nullptr) {
-        float b[N];
-        Vec<T>::load(a + row * E + col, b);
+    if (col < E) raw[i] = *reinterpret_cast<const uint4*>(xr + col);
+  }
+  float ss = 0.f;
+  if (a != nullptr) {
+    uint4 rawa[NV];
 #pragma unroll
-        for (int e = 0; e < N; ++e) v[i][e] = Vec<T>::round(v[i][e] + b[e]);  // the sum lives in T, as in eager PyTorch
-        if (h_out != nullptr) Vec<T>::store(h_out + row * E + col, v[i]);
+    for (int i = 0; i < NV; ++i) {
+      const int col = (i * 32 + lane) * N;
+      if (col < E) rawa[i] = *reinterpret_cast<const uint4*>(a + row * E + col);
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int col = (i * 32 + lane) * N;
+      if (col < E) {
+        float v[N], b[N];
+        Vec<T>::unpack(raw[i], v);
+        Vec<T>::unpack(rawa[i], b);
+#pragma unroll
+        for (int e = 0; e < N; ++e) {
+          v[e] = Vec<T>::round(v[e] + b[e]);  // the sum lives in T, as in eager PyTorch
+          ss += v[e] * v[e];
+        }
+        raw[i] = Vec<T>::pack(v);
+        if (h_out != nullptr) *reinterpret_cast<uint4*>(h_out + row * E + col) = raw[i];
       }
+    }
+  } else {
 #pragma unroll
-      for (int e = 0; e < N; ++e) ss += v[i][e] * v[i][e];
+    for (int i = 0; i < NV; ++i) {
+      const int col = (i * 32 + lane) * N;
+      if (col < E) {
+        float v[N];
+        Vec<T>::unpack(raw[i], v);
+#pragma unroll
+        for (int e = 0; e < N; ++e) ss += v[e] * v[e];
+      }
     }
   }
   const float rstd = rsqrtf(warp_sum(ss) / (float)E + eps);
@@ -101,10 +141,11 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) rmsnorm_kernel(const T* __r
   for (int i = 0; i < NV; ++i) {
     const int col = (i * 32 + lane) * N;
     if (col < E) {
-      float g[N];
+      float v[N], g[N];
+      Vec<T>::unpack(raw[i], v);
       Vec<T>::load(w + col, g);
 #pragma unroll
-      for (int e = 0; e < N; ++e) g[e] = v[i][e] * rstd * g[e];
+      for (int e = 0; e < N; ++e) g[e] = v[e] * rstd * g[e];
       Vec<T>::store(y + row * E + col, g);
     }
   }
@@ -144,54 +185,121 @@ struct WaveFilters {
 //   cA[k] = sum_m lo[m] x[(2k + 1 - m) mod n],  cD likewise with hi,  k < (n + 7) / 2
 // (periodic extension of the level's own input, even or odd; n_out = floor((n + 8 - 1) / 2)).
 // Output row: [cA_L, cD_L, cD_{L-1}, ..., cD_1], then RMSNorm over the whole row, times `w`.
+//
+// A level's input sits in shared memory with its periodic extension written out: ten samples of its end in
+// front, eight of its start behind, b[10 + i] = x[i].  Output k reads x[2k-6 .. 2k+1] = b[2k+4 .. 2k+11], so
+// a thread that makes outputs 2t and 2t+1 of both bands needs the ten floats b[4t+4 .. 4t+13]: two 16-byte
+// loads and one 8-byte load, no index arithmetic per tap, consecutive threads on consecutive banks.  The
+// approximation is written straight into the next level's padded layout.
+constexpr int kWaveThreads = 128;
+constexpr int kWaveFront = 10, kWaveBack = 8;
+__host__ __device__ constexpr int wave_buf_floats(int n) { return (n + kWaveFront + kWaveBack + 2 + 3) & ~3; }
+
 template <typename Tin, typename Tout>
-__global__ void __launch_bounds__(256) wave_encode_kernel(const Tin* __restrict__ x, int64_t ld_x, const WaveLevels lv,
-                                                          const WaveFilters flt, const Tout* __restrict__ w,
-                                                          Tout* __restrict__ out, int64_t ld_out, float eps) {
-  extern __shared__ float smem[];
-  float* coef = smem;                        // [total]
-  float* buf0 = coef + ((lv.total + 3) & ~3);  // level input  (at most len[0])
-  float* buf1 = buf0 + ((lv.len[0] + 3) & ~3);  // level output (at most len[1])
-  __shared__ float s_red[8];
+__global__ void __launch_bounds__(kWaveThreads) wave_encode_kernel(const Tin* __restrict__ x, int64_t ld_x,
+                                                                   const WaveLevels lv, const WaveFilters flt,
+                                                                   const Tout* __restrict__ w, Tout* __restrict__ out,
+                                                                   int64_t ld_out, float eps) {
+  extern __shared__ __align__(16) float smem[];
+  float* coef = smem;                                  // [total], padded to 8
+  float* buf0 = coef + ((lv.total + 7) & ~7);          // level input, extended
+  float* buf1 = buf0 + wave_buf_floats(lv.len[0]);     // next level's input, extended
+  __shared__ float s_red[kWaveThreads / 32];
+  const int tid = threadIdx.x;
   const int64_t row = blockIdx.x;
   const Tin* xr = x + row * ld_x;
-  for (int i = threadIdx.x; i < lv.len[0]; i += blockDim.x) buf0[i] = to_f32<Tin>(xr[i]);
+  const int n0 = lv.len[0];
+  if (lv.n_levels == 0) {
+    for (int i = tid; i < n0; i += kWaveThreads) coef[i] = to_f32<Tin>(xr[i]);
+  } else {
+    bool vec = false;
+    if constexpr (sizeof(Tin) == 4) vec = (ld_x % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) && (n0 % 4 == 0);
+    if (vec) {
+      if constexpr (sizeof(Tin) == 4) {
+        const float4* x4 = reinterpret_cast<const float4*>(xr);
+        for (int i = tid; i < n0 / 4; i += kWaveThreads) {
+          const float4 v = x4[i];
+          float2* d = reinterpret_cast<float2*>(buf0 + kWaveFront + 4 * i);  // 8-byte aligned
+          d[0] = make_float2(v.x, v.y);
+          d[1] = make_float2(v.z, v.w);
+        }
+      }
+    } else {
+      for (int i = tid; i < n0; i += kWaveThreads) buf0[kWaveFront + i] = to_f32<Tin>(xr[i]);
+    }
+    if (tid < kWaveFront) buf0[tid] = to_f32<Tin>(xr[n0 - kWaveFront + tid]);
+    else if (tid < kWaveFront + kWaveBack) buf0[kWaveFront + n0 + tid - kWaveFront] = to_f32<Tin>(xr[tid - kWaveFront]);
+  }
   __syncthreads();
   float* src = buf0;
   float* dst = buf1;
   for (int l = 0; l < lv.n_levels; ++l) {
-    const int n = lv.len[l], m = lv.len[l + 1];
+    const int m = lv.len[l + 1];
     const bool last = l == lv.n_levels - 1;
     float* det = coef + lv.out_off[l];
-    float* app = last ? coef : dst;
-    for (int k = threadIdx.x; k < m; k += blockDim.x) {
-      float a = 0.f, d = 0.f;
-      int idx = (2 * k + 1) % n;  // tap m = 0 reads x[2k+1], tap m reads x[2k+1-m]
+    for (int t = tid; 2 * t < m; t += kWaveThreads) {
+      const float4 p0 = *reinterpret_cast<const float4*>(src + 4 * t + 4);
+      const float4 p1 = *reinterpret_cast<const float4*>(src + 4 * t + 8);
+      const float2 p2 = *reinterpret_cast<const float2*>(src + 4 * t + 12);
+      const float v[10] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w, p2.x, p2.y};  // x[4t-6 .. 4t+3]
+      float a0 = 0.f, d0 = 0.f, a1 = 0.f, d1 = 0.f;
 #pragma unroll
-      for (int t = 0; t < 8; ++t) {
-        const float v = src[idx];
-        a = fmaf(flt.lo[t], v, a);
-        d = fmaf(flt.hi[t], v, d);
-        idx = idx == 0 ? n - 1 : idx - 1;
+      for (int tap = 0; tap < 8; ++tap) {
+        a0 = fmaf(flt.lo[tap], v[7 - tap], a0);
+        d0 = fmaf(flt.hi[tap], v[7 - tap], d0);
+        a1 = fmaf(flt.lo[tap], v[9 - tap], a1);
+        d1 = fmaf(flt.hi[tap], v[9 - tap], d1);
       }
-      app[k] = a;
-      det[k] = d;
+      const int k0 = 2 * t, k1 = 2 * t + 1;
+      const bool two = k1 < m;
+      det[k0] = d0;
+      if (two) det[k1] = d1;
+      if (last) {
+        coef[k0] = a0;
+        if (two) coef[k1] = a1;
+      } else {
+        dst[kWaveFront + k0] = a0;
+        if (two) dst[kWaveFront + k1] = a1;
+        // the next level's periodic extension: its last ten samples in front, its first eight behind
+        if (k0 >= m - kWaveFront) dst[k0 - (m - kWaveFront)] = a0;
+        if (two && k1 >= m - kWaveFront) dst[k1 - (m - kWaveFront)] = a1;
+        if (k0 < kWaveBack) dst[kWaveFront + m + k0] = a0;
+        if (two && k1 < kWaveBack) dst[kWaveFront + m + k1] = a1;
+      }
     }
     __syncthreads();
     float* t = src; src = dst; dst = t;
   }
   float ss = 0.f;
-  for (int i = threadIdx.x; i < lv.total; i += blockDim.x) ss += coef[i] * coef[i];
+  for (int i = tid; i < lv.total; i += kWaveThreads) ss += coef[i] * coef[i];
   ss = warp_sum(ss);
-  if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = ss;
+  if ((tid & 31) == 0) s_red[tid >> 5] = ss;
   __syncthreads();
   float tot = 0.f;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) tot += s_red[i];
+  for (int i = 0; i < kWaveThreads / 32; ++i) tot += s_red[i];
   const float rstd = rsqrtf(tot / (float)lv.total + eps);
   Tout* orow = out + row * ld_out;
-  for (int i = threadIdx.x; i < (int)ld_out; i += blockDim.x)
-    orow[i] = i < lv.total ? from_f32<Tout>(coef[i] * rstd * to_f32<Tout>(w[i])) : from_f32<Tout>(0.f);
+  constexpr int N = Vec<Tout>::N;
+  const bool vec_out = (ld_out % N == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0) &&
+                       ((reinterpret_cast<uintptr_t>(w) & 15) == 0);
+  if (vec_out) {
+    for (int i = tid * N; i < (int)ld_out; i += kWaveThreads * N) {
+      float g[N], y[N];
+      if (i + N <= lv.total) {
+        Vec<Tout>::load(w + i, g);
+#pragma unroll
+        for (int e = 0; e < N; ++e) y[e] = coef[i + e] * rstd * g[e];
+      } else {
+#pragma unroll
+        for (int e = 0; e < N; ++e) y[e] = i + e < lv.total ? coef[i + e] * rstd * to_f32<Tout>(w[i + e]) : 0.f;
+      }
+      Vec<Tout>::store(orow + i, y);
+    }
+  } else {
+    for (int i = tid; i < (int)ld_out; i += kWaveThreads)
+      orow[i] = i < lv.total ? from_f32<Tout>(coef[i] * rstd * to_f32<Tout>(w[i])) : from_f32<Tout>(0.f);
+  }
 }
 
 // out[b, :] = mean over channels of h[b, T-1, :, :]   (h is (B, T, C, E), contiguous)
@@ -213,7 +321,7 @@ __global__ void __launch_bounds__(256) channel_mean_kernel(const T* __restrict__
 //   -inf for a negative that equals the positive (|neg - pos| < 1e-8 + 1e-5 |pos|).
 // One warp per target position; p and the positive stay in registers while the negatives stream by.
 template <typename T, int NV>
-__global__ void __launch_bounds__(kWarpsPerCta * 32) contrastive_kernel(const T* __restrict__ pred, const T* __restrict__ enc,
+__global__ void __launch_bounds__(kWarpsPerCta * 32, 2) contrastive_kernel(const T* __restrict__ pred, const T* __restrict__ enc,
                                                                         const int* __restrict__ neg, float* __restrict__ logits,
                                                                         int B, int Tn, int C, int E, int K, float inv_temp) {
   constexpr int N = Vec<T>::N;
@@ -225,49 +333,67 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) contrastive_kernel(const T*
   const int t = (int)((n / C) % (Tn - 1)) + 1;
   const int b = (int)(n / ((int64_t)C * (Tn - 1)));
   const int64_t tok_pos = ((int64_t)b * Tn + t) * C + c, tok_pred = tok_pos - C;
-  float p[NV][N], q[NV][N];
+  // p, the positive and the candidate rows stay in their storage format; the next candidate's row is
+  // requested before the current one is reduced, so its latency hides behind the arithmetic.
+  uint4 pr[NV], qr[NV], cur[NV], nxt[NV];
   float pp = 0.f, qq = 0.f, pq = 0.f;
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     const int col = (i * 32 + lane) * N;
     if (col < E) {
-      Vec<T>::load(pred + tok_pred * E + col, p[i]);
-      Vec<T>::load(enc + tok_pos * E + col, q[i]);
+      pr[i] = *reinterpret_cast<const uint4*>(pred + tok_pred * E + col);
+      qr[i] = *reinterpret_cast<const uint4*>(enc + tok_pos * E + col);
+      float p[N], q[N];
+      Vec<T>::unpack(pr[i], p);
+      Vec<T>::unpack(qr[i], q);
 #pragma unroll
       for (int e = 0; e < N; ++e) {
-        pp += p[i][e] * p[i][e];
-        qq += q[i][e] * q[i][e];
-        pq += p[i][e] * q[i][e];
+        pp += p[e] * p[e];
+        qq += q[e] * q[e];
+        pq += p[e] * q[e];
       }
     }
   }
+  auto fetch = [&](uint4 (&dst)[NV], int j) {
+    const int64_t src = neg[tok_pos * K + j];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int col = (i * 32 + lane) * N;
+      if (col < E) dst[i] = *reinterpret_cast<const uint4*>(enc + src * E + col);
+    }
+  };
+  if (K > 0) fetch(cur, 0);
   pp = warp_sum(pp); qq = warp_sum(qq); pq = warp_sum(pq);
   const float np_ = fmaxf(sqrtf(pp), 1e-8f), nq = sqrtf(qq);
   float* lrow = logits + n * (K + 1);
   if (lane == 0) lrow[0] = pq / (np_ * fmaxf(nq, 1e-8f)) * inv_temp;
   for (int j = 0; j < K; ++j) {
-    const int64_t src = neg[tok_pos * K + j];
-    float rr = 0.f, pr = 0.f, dd = 0.f;
+    if (j + 1 < K) fetch(nxt, j + 1);
+    float rr = 0.f, prd = 0.f, dd = 0.f;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int col = (i * 32 + lane) * N;
       if (col < E) {
-        float r[N];
-        Vec<T>::load(enc + src * E + col, r);
+        float r[N], p[N], q[N];
+        Vec<T>::unpack(cur[i], r);
+        Vec<T>::unpack(pr[i], p);
+        Vec<T>::unpack(qr[i], q);
 #pragma unroll
         for (int e = 0; e < N; ++e) {
           rr += r[e] * r[e];
-          pr += p[i][e] * r[e];
-          const float df = Vec<T>::round(r[e] - q[i][e]);
+          prd += p[e] * r[e];
+          const float df = Vec<T>::round(r[e] - q[e]);
           dd += df * df;
         }
       }
     }
-    rr = warp_sum(rr); pr = warp_sum(pr); dd = warp_sum(dd);
+    rr = warp_sum(rr); prd = warp_sum(prd); dd = warp_sum(dd);
     if (lane == 0) {
       const bool same = sqrtf(dd) < 1e-8f + 1e-5f * nq;
-      lrow[j + 1] = same ? -INFINITY : pr / (np_ * fmaxf(sqrtf(rr), 1e-8f)) * inv_temp;
+      lrow[j + 1] = same ? -INFINITY : prd / (np_ * fmaxf(sqrtf(rr), 1e-8f)) * inv_temp;
     }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) cur[i] = nxt[i];
   }
 }
 
@@ -402,13 +528,14 @@ int mvpa_wave_encode(const void* x, int64_t ld_x, int32_t x_dtype, const float* 
     off -= lv.len[l + 1];
     lv.out_off[l] = off;
   }
-  const size_t smem = sizeof(float) * (((total + 3) & ~3) + ((lv.len[0] + 3) & ~3) + ((lv.len[1] + 3) & ~3));
+  const size_t smem = sizeof(float) * (((total + 7) & ~7) + wave_buf_floats(lv.len[0]) +
+                                       wave_buf_floats(lv.n_levels > 0 ? lv.len[1] : 0));
   cudaStream_t s = (cudaStream_t)cuda_stream;
 #define MVPA_WAVE(TI, TO)                                                                                         \
   do {                                                                                                            \
     MVPA_CUDA_CHECK(cudaFuncSetAttribute(wave_encode_kernel<TI, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                          (int)smem));                                                             \
-    wave_encode_kernel<TI, TO><<<(unsigned)rows, 256, smem, s>>>((const TI*)x, ld_x, lv, flt, (const TO*)weight,   \
+    wave_encode_kernel<TI, TO><<<(unsigned)rows, kWaveThreads, smem, s>>>((const TI*)x, ld_x, lv, flt, (const TO*)weight, \
                                                                  (TO*)out, ld_out, eps);                          \
   } while (0)
   if (x_dtype == MVPA_F32 && out_dtype == MVPA_F32) MVPA_WAVE(float, float);
