@@ -258,8 +258,8 @@ __global__ void __launch_bounds__(kWaveThreads) wave_encode_kernel(const Tin* __
         coef[k0] = a0;
         if (two) coef[k1] = a1;
       } else {
-        dst[kWaveFront + k0] = a0;
-        if (two) dst[kWaveFront + k1] = a1;
+        if (two) *reinterpret_cast<float2*>(dst + kWaveFront + k0) = make_float2(a0, a1);  // 8-byte aligned: one store
+        else dst[kWaveFront + k0] = a0;
         // the next level's periodic extension: its last ten samples in front, its first eight behind
         if (k0 >= m - kWaveFront) dst[k0 - (m - kWaveFront)] = a0;
         if (two && k1 >= m - kWaveFront) dst[k1 - (m - kWaveFront)] = a1;
@@ -289,7 +289,13 @@ __global__ void __launch_bounds__(kWaveThreads) wave_encode_kernel(const Tin* __
       if (i + N <= lv.total) {
         Vec<Tout>::load(w + i, g);
 #pragma unroll
-        for (int e = 0; e < N; ++e) y[e] = coef[i + e] * rstd * g[e];
+        for (int e4 = 0; e4 < N; e4 += 4) {  // 16-byte shared-memory reads (coef is 16-byte aligned, i a multiple of 4)
+          const float4 c = *reinterpret_cast<const float4*>(coef + i + e4);
+          y[e4] = c.x * rstd * g[e4];
+          y[e4 + 1] = c.y * rstd * g[e4 + 1];
+          y[e4 + 2] = c.z * rstd * g[e4 + 2];
+          y[e4 + 3] = c.w * rstd * g[e4 + 3];
+        }
       } else {
 #pragma unroll
         for (int e = 0; e < N; ++e) y[e] = i + e < lv.total ? coef[i + e] * rstd * to_f32<Tout>(w[i + e]) : 0.f;
