@@ -360,6 +360,7 @@ def time_model(torch, dist, dev, name, world, rank, flush, steps=2, warm=1):
         cls = models.HMVPFormer if gen else models.ClassificationHMVPFormer
         task = cls(cfg, models.WaveEncoder(n, E), models.MVPFormerHead(E, None if gen else 2), num_negatives=30)
     task = task.to(dev).to(torch.bfloat16).eval()
+    task.mvpformer.enable_cuda_graph()                       # the block stack replays as one graph launch
     x = synthetic_ieeg(B, T, C, n, seed=1000 * spec["seed"] + rank, device=dev)   # fp32, in HBM
     neg = task._negative_indices((B, T, C), torch.Generator(device=dev).manual_seed(7)) if gen and B > 1 else None
 
@@ -412,7 +413,8 @@ def time_model(torch, dist, dev, name, world, rank, flush, steps=2, warm=1):
     return {"ms": step_ms, "tokens_per_s": B_total * N / (step_ms * 1e-3), "global_batch": B_total, "per_gpu_batch": B,
             "tokens_per_sample": N, "share_of_attention": a["n_layer"] * statistics.mean(att) / statistics.mean(ms),
             "model_tflops_f_alg": spec["tflop_per_sample"] * B_total / (step_ms * 1e-3), "finite": finite,
-            "input": "synthetic 1/f iEEG + 3-8 Hz bursts, fp32, generated on the device", "task": spec["task"]}
+            "input": "synthetic 1/f iEEG + 3-8 Hz bursts, fp32, generated on the device", "task": spec["task"],
+            "cuda_graph": True}
 
 
 def time_long_sample(torch, dist, dev, world, rank, flush, one_gpu_ms):

@@ -162,6 +162,7 @@ class MVPFormerModel(torch.nn.Module):
         self.channel_embedding = torch.nn.Embedding(config.max_channel_embeddings, self.embed_dim)
         self.gradient_checkpointing = gradient_checkpointing
         self._rel = None
+        self._use_graph, self._graphs = False, {}
         std = config.initializer_range                                     # `_init_weights` (`:179-188`)
         for m in self.modules():
             if isinstance(m, (torch.nn.Linear, torch.nn.Embedding)):
@@ -193,20 +194,67 @@ class MVPFormerModel(torch.nn.Module):
             position_ids = torch.arange(T, dtype=torch.long, device=dev).unsqueeze(0)
         if channel_ids is None:
             channel_ids = torch.arange(C, dtype=torch.long, device=dev).unsqueeze(0)
-        position_embeds = self.positional_embedding(position_ids)          # (1,T,E)
-        channel_embeds = self.channel_embedding(channel_ids)               # (1,C,E)
         hidden = self.drop(inputs_embeds)
         if torch.is_grad_enabled() or self.training:
+            position_embeds = self.positional_embedding(position_ids)      # (1,T,E)
+            channel_embeds = self.channel_embedding(channel_ids)           # (1,C,E)
             for block in self.h:
                 hidden = block(hidden, position_embeds, channel_embeds)[0]
             hidden = self.ln_f(hidden)
+        elif self._use_graph:
+            hidden = self._graphed_forward(hidden, position_ids, channel_ids)
         else:
-            hidden = self._fused_forward(hidden, position_embeds, channel_embeds)
+            hidden = self._fused_forward(hidden, position_ids, channel_ids)
         return SimpleNamespace(last_hidden_state=hidden.view(B, T, C, E), past_key_values=None, hidden_states=None,
                                attentions=None, cross_attentions=None)
 
+    def enable_cuda_graph(self, flag: bool = True):
+        """Inference with frozen weights: capture the fused forward of each input shape in a CUDA graph on
+        first use and replay it afterwards (one launch from the host instead of about ten per block, which
+        matters when a rank's share of the batch is small).  The returned tensor is the graph's own output
+        buffer: it is overwritten by the next call with the same shape.  Call again (or `reset_cuda_graphs`)
+        after changing or moving the weights."""
+        self._use_graph = bool(flag)
+        self._graphs = {}
+        return self
+
+    def reset_cuda_graphs(self):
+        self._graphs = {}
+
     @torch.no_grad()
-    def _fused_forward(self, hidden, position_embeds, channel_embeds):
+    def _graphed_forward(self, hidden, position_ids, channel_ids):
+        import attentions.attn as attn_mod
+        key = (tuple(hidden.shape), hidden.dtype, hidden.device.index, tuple(position_ids.shape), tuple(channel_ids.shape))
+        entry = self._graphs.get(key)
+        if entry is None:
+            static_in = hidden.clone()
+            pos, chan = position_ids.clone(), channel_ids.clone()
+            cur = torch.cuda.current_stream(hidden.device)
+            side = torch.cuda.Stream(device=hidden.device)
+            side.wait_stream(cur)
+            check = attn_mod._CHECK_STATUS
+            attn_mod._CHECK_STATUS = False                 # reading the status word back synchronises: not under capture
+            try:
+                with torch.cuda.stream(side):              # warm-up: lazy initialisations, allocator, fused weights
+                    self._fused_forward(static_in, pos, chan)
+                cur.wait_stream(side)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    static_out = self._fused_forward(static_in, pos, chan)
+            finally:
+                attn_mod._CHECK_STATUS = check
+            # the graph reads these buffers on every replay: the index tensors stay alive with it
+            entry = (graph, static_in, static_out, pos, chan)
+            self._graphs[key] = entry
+        graph, static_in, static_out = entry[:3]
+        static_in.copy_(hidden)
+        graph.replay()
+        return static_out
+
+    @torch.no_grad()
+    def _fused_forward(self, hidden, position_ids, channel_ids):
+        position_embeds = self.positional_embedding(position_ids)          # (1,T,E)
+        channel_embeds = self.channel_embedding(channel_ids)               # (1,C,E)
         B, T, C, E = hidden.shape
         L, Hkv, D = len(self.h), self.num_kv_heads, self.head_dim
         w_pos, w_chan = self._rel_weights()

@@ -137,6 +137,27 @@ def test_fused_model_forward_bf16_vs_port(cuda, shape):
     assert (got - ref).abs().max() <= 3e-2 * ref.abs().max(), float((got - ref).abs().max())
 
 
+def test_cuda_graph_replay_equals_eager_launches(cuda):
+    """The fused forward captured in a CUDA graph: same bits as the eager launches, for two different inputs
+    (the second one replays the graph captured for the first), and the caller's tensors are left alone."""
+    E, H, Hkv, I, L, T, C, B = 256, 4, 2, 352, 2, 12, 32, 2
+    torch.manual_seed(8)
+    cfg = models.MVPFormerConfig(n_positions=T, n_channels=C, n_embd=E, n_layer=L, n_head=H, n_inner=I, n_head_kv=Hkv)
+    m = models.MVPFormerModel(cfg).to(torch.bfloat16).to(cuda).eval()
+    xs = [torch.randn(B, T, C, E, device=cuda).to(torch.bfloat16) for _ in range(2)]
+    with torch.no_grad():
+        eager = [m(inputs_embeds=x).last_hidden_state.clone() for x in xs]
+        m.enable_cuda_graph()
+        for x, ref in zip(xs, eager):
+            keep = x.clone()
+            out = m(inputs_embeds=x).last_hidden_state
+            assert torch.equal(out, ref)
+            assert torch.equal(x, keep)
+        assert len(m._graphs) == 1
+        m.enable_cuda_graph(False)
+        assert torch.equal(m(inputs_embeds=xs[0]).last_hidden_state, eager[0])
+
+
 def test_tasks_end_to_end_on_synthetic_ieeg(cuda):
     """Encoder -> model -> heads on synthetic iEEG: classification logits and contrastive next-state logits of
     the task wrappers against the same pipeline assembled from the restatement."""
