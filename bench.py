@@ -163,25 +163,76 @@ def use_all_host_threads(torch):
     return torch.get_num_threads()
 
 
-def cpu_port_time(sample, reps=1, seed=1):
-    """Seconds per pass of the materialised PyTorch attention over `sample` on the host cores."""
+_REF_LAYER = None
+
+
+def reference_layer_class():
+    """The reference's own `MVPFormerGQAAttention` (`layers/mvpa.py`), loaded unmodified from baseline/_ref/
+    where the build staged it, or None when it is not there.  Only its CPU method `_rel_attn` is used; the
+    `loralib` import it makes (for LoRA fine-tuning, off here) is answered with an empty module."""
+    global _REF_LAYER
+    if _REF_LAYER is None:
+        _REF_LAYER = False
+        ref = os.path.join(ROOT, "baseline", "_ref")
+        if os.path.exists(os.path.join(ref, "layers", "mvpa.py")) and os.path.exists(os.path.join(ref, "attentions")):
+            import importlib
+            import types
+            mine = lambda k: k in ("attentions", "layers", "loralib") or k.startswith(("attentions.", "layers."))
+            saved_path, saved_mods = list(sys.path), {k: m for k, m in sys.modules.items() if mine(k)}
+            try:
+                for k in saved_mods:
+                    del sys.modules[k]
+                sys.modules["loralib"] = types.ModuleType("loralib")
+                sys.path.insert(0, ref)
+                _REF_LAYER = importlib.import_module("layers.mvpa").MVPFormerGQAAttention
+            except Exception:
+                _REF_LAYER = False
+            finally:   # this library's own `attentions` / `layers` stay what the rest of the bench imports
+                sys.path[:] = saved_path
+                for k in [k for k in sys.modules if mine(k)]:
+                    del sys.modules[k]
+                sys.modules.update(saved_mods)
+    return _REF_LAYER or None
+
+
+def cpu_attention(sample, seed):
+    """(callable running one pass of the materialised attention over `sample`, kind): the reference's own
+    `_rel_attn` when baseline/_ref/ holds it ("reference"), else its port in oracle/ ("port")."""
     import torch
-    use_all_host_threads(torch)
-    sys.path.insert(0, os.path.join(ROOT, "oracle"))
-    import mvpa_port_torch as port
     B, H, Hkv, T, C, D = (sample[k] for k in ("B", "H", "Hkv", "T", "C", "D"))
     g = torch.Generator().manual_seed(seed)
     N = T * C
     r = lambda *s: torch.randn(*s, generator=g)
-    args = (r(B, H, N, D), r(Hkv, D), r(Hkv, D), r(Hkv, D), r(B, Hkv, N, D), r(Hkv, T, D), r(Hkv, C, D),
-            r(B, Hkv, N, D))
+    q, u, vt, z, k, rt, rc, v = (r(B, H, N, D), r(Hkv, D), r(Hkv, D), r(Hkv, D), r(B, Hkv, N, D), r(Hkv, T, D),
+                                 r(Hkv, C, D), r(B, Hkv, N, D))
+    cls = reference_layer_class()
+    if cls is not None:
+        from types import SimpleNamespace as NS
+        cfg = NS(max_position_embeddings=T, hidden_size=H * D, num_attention_heads=H, n_head_kv=Hkv, n_inner=4 * H * D,
+                 global_att=True, scale_attn_weights=True, scale_attn_by_inverse_layer_idx=False,
+                 reorder_and_upcast_attn=False, lora=False, attn_pdrop=0.0, resid_pdrop=0.0)
+        layer = cls(cfg, layer_idx=0).eval()
+        layer.attn_bias.data = torch.cat([u.flatten(), vt.flatten(), z.flatten()])
+        a = (q.view(B, H, T, C, D), k.view(B, Hkv, T, C, D), rt.view(1, Hkv, T, 1, D), rc.view(1, Hkv, 1, C, D),
+             v.view(B, Hkv, T, C, D))
+        return (lambda: layer._rel_attn(*a)), "reference"
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import mvpa_port_torch as port
+    return (lambda: port.rel_attn(q, u, vt, z, k, rt, rc, v, D ** -0.5, sample["window"])), "port"
+
+
+def cpu_port_time(sample, reps=1, seed=1):
+    """(seconds per pass of the materialised PyTorch attention over `sample` on the host cores, threads, kind)."""
+    import torch
+    use_all_host_threads(torch)
+    fn, kind = cpu_attention(sample, seed)
     ts = []
     with torch.no_grad():
         for _ in range(reps):
             t0 = time.perf_counter()
-            port.rel_attn(*args, D ** -0.5, sample["window"])
+            fn()
             ts.append(time.perf_counter() - t0)
-    return statistics.median(ts), torch.get_num_threads()
+    return statistics.median(ts), torch.get_num_threads(), kind
 
 
 def cpu_config1():
@@ -190,28 +241,25 @@ def cpu_config1():
     3 warm-up passes, 20 timed."""
     import torch
     threads = use_all_host_threads(torch)
-    sys.path.insert(0, os.path.join(ROOT, "oracle"))
-    import mvpa_port_torch as port
     B, H, Hkv, T, C, D = 1, 4, 4, 32, 16, 64
-    g = torch.Generator().manual_seed(0)
-    N = T * C
-    r = lambda *s: torch.randn(*s, generator=g)
-    a = (r(B, H, N, D), r(Hkv, D), r(Hkv, D), r(Hkv, D), r(B, Hkv, N, D), r(Hkv, T, D), r(Hkv, C, D), r(B, Hkv, N, D))
+    fn, kind = cpu_attention(dict(B=B, H=H, Hkv=Hkv, T=T, C=C, D=D, window=10), seed=0)
     ts = []
     with torch.no_grad():
         for i in range(23):
             t0 = time.perf_counter()
-            port.rel_attn(*a, D ** -0.5, 10)
+            fn()
             if i >= 3:
                 ts.append(time.perf_counter() - t0)
     f = flops(B, H, T, C, D)["f_alg"]
     return {"workload": "config 1: fp32, B1 x 4 heads x 512 tokens (16 ch x 32 seg), head_dim 64", "reps": len(ts),
+            "kind": kind,
             "mean_ms": 1e3 * statistics.mean(ts), "median_ms": 1e3 * statistics.median(ts),
             "tflops_f_alg": f / statistics.median(ts) / 1e12, "torch_threads": threads, "cpu_count": os.cpu_count()}
 
 
 def run_reference(args):
-    """Reference arm: the CPU port of the reference attention on the box's host cores."""
+    """Reference arm: the reference's own PyTorch attention (`_rel_attn`, staged under baseline/_ref/ by the
+    build; its port in oracle/ where that is absent) on the box's host cores."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -219,9 +267,9 @@ def run_reference(args):
     for _ in range(min(args.warmup, 2)):
         cpu_port_time(dict(sample, H=1, Hkv=1))
     t0 = time.perf_counter()
-    per, cores = [], 1
+    per, cores, kind = [], 1, "port"
     for _ in range(args.steps):
-        t, cores = cpu_port_time(sample)
+        t, cores, kind = cpu_port_time(sample)
         per.append(t)
     total = sum(per)
     f = flops(**sample)["f_alg"] * args.steps
@@ -232,7 +280,7 @@ def run_reference(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "config": {"workload": NAME, "sample": desc},
-        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": kind, "sample": desc},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "wall_s": time.perf_counter() - t0,
     }))
@@ -809,9 +857,9 @@ def main():
         if not args.no_cpu and world == 1:  # the CPU leg belongs to the single-GPU run
             sample = dict(w, B=1)
             cpu_port_time(dict(sample, H=1, Hkv=1))  # warm-up: thread pool, allocator
-            sec, cores = cpu_port_time(sample, reps=10)  # about 10 s of CPU work
+            sec, cores, kind = cpu_port_time(sample, reps=10)  # about 10 s of CPU work
             out["cpu_baseline"] = {"value": flops(**sample)["f_alg"] / sec / 1e12, "unit": UNIT, "cores": cores,
-                                   "kind": "port", "sample": "1 of the 4 batch elements (16 heads, 4096 tokens), fp32, median of 10 passes",
+                                   "kind": kind, "sample": "1 of the 4 batch elements (16 heads, 4096 tokens), fp32, median of 10 passes",
                                    "seconds": sec}
         print(json.dumps(out))
     if world > 1:

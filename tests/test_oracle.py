@@ -91,3 +91,35 @@ def test_flop_count_matches_baseline_table():
     f = mo.algorithmic_flops(4, 16, 64, 64, 64)
     assert f["p_c"] == 8519680 and f["p_w"] == 2875392
     assert abs(f["f_alg"] / 1e12 - 0.0976) < 1e-3 and abs(f["f_dense"] / 1e12 - 0.1396) < 1e-3
+
+
+def test_staged_reference_layer_agrees_with_the_port():
+    """Where the build has staged the reference's own layer under baseline/_ref/ (the CPU arm of the
+    benchmark then times it instead of the port), both give the same attention output on the same draws."""
+    import importlib.util
+    import os
+    import sys
+
+    import pytest
+    import torch
+    from conftest import ROOT
+    spec = importlib.util.spec_from_file_location("bench_for_test", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    argv, sys.argv = sys.argv, ["bench.py"]
+    try:
+        spec.loader.exec_module(bench)
+    finally:
+        sys.argv = argv
+    if bench.reference_layer_class() is None:
+        pytest.skip("baseline/_ref/ is not staged here")
+    sample = dict(B=1, H=4, Hkv=2, T=13, C=6, D=16, window=10)
+    fn, kind = bench.cpu_attention(sample, seed=3)
+    assert kind == "reference"
+    with torch.no_grad():
+        ref = fn()[0]                                        # (B,H,T,C,D)
+    bench._REF_LAYER = False                                 # the same draws through the port
+    fn2, kind2 = bench.cpu_attention(sample, seed=3)
+    assert kind2 == "port"
+    with torch.no_grad():
+        out = fn2()                                          # (B,H,N,D)
+    assert (ref.reshape(out.shape) - out).abs().max() <= 5e-6
