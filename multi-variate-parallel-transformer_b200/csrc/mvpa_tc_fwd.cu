@@ -246,11 +246,17 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
     }
   } else if (warp == 9) {
     // ------------------------------- MMA issuer -------------------------------
-    if (lane == 0) {
+    // The whole warp runs this stream in convergent code and only the tcgen05 instructions are
+    // guarded by the elected lane: their operands then come straight from warp-uniform registers and
+    // the stream issues at the tensor pipe's rate (a single-lane branch costs 80-160 cycles per MMA).
+    {
+      constexpr uint32_t kFull = 0xffffffffu;
+      const uint32_t el = elect_one();
+      const uint32_t tm = __shfl_sync(kFull, tmem, 0);
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0);
       constexpr uint32_t idesc_c = make_idesc_bf16(128, CP, 0);
       constexpr uint32_t idesc_o = make_idesc_bf16(128, D, 1);
-      bool ok = mbar_wait(&bars[kBarProFull], 0, p.status, 20);
+      bool ok = __all_sync(kFull, mbar_wait(&bars[kBarProFull], 0, p.status, 20));
       if (ok) {
         tc_fence_after();
         const DescHalves dq = make_desc_halves_sw128(smem_u32(sQ), 16, 1024);
@@ -259,19 +265,17 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
 #pragma unroll
         for (int kk = 0; kk < KSTEPS; ++kk) {  // raw temporal products, all 128 columns at once
           const uint32_t off = (kk / 4) * HALF + (kk % 4) * 32;
-          mma_ss_h(tmem + kColTB, dq, off, dr, off, idesc_s, kk > 0);
+          mma_ss_w(el, tm + kColTB, dq, off, dr, off, idesc_s, kk > 0);
         }
 #pragma unroll
         for (int kk = 0; kk < KSTEPS; ++kk) {  // raw channel products -> S0 columns [0, CP)
           const uint32_t offa = (kk / 4) * HALF + (kk % 4) * 32;
           const uint32_t offb = (kk / 4) * (CP * 128) + (kk % 4) * 32;
-          mma_ss_h(tmem + kColS, dq, offa, dc, offb, idesc_c, kk > 0);
+          mma_ss_w(el, tm + kColS, dq, offa, dc, offb, idesc_c, kk > 0);
         }
-        mma_commit(&bars[kBarProMma]);
-        ok = mbar_wait(&bars[kBarProDone], 0, p.status, 21);  // Q rewritten as (q+u) c2; S0 free
+        mma_commit_w(el, smem_u32(&bars[kBarProMma]));
+        ok = __all_sync(kFull, mbar_wait(&bars[kBarProDone], 0, p.status, 21));  // Q rewritten as (q+u) c2; S0 free
       }
-      // From here on the thread keeps running counters instead of recomputing tile -> slot maps:
-      // its instruction stream is latency-bound, and everything that is not an MMA costs tensor time.
       const DescHalves dq = make_desc_halves_sw128(smem_u32(sQ), 16, 1024);
       const DescHalves dk0 = make_desc_halves_sw128(smem_u32(ring), 16, 1024);
       const DescHalves dv0 = make_desc_halves_sw128(smem_u32(ring), HALF, 1024);
@@ -285,10 +289,10 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
         if (sl >= (uint32_t)NS) { sl -= NS; par ^= 1; }
       };
       auto issue_qk = [&](int s) {  // S_s = Q' K_s^T ; K_s sits in slot (2s) % NS
-        ok = mbar_wait_a(a_full + 8 * k_sl, k_par, p.status, 22);
+        ok = __all_sync(kFull, mbar_wait_a(a_full + 8 * k_sl, k_par, p.status, 22));
         if (!ok) return;
         tc_fence_after();
-        const uint32_t d_s = tmem + kColS + 128 * (s & 1);
+        const uint32_t d_s = tm + kColS + 128 * (s & 1);
         const uint32_t klo = dk0.lo + k_sl * (TILE >> 4);
 #pragma unroll
         for (int kk = 0; kk < KSTEPS; ++kk) {
@@ -296,61 +300,53 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
           DescHalves da = dq, db = dk0;
           da.lo = dq.lo + off;
           db.lo = klo + off;
-          mma_ss_h(d_s, da, 0, db, 0, idesc_s, kk > 0);
+          mma_ss_w(el, d_s, da, 0, db, 0, idesc_s, kk > 0);
         }
-        mma_commit_a(a_sfull + 8 * (s & 1));
-        mma_commit_a(a_free + 8 * k_sl);
+        mma_commit_w(el, a_sfull + 8 * (s & 1));
+        mma_commit_w(el, a_free + 8 * k_sl);
         advance(k_sl, k_par, 2);
       };
       if (ok && n_dense > 0) issue_qk(0);
       // The completion of PV_s is signalled on the free-barrier of the V slot it read: the producer
       // waits there to refill the slot, the softmax warps to reuse P columns / rescale O / finish.
-      // Issue blocks once about three MMAs are queued, so the look-ahead for the next tile sits
-      // between the two halves of a tile's MMAs, where queued work hides its latency.
       // (The softmax warps wait for V_s to land before they report P_s, so P-ready implies V-ready
-      // and this thread has a single barrier per tile.)
+      // and this warp has a single barrier per tile.)
       uint32_t v_sl = 1 % NS;  // slot of V_s (V_0 is load 1)
       auto advance_v = [&](int by) {
         v_sl += by;
         if (v_sl >= (uint32_t)NS) v_sl -= NS;
       };
-      bool pre_p = false;  // P of the coming tile already seen complete
       // ---- dense tiles ----
       for (int s = 0; ok && s < n_dense; ++s) {
         if (s + 1 < n_dense) issue_qk(s + 1);  // S of the next tile first: its softmax is the long pole
-        if (ok && !pre_p) ok = mbar_wait_a(a_pfull + 8 * (s & 1), (s >> 1) & 1, p.status, 23);
+        if (ok) ok = __all_sync(kFull, mbar_wait_a(a_pfull + 8 * (s & 1), (s >> 1) & 1, p.status, 23));
         if (!ok) break;
         tc_fence_after();
         // P_s: two 32-column halves at the start of each warpgroup's S columns (stride 64)
-        const uint32_t a0 = tmem + kColS + 128 * (s & 1);
+        const uint32_t a0 = tm + kColS + 128 * (s & 1);
         const uint32_t b_lo = dv0.lo + v_sl * (TILE >> 4);
-        // A blocking wait for P_{s+1} here could deadlock against a rescale that waits for PV_s;
-        // a peek cannot.
         const bool dn = s + 1 < n_dense;
         // alternating path: P_s is one contiguous 64-column block, O of even / odd tiles are separate
-        const uint32_t d_o = ALT ? tmem + kColO + 64 * (s & 1) : tmem + kColO;
+        const uint32_t d_o = ALT ? tm + kColO + 64 * (s & 1) : tm + kColO;
         const uint32_t acc0 = ALT ? (uint32_t)(s > 1) : (uint32_t)(s > 0);
-        pre_p = mma_ts_x4_peek(d_o, a0, b_lo, dv0.hi, 2048 >> 4, idesc_o, acc0,
-                               dn ? a_pfull + 8 * ((s + 1) & 1) : a_plfull, dn ? ((s + 1) >> 1) & 1 : 0);
-        if (s + 1 >= n_tiles) pre_p = false;
-        mma_ts_x4(d_o, a0 + (ALT ? 32 : 64), b_lo + 4 * (2048 >> 4), dv0.hi, 2048 >> 4, idesc_o, 1u);
-        mma_commit_a(a_free + 8 * v_sl);
+        mma_ts_x4_w(el, d_o, a0, b_lo, dv0.hi, 2048 >> 4, idesc_o, acc0);
+        mma_ts_x4_w(el, d_o, a0 + (ALT ? 32 : 64), b_lo + 4 * (2048 >> 4), dv0.hi, 2048 >> 4, idesc_o, 1u);
+        mma_commit_w(el, a_free + 8 * v_sl);
         advance_v(dn ? 2 : 1);  // a dense successor's V is two loads on, a light successor's one
       }
       // ---- light tiles: P in four contiguous 64-column buffers ----
       uint32_t pb = 0, pb_par = 0;
       for (int l = 0; ok && l < n_light; ++l) {
-        if (!pre_p) ok = mbar_wait_a(a_plfull + 8 * pb, pb_par, p.status, 23);
+        ok = __all_sync(kFull, mbar_wait_a(a_plfull + 8 * pb, pb_par, p.status, 23));
         if (!ok) break;
         tc_fence_after();
-        const uint32_t a0 = tmem + kColS + 64 * pb;
+        const uint32_t a0 = tm + kColS + 64 * pb;
         const uint32_t b_lo = dv0.lo + v_sl * (TILE >> 4);
         pb = (pb + 1) & 3;
         if (pb == 0) pb_par ^= 1;
-        pre_p = mma_ts_x4_peek(tmem + kColO, a0, b_lo, dv0.hi, 2048 >> 4, idesc_o, 1u, a_plfull + 8 * pb, pb_par);
-        if (l + 1 >= n_light) pre_p = false;
-        mma_ts_x4(tmem + kColO, a0 + 32, b_lo + 4 * (2048 >> 4), dv0.hi, 2048 >> 4, idesc_o, 1u);
-        mma_commit_a(a_free + 8 * v_sl);
+        mma_ts_x4_w(el, tm + kColO, a0, b_lo, dv0.hi, 2048 >> 4, idesc_o, 1u);
+        mma_ts_x4_w(el, tm + kColO, a0 + 32, b_lo + 4 * (2048 >> 4), dv0.hi, 2048 >> 4, idesc_o, 1u);
+        mma_commit_w(el, a_free + 8 * v_sl);
         advance_v(1);
       }
     }

@@ -385,6 +385,72 @@ __device__ __forceinline__ bool mma_ts_x4_peek(uint32_t d_tmem, uint32_t a_tmem,
   return ready != 0;
 }
 
+// ---------------------- warp-convergent issue (elected lane) ----------------------
+// The tcgen05 instructions take their descriptors and addresses from warp-uniform registers.  Issued
+// from a branch only one lane enters, each MMA costs that lane 80-160 cycles (more when the other warps
+// of the SM are busy); issued by the whole warp in convergent code, with only the instruction itself
+// guarded by the elected lane's predicate, the same stream runs at the tensor pipe's own rate (64 cycles
+// for M128 N128 K16).  These variants take that predicate (`el`, 1 on the elected lane, 0 elsewhere);
+// every lane of the warp must call them together with identical arguments.
+__device__ __forceinline__ uint32_t elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred;
+}
+__device__ __forceinline__ void mma_commit_w(uint32_t el, uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .pred pe;\n\tsetp.ne.b32 pe, %1, 0;\n\t"
+      "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(bar),
+      "r"(el)
+      : "memory");
+}
+__device__ __forceinline__ void mma_ss_w(uint32_t el, uint32_t d_tmem, DescHalves a, uint32_t a_off_bytes,
+                                         DescHalves b, uint32_t b_off_bytes, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, pe;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "setp.ne.b32 pe, %7, 0;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}" ::"r"(d_tmem),
+      "r"(a.lo + (a_off_bytes >> 4)), "r"(a.hi), "r"(b.lo + (b_off_bytes >> 4)), "r"(b.hi), "r"(idesc),
+      "r"(accumulate), "r"(el)
+      : "memory");
+}
+__device__ __forceinline__ void mma_ts_w(uint32_t el, uint32_t d_tmem, uint32_t a_tmem, DescHalves b,
+                                         uint32_t b_off_bytes, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, pe;\n\t.reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "setp.ne.b32 pe, %6, 0;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "r"(b.lo + (b_off_bytes >> 4)), "r"(b.hi), "r"(idesc), "r"(accumulate), "r"(el)
+      : "memory");
+}
+// Four consecutive K-steps of  D[tmem] (+)= A[tmem] * B[smem]  (A: 16 keys = 8 packed columns per
+// step; B: MN-major, `b_step16` 16-byte descriptor units per step from low word `b_lo`).
+__device__ __forceinline__ void mma_ts_x4_w(uint32_t el, uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
+                                            uint32_t b_hi, uint32_t b_step16, uint32_t idesc,
+                                            uint32_t accumulate_first) {
+  asm volatile(
+      "{\n\t.reg .pred p0, p1, pe;\n\t.reg .b64 db;\n\t.reg .b32 lo;\n\t"
+      "setp.ne.b32 p0, %6, 0;\n\t"
+      "setp.ne.b32 pe, %7, 0;\n\t"
+      "setp.eq.b32 p1, 0, 0;\n\t"
+      "mov.b32 lo, %2;\n\t"
+      "mov.b64 db, {lo, %3};\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %5, p0;\n\t"
+      "add.u32 lo, lo, %4;\n\t mov.b64 db, {lo, %3};\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [%1 + 8], db, %5, p1;\n\t"
+      "add.u32 lo, lo, %4;\n\t mov.b64 db, {lo, %3};\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [%1 + 16], db, %5, p1;\n\t"
+      "add.u32 lo, lo, %4;\n\t mov.b64 db, {lo, %3};\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [%1 + 24], db, %5, p1;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(b_step16), "r"(idesc), "r"(accumulate_first), "r"(el)
+      : "memory");
+}
+
 // Instruction descriptor for kind::f16 with bf16 A/B and fp32 accumulation.
 //   [4,6) D fmt = 1 (f32)  [7,10) A fmt = 1 (bf16)  [10,13) B fmt = 1 (bf16)
 //   [15] A major (0 = K)   [16] B major (0 = K, 1 = MN)   [17,23) N >> 3   [24,29) M >> 4
