@@ -309,16 +309,15 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
       if (ok && n_dense > 0) issue_qk(0);
       // The completion of PV_s is signalled on the free-barrier of the V slot it read: the producer
       // waits there to refill the slot, the softmax warps to reuse P columns / rescale O / finish.
-      // (The softmax warps wait for V_s to land before they report P_s, so P-ready implies V-ready
-      // and this warp has a single barrier per tile.)
-      uint32_t v_sl = 1 % NS;  // slot of V_s (V_0 is load 1)
+      uint32_t v_sl = 1 % NS, v_par = 0;  // slot / parity of V_s (V_0 is load 1)
       auto advance_v = [&](int by) {
         v_sl += by;
-        if (v_sl >= (uint32_t)NS) v_sl -= NS;
+        if (v_sl >= (uint32_t)NS) { v_sl -= NS; v_par ^= 1; }
       };
       // ---- dense tiles ----
       for (int s = 0; ok && s < n_dense; ++s) {
         if (s + 1 < n_dense) issue_qk(s + 1);  // S of the next tile first: its softmax is the long pole
+        if (ok) ok = __all_sync(kFull, mbar_wait_a(a_full + 8 * v_sl, v_par, p.status, 24));
         if (ok) ok = __all_sync(kFull, mbar_wait_a(a_pfull + 8 * (s & 1), (s >> 1) & 1, p.status, 23));
         if (!ok) break;
         tc_fence_after();
@@ -337,7 +336,8 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
       // ---- light tiles: P in four contiguous 64-column buffers ----
       uint32_t pb = 0, pb_par = 0;
       for (int l = 0; ok && l < n_light; ++l) {
-        ok = __all_sync(kFull, mbar_wait_a(a_plfull + 8 * pb, pb_par, p.status, 23));
+        ok = __all_sync(kFull, mbar_wait_a(a_full + 8 * v_sl, v_par, p.status, 24));
+        if (ok) ok = __all_sync(kFull, mbar_wait_a(a_plfull + 8 * pb, pb_par, p.status, 23));
         if (!ok) break;
         tc_fence_after();
         const uint32_t a0 = tm + kColS + 64 * pb;
@@ -508,12 +508,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
 #pragma unroll
       for (int tt = 0; tt < TPB; ++tt) tb_all[tt] = p.c2 * (__uint_as_float(raw[tt]) + s_vr[colj[tt]]) + mc;
     };
-    // V_s has landed?  (These warps vouch for it when they report P_s, so the MMA issuer has a
-    // single barrier per tile.)
-    auto wait_v = [&](int s) -> bool {
-      const int qv = q_of_v(s);
-      return warp_wait(&slot_full[qv % NS], (qv / NS) & 1, p.status, 38);
-    };
 
     // ------------------------------ dense tiles ------------------------------
     // Abort protocol: this loop contains a named barrier, which must never lose a participant.
@@ -569,7 +563,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
         tmem_ld_wait();
         tmem_ld32(s_addr, va);  // first chunk of pass 2
         max_chunk(vb, 3);
-        if (!wait_v(s)) { ok = false; break; }  // these warps vouch for V_s when they report P_s
         if (s == wg) {
           m_used = (m_tile == -INFINITY) ? 0.f : m_tile;
         } else {
@@ -685,7 +678,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
         uint32_t v0[32], v1[32];
         tmem_ld32(s_addr, v0);
         tmem_ld32(s_addr + 32, v1);
-        if (!wait_v(s)) ok = false;  // overlaps the TMEM round trips
         tmem_ld_wait();
         tb_finish(tb_raw, tb_col, tb_all);
 #pragma unroll
@@ -764,29 +756,73 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
     // multiplies for the rest.  Four P buffers of 64 TMEM columns (the idle S columns) let these
     // warps run ahead of the PV products.
     if (ok && n_light > 0) {
-      // the buffers overlap S0 / S1: the last dense PV products must be done with them
+      // the buffers overlap S0 / S1: the last dense PV products must be done with them (and with O)
       const int q1 = q_of_v(n_dense - 1);
       ok = warp_wait(&slot_free[q1 % NS], (q1 / NS) & 1, p.status, 37);
       tc_fence_after();
     }
+    // Every light tile's score is its temporal score alone (the channel maximum is folded into bc), and
+    // the temporal scores of the row sit in TMEM: one pass finds the maximum over all light tiles, one
+    // rescale of O covers the whole phase, and the loop below carries no maximum.
+    // Key step tk of the light tiles (0 <= tk < n_light * TPB) is temporal column col0 + tk.
+    const int col0 = T - 1 - ti_abs;
+    if (ok && n_light > 0) {
+      const int col1 = col0 + n_light * TPB;
+      float m_light = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        if (32 * c + 32 <= col0 || 32 * c >= col1) continue;  // (warp-uniform)
+        uint32_t v[32];
+        tmem_ld32(lane_base + kColTB + 32 * c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) {
+          const int col = 32 * c + jj;
+          const float tb = p.c2 * (__uint_as_float(v[jj]) + s_vr[col]) + mc;
+          if (col >= col0 && col < col1) m_light = fmaxf(m_light, tb);
+        }
+      }
+      const bool need = m_light > m_used + kRescaleThreshold;
+      if (__any_sync(0xffffffffu, need)) {
+        const float alpha = need ? ex2(m_used - m_light) : 1.f;
+#pragma unroll
+        for (int c0 = 0; c0 < DW; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld32(lane_base + kColO + wg * DW + c0, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) v[jj] = __float_as_uint(__uint_as_float(v[jj]) * alpha);
+          tmem_st32(lane_base + kColO + wg * DW + c0, v);
+        }
+        tmem_st_wait();
+        l_sum *= alpha;
+        if (need) m_used = m_light;
+      }
+    }
+    // The temporal scores of the next tile are fetched while the current one is written.
+    uint32_t tb_next[TPB];
+    if (ok && n_light > 0) {
+#pragma unroll
+      for (int tt = 0; tt < TPB; ++tt) tmem_ld1(lane_base + kColTB + col0 + tt, tb_next[tt]);
+    }
     for (int l = 0; ok && l < n_light; ++l) {
       const int s = n_dense + l;
-      float tb_all[TPB];
-      bool valid_all[TPB];
-      {
-        uint32_t tb_raw[TPB];
-        int tb_col[TPB];
-        tb_issue(l, tb_raw, tb_col, valid_all);
-        ok = wait_v(s);  // overlaps the TMEM round trip
-        tmem_ld_wait();
-        if (!ok) break;
-        tb_finish(tb_raw, tb_col, tb_all);
-      }
-      float m_tile = -INFINITY;
+      float a_t[TPW];  // exp2(temporal score - m) of this thread's key steps
+      tmem_ld_wait();
 #pragma unroll
-      for (int tt = 0; tt < TPB; ++tt)
-        if (valid_all[tt]) m_tile = fmaxf(m_tile, tb_all[tt]);  // max over channels of (cb - mc) is 0
-      if (!maybe_rescale(s, m_tile)) { ok = false; break; }
+      for (int tl = 0; tl < TPW; ++tl) {
+        const int tt = tt_base + tl;
+        uint32_t raw = 0;
+#pragma unroll
+        for (int q = 0; q < TPB; ++q)
+          if (q == tt) raw = tb_next[q];
+        const float tb = p.c2 * (__uint_as_float(raw) + s_vr[col0 + l * TPB + tt]) + mc;
+        a_t[tl] = ex2(tb - m_used);
+      }
+      if (l + 1 < n_light) {
+#pragma unroll
+        for (int tt = 0; tt < TPB; ++tt) tmem_ld1(lane_base + kColTB + col0 + (l + 1) * TPB + tt, tb_next[tt]);
+      }
       if (l >= 4) {
         // this buffer last held P of light tile l-4: its PV product frees the V slot it read
         const int q = q_of_v(s - 4);
@@ -797,14 +833,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
       uint32_t lo[16], hi[16];
 #pragma unroll
       for (int tl = 0; tl < TPW; ++tl) {
-        const int tt = tt_base + tl;
-        float tsel = 0.f;
-        bool vsel = false;
-#pragma unroll
-        for (int q = 0; q < TPB; ++q)
-          if (q == tt) { tsel = tb_all[q]; vsel = valid_all[q]; }
-        const float a = vsel ? ex2(tsel - m_used) : 0.f;
-        const uint32_t a2 = pack_bf16(a, a);
+        const uint32_t a2 = pack_bf16(a_t[tl], a_t[tl]);
         l_sum += __uint_as_float(a2 << 16) * sum_bc;
 #pragma unroll
         for (int k2 = 0; k2 < NCH / 2; ++k2) {
