@@ -280,7 +280,11 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
     }
   } else if (warp == 9) {
     // ------------------------------- MMA issuer -------------------------------
-    if (lane == 0) {
+    // (the whole warp, in convergent code; the tcgen05 instructions are guarded by the elected lane)
+    {
+      constexpr uint32_t kFull = 0xffffffffu;
+      const uint32_t el = elect_one();
+      const uint32_t tm = __shfl_sync(kFull, tmem, 0);
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0);
       constexpr uint32_t idesc_c = make_idesc_bf16(128, CP, 0);
       constexpr uint32_t idesc_q = make_idesc_bf16(128, D, 1);
@@ -288,7 +292,7 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
       const DescHalves ddo = make_desc_halves_sw128(smem_u32(sDO), 16, 1024);
       const DescHalves dkm0 = make_desc_halves_sw128(smem_u32(ring), 16, 1024);    // K-major view of a slot
       const DescHalves dmn0 = make_desc_halves_sw128(smem_u32(ring), HALF, 1024);  // MN-major view of a slot
-      bool ok = mbar_wait(&bars[kBarProFull], 0, p.status, 120);
+      bool ok = __all_sync(kFull, mbar_wait(&bars[kBarProFull], 0, p.status, 120));
       if (ok) {
         tc_fence_after();
         const DescHalves dr = make_desc_halves_sw128(smem_u32(sR), 16, 1024);
@@ -296,17 +300,17 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
 #pragma unroll
         for (int kk = 0; kk < KSTEPS; ++kk) {
           const uint32_t off = (kk / 4) * HALF + (kk % 4) * 32;
-          mma_ss_h(tmem + kQDQ, dq, off, dr, off, idesc_s, kk > 0);
+          mma_ss_w(el, tm + kQDQ, dq, off, dr, off, idesc_s, kk > 0);
         }
 #pragma unroll
         for (int kk = 0; kk < KSTEPS; ++kk) {
           const uint32_t offa = (kk / 4) * HALF + (kk % 4) * 32;
           const uint32_t offb = (kk / 4) * (CP * 128) + (kk % 4) * 32;
-          mma_ss_h(tmem + kQS, dq, offa, dc, offb, idesc_c, kk > 0);
+          mma_ss_w(el, tm + kQS, dq, offa, dc, offb, idesc_c, kk > 0);
         }
-        mma_commit(&bars[kBarProMma]);
-        ok = mbar_wait(&bars[kBarProDone], 0, p.status, 121);
-        if (ok) {  // Q' (written to sQ and fenced by the softmax warps) goes out for the key-side kernel
+        mma_commit_w(el, smem_u32(&bars[kBarProMma]));
+        ok = __all_sync(kFull, mbar_wait(&bars[kBarProDone], 0, p.status, 121));
+        if (ok && lane == 0) {  // Q' (written to sQ and fenced by the softmax warps) goes out for the key-side kernel
 #pragma unroll
           for (int hh = 0; hh < NH; ++hh) tma_store_5d(&maps.qp, sQ + hh * HALF, hh * 64, 0, I * TPB, h, b);
           tma_store_commit();
@@ -316,7 +320,7 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
       // tile s; once they report dS_s, dP_{s+1} goes first (their second phase waits for it), then dQ += dS_s K_s.
       auto issue_s = [&](int s) {
         const int qk = q_of_k(s), ksl = qk % NS;
-        ok = mbar_wait(&slot_full[ksl], (qk / NS) & 1, p.status, 123);
+        ok = __all_sync(kFull, mbar_wait(&slot_full[ksl], (qk / NS) & 1, p.status, 123));
         if (!ok) return;
         tc_fence_after();
         DescHalves dk = dkm0;
@@ -324,13 +328,13 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
 #pragma unroll
         for (int kk = 0; kk < KSTEPS; ++kk) {  // S = Q' K^T
           const uint32_t off = (kk / 4) * HALF + (kk % 4) * 32;
-          mma_ss_h(tmem + kQS + 128 * (s & 1), dq, off, dk, off, idesc_s, kk > 0);
+          mma_ss_w(el, tm + kQS + 128 * (s & 1), dq, off, dk, off, idesc_s, kk > 0);
         }
-        mma_commit(&bars[kBarSFull + (s & 1)]);
+        mma_commit_w(el, smem_u32(&bars[kBarSFull + (s & 1)]));
       };
       auto issue_dp = [&](int s) {
         const int qv = q_of_v(s), vsl = qv % NS;
-        ok = mbar_wait(&slot_full[vsl], (qv / NS) & 1, p.status, 124);
+        ok = __all_sync(kFull, mbar_wait(&slot_full[vsl], (qv / NS) & 1, p.status, 124));
         if (!ok) return;
         tc_fence_after();
         DescHalves dv = dkm0;
@@ -339,10 +343,10 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
         for (int kk = 0; kk < KSTEPS; ++kk) {  // dP = dO V^T  (V rows = keys, D contiguous: K-major operand)
           const uint32_t off = (kk / 4) * HALF + (kk % 4) * 32;
           // a light tile has no score product: its dP takes the idle S buffer, so two are in flight
-          mma_ss_h(tmem + (is_dense(s) ? kQDP : kQS + 128 * (s & 1)), ddo, off, dv, off, idesc_s, kk > 0);
+          mma_ss_w(el, tm + (is_dense(s) ? kQDP : kQS + 128 * (s & 1)), ddo, off, dv, off, idesc_s, kk > 0);
         }
-        mma_commit(&bars[kBarDpFull + (s & 1)]);
-        mma_commit(&slot_free[vsl]);
+        mma_commit_w(el, smem_u32(&bars[kBarDpFull + (s & 1)]));
+        mma_commit_w(el, smem_u32(&slot_free[vsl]));
       };
       if (ok && is_dense(0)) issue_s(0);
       if (ok) issue_dp(0);
@@ -353,7 +357,7 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
         if (ok && next && !next_dense) issue_dp(s + 1);
         // (two barriers, by tile parity: in the light phase a fast warp may report tile s+1 before a slow
         // one has reported tile s, and arrivals of two tiles must not mix in one phase)
-        if (ok) ok = mbar_wait(&bars[kBarDsFull + (s & 1)], (s >> 1) & 1, p.status, 122);  // dS_w in the S columns, dP read
+        if (ok) ok = __all_sync(kFull, mbar_wait(&bars[kBarDsFull + (s & 1)], (s >> 1) & 1, p.status, 122));  // dS_w in the S columns, dP read
         if (!ok) break;
         tc_fence_after();
         if (next_dense) issue_dp(s + 1);
@@ -361,27 +365,27 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
         if (is_dense(s)) {  // dQ += dS_w K   (A from TMEM, K as MN-major operand)
           const int ksl = q_of_k(s) % NS;
           const uint32_t b_lo = dmn0.lo + (uint32_t)ksl * (TILE >> 4);
-          const uint32_t a0 = tmem + kQS + 128 * (s & 1);
-          mma_ts_x4(tmem + kQDQ, a0, b_lo, dmn0.hi, 2048 >> 4, idesc_q, (uint32_t)(s > n_light));
-          mma_ts_x4(tmem + kQDQ, a0 + 64, b_lo + 4 * (2048 >> 4), dmn0.hi, 2048 >> 4, idesc_q, 1u);
-          mma_commit(&slot_free[ksl]);
+          const uint32_t a0 = tm + kQS + 128 * (s & 1);
+          mma_ts_x4_w(el, tm + kQDQ, a0, b_lo, dmn0.hi, 2048 >> 4, idesc_q, (uint32_t)(s > n_light));
+          mma_ts_x4_w(el, tm + kQDQ, a0 + 64, b_lo + 4 * (2048 >> 4), dmn0.hi, 2048 >> 4, idesc_q, 1u);
+          mma_commit_w(el, smem_u32(&slot_free[ksl]));
         }
       }
-      mma_commit(&bars[kBarAllDone]);
+      mma_commit_w(el, smem_u32(&bars[kBarAllDone]));
       // finish: dQ += dTB r_time + dCB r_chan  (autograd through `_rel_bias`, `attentions/attn.py:1305-1314`);
       // the softmax warps have put dTB / dCB of the tile's rows into TMEM as bf16
-      if (ok) ok = mbar_wait(&bars[kBarFinFull], 0, p.status, 125);
-      if (ok) ok = mbar_wait(&bars[kBarFinLoaded], 0, p.status, 126);
+      if (ok) ok = __all_sync(kFull, mbar_wait(&bars[kBarFinFull], 0, p.status, 125));
+      if (ok) ok = __all_sync(kFull, mbar_wait(&bars[kBarFinLoaded], 0, p.status, 126));
       if (ok) {
         tc_fence_after();
         const DescHalves dfr = make_desc_halves_sw128(smem_u32(ring + 65536), HALF, 1024);
         const DescHalves dfc = make_desc_halves_sw128(smem_u32(ring + 65536 + TILE), CP * 128, 1024);
-        mma_ts_x4(tmem + kQDQ, tmem + kQS, dfr.lo, dfr.hi, 2048 >> 4, idesc_q, 1u);
-        mma_ts_x4(tmem + kQDQ, tmem + kQS + 32, dfr.lo + 4 * (2048 >> 4), dfr.hi, 2048 >> 4, idesc_q, 1u);
+        mma_ts_x4_w(el, tm + kQDQ, tm + kQS, dfr.lo, dfr.hi, 2048 >> 4, idesc_q, 1u);
+        mma_ts_x4_w(el, tm + kQDQ, tm + kQS + 32, dfr.lo + 4 * (2048 >> 4), dfr.hi, 2048 >> 4, idesc_q, 1u);
 #pragma unroll
-        for (int kk = 0; kk < CP / 16; ++kk) mma_ts_h(tmem + kQDQ, tmem + kQDP + kk * 8, dfc, kk * 2048, idesc_q, 1u);
+        for (int kk = 0; kk < CP / 16; ++kk) mma_ts_w(el, tm + kQDQ, tm + kQDP + kk * 8, dfc, kk * 2048, idesc_q, 1u);
       }
-      mma_commit(&bars[kBarFinDone]);
+      mma_commit_w(el, smem_u32(&bars[kBarFinDone]));
       // Relative-key gradients of this tile's rows (autograd through `_rel_bias`, `attentions/attn.py:1305-1314`):
       //   R_t[j, d] = sum_i dTB[i, j] Q'[i, d],  R_c[j, d] = sum_i dCB[i, j] Q'[i, d]   (A = the bf16 tiles the
       //   softmax warps left in shared memory, keys-of-the-sum = query rows; B = Q' as MN-major operand)
@@ -395,18 +399,18 @@ tc_bwd_q_kernel(const __grid_constant__ BqMaps maps, const BqArgs p) {
         const DescHalves dqm = make_desc_halves_sw128(smem_u32(sQ), HALF, 1024);
         const DescHalves dones = make_desc_halves_sw128(smem_u32(ring + 32768), 16, 1024);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) mma_ss_h(tmem + kQS1, dtbt, kk * 2048, dqm, kk * 2048, idesc_r, kk > 0);
+        for (int kk = 0; kk < 8; ++kk) mma_ss_w(el, tm + kQS1, dtbt, kk * 2048, dqm, kk * 2048, idesc_r, kk > 0);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) mma_ss_h(tmem + kQS, dcbt, kk * 2048, dqm, kk * 2048, idesc_r, kk > 0);
+        for (int kk = 0; kk < 8; ++kk) mma_ss_w(el, tm + kQS, dcbt, kk * 2048, dqm, kk * 2048, idesc_r, kk > 0);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t offb = (kk / 4) * 2048 + (kk % 4) * 32;
-          mma_ss_h(tmem + kQDP, dtbt, kk * 2048, dones, offb, idesc_1, kk > 0);
-          mma_ss_h(tmem + kQDP + 16, dcbt, kk * 2048, dones, offb, idesc_1, kk > 0);
+          mma_ss_w(el, tm + kQDP, dtbt, kk * 2048, dones, offb, idesc_1, kk > 0);
+          mma_ss_w(el, tm + kQDP + 16, dcbt, kk * 2048, dones, offb, idesc_1, kk > 0);
         }
       }
-      mma_commit(&bars[kBarRelDone]);
-      tma_store_wait_all();  // the store reads sQ: it has to finish before the CTA can go away
+      mma_commit_w(el, smem_u32(&bars[kBarRelDone]));
+      if (lane == 0) tma_store_wait_all();  // the store reads sQ: it has to finish before the CTA can go away
     }
   }
   } else {
@@ -1095,7 +1099,10 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
       }
     }
   } else if (warp == 9) {
-    if (lane == 0) {  // ---- MMA issuer ----
+    {  // ---- MMA issuer: the whole warp, in convergent code; the tcgen05 instructions are guarded by the elected lane ----
+      constexpr uint32_t kFull = 0xffffffffu;
+      const uint32_t el = elect_one();
+      const uint32_t tm = __shfl_sync(kFull, tmem, 0);
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0);
       constexpr uint32_t idesc_g = make_idesc_bf16_ab(128, D, 1, 1);  // A = P^T / dS^T (MN-major), B MN-major
       const DescHalves dqk = make_desc_halves_sw128(smem_u32(sQ), 16, 1024);
@@ -1106,11 +1113,11 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
       const DescHalves ddom = make_desc_halves_sw128(smem_u32(sDO), HALF, 1024);
       const DescHalves dpm = make_desc_halves_sw128(smem_u32(sP), HALF, 1024);
       const DescHalves ddsm = make_desc_halves_sw128(smem_u32(sDS), HALF, 1024);
-      bool ok = mbar_wait(&bars[kKvFull], 0, p.status, 220);
+      bool ok = __all_sync(kFull, mbar_wait(&bars[kKvFull], 0, p.status, 220));
       const uint32_t set1 = (uint32_t)(C_::SMEM_QDO1 - C_::SMEM_Q) >> 4;  // descriptor distance to the second set
       auto issue_sdp = [&](int s) {  // S = Q' K^T, dP = dO V^T of dense pair s
         const int set = s % NSET;
-        ok = mbar_wait(&bars[kQdoFull + set], (s / NSET) & 1, p.status, 221);
+        ok = __all_sync(kFull, mbar_wait(&bars[kQdoFull + set], (s / NSET) & 1, p.status, 221));
         if (!ok) return;
         tc_fence_after();
         DescHalves a_q = dqk, a_do = ddok;
@@ -1119,19 +1126,19 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
 #pragma unroll
         for (int kk = 0; kk < KSTEPS; ++kk) {
           const uint32_t off = (kk / 4) * HALF + (kk % 4) * 32;
-          mma_ss_h(tmem + kColS, a_q, off, dk, off, idesc_s, kk > 0);
+          mma_ss_w(el, tm + kColS, a_q, off, dk, off, idesc_s, kk > 0);
         }
 #pragma unroll
         for (int kk = 0; kk < KSTEPS; ++kk) {
           const uint32_t off = (kk / 4) * HALF + (kk % 4) * 32;
-          mma_ss_h(tmem + kColDP, a_do, off, dv, off, idesc_s, kk > 0);
+          mma_ss_w(el, tm + kColDP, a_do, off, dv, off, idesc_s, kk > 0);
         }
-        mma_commit(&bars[kBkSdpFull]);
+        mma_commit_w(el, smem_u32(&bars[kBkSdpFull]));
       };
       if (ok && n_dense > 0) issue_sdp(0);
       for (int s = 0; ok && s < n_dense; ++s) {
         const int set = s % NSET;
-        ok = mbar_wait(&bars[kPdsFull], s & 1, p.status, 222);  // P / dS_w are in shared memory, S / dP consumed
+        ok = __all_sync(kFull, mbar_wait(&bars[kPdsFull], s & 1, p.status, 222));  // P / dS_w are in shared memory, S / dP consumed
         if (!ok) break;
         tc_fence_after();
         // with a second buffer set the next pair's S / dP go first: the softmax warps wait for them
@@ -1142,29 +1149,29 @@ tc_bwd_kv_kernel(const __grid_constant__ BkMaps maps, const BkArgs p) {
         b_q.lo += set * set1;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)  // dV += P^T dO   (K = 128 query rows, 16 per step)
-          mma_ss_h(tmem + kColDV, dpm, kk * 2048, b_do, kk * 2048, idesc_g, (s > 0 || kk > 0));
+          mma_ss_w(el, tm + kColDV, dpm, kk * 2048, b_do, kk * 2048, idesc_g, (s > 0 || kk > 0));
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)  // dK += dS_w^T Q'
-          mma_ss_h(tmem + kColDK, ddsm, kk * 2048, b_q, kk * 2048, idesc_g, (s > 0 || kk > 0));
-        mma_commit(&bars[kPairDone]);
+          mma_ss_w(el, tm + kColDK, ddsm, kk * 2048, b_q, kk * 2048, idesc_g, (s > 0 || kk > 0));
+        mma_commit_w(el, smem_u32(&bars[kPairDone]));
         if (NSET == 1 && s + 1 < n_dense) issue_sdp(s + 1);
       }
       const DescHalves dkm = make_desc_halves_sw128(smem_u32(sK), HALF, 1024);  // K / V areas as dO buffers
       const DescHalves dvm = make_desc_halves_sw128(smem_u32(sV), HALF, 1024);
       for (int l = 0; ok && l < n_light; ++l) {  // dV += P^T dO
         const int bsel = l & 1, dsel = l & 3;
-        ok = mbar_wait(&bars[kLdoFull + dsel], (l >> 2) & 1, p.status, 223);
-        if (ok) ok = mbar_wait(&bars[kLpFull + bsel], (l >> 1) & 1, p.status, 224);
+        ok = __all_sync(kFull, mbar_wait(&bars[kLdoFull + dsel], (l >> 2) & 1, p.status, 223));
+        if (ok) ok = __all_sync(kFull, mbar_wait(&bars[kLpFull + bsel], (l >> 1) & 1, p.status, 224));
         if (!ok) break;
         tc_fence_after();
         const DescHalves ap = bsel == 0 ? dpm : ddsm;   // P buffers: the P and the dS areas
         const DescHalves bd = dsel == 0 ? ddom : dsel == 1 ? dqm : dsel == 2 ? dkm : dvm;
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) mma_ss_h(tmem + kColDV, ap, kk * 2048, bd, kk * 2048, idesc_g, 1u);
-        mma_commit(&bars[kLFree + bsel]);
-        mma_commit(&bars[kLdoFree + dsel]);
+        for (int kk = 0; kk < 8; ++kk) mma_ss_w(el, tm + kColDV, ap, kk * 2048, bd, kk * 2048, idesc_g, 1u);
+        mma_commit_w(el, smem_u32(&bars[kLFree + bsel]));
+        mma_commit_w(el, smem_u32(&bars[kLdoFree + dsel]));
       }
-      mma_commit(&bars[kBkAllDone]);
+      mma_commit_w(el, smem_u32(&bars[kBkAllDone]));
     }
   }
   } else {
