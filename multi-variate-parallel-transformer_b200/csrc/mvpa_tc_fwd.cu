@@ -799,42 +799,20 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
         if (need) m_used = m_light;
       }
     }
-    // The temporal scores of the next tile are fetched while the current one is written.
-    uint32_t tb_next[TPB];
-    if (ok && n_light > 0) {
+    // Two tiles per turn: one round trip for the temporal scores and one look at the barriers serve both,
+    // and the second tile's products are formed while the first tile's stores are in flight.  (The scores
+    // of the next pair are fetched meanwhile; with an odd count the last fetch reads the column after the
+    // light tiles, still inside the temporal columns, and drops it.)
+    uint32_t tb_next[2 * TPB];
+    auto tb_fetch = [&](int l) {
 #pragma unroll
-      for (int tt = 0; tt < TPB; ++tt) tmem_ld1(lane_base + kColTB + col0 + tt, tb_next[tt]);
-    }
-    for (int l = 0; ok && l < n_light; ++l) {
-      const int s = n_dense + l;
-      float a_t[TPW];  // exp2(temporal score - m) of this thread's key steps
-      tmem_ld_wait();
-#pragma unroll
-      for (int tl = 0; tl < TPW; ++tl) {
-        const int tt = tt_base + tl;
-        uint32_t raw = 0;
-#pragma unroll
-        for (int q = 0; q < TPB; ++q)
-          if (q == tt) raw = tb_next[q];
-        const float tb = p.c2 * (__uint_as_float(raw) + s_vr[col0 + l * TPB + tt]) + mc;
-        a_t[tl] = ex2(tb - m_used);
-      }
-      if (l + 1 < n_light) {
-#pragma unroll
-        for (int tt = 0; tt < TPB; ++tt) tmem_ld1(lane_base + kColTB + col0 + (l + 1) * TPB + tt, tb_next[tt]);
-      }
-      if (l >= 4) {
-        // this buffer last held P of light tile l-4: its PV product frees the V slot it read
-        const int q = q_of_v(s - 4);
-        ok = warp_wait(&slot_free[q % NS], (q / NS) & 1, p.status, 35);
-        if (!ok) break;
-        tc_fence_after();
-      }
-      uint32_t lo[16], hi[16];
+      for (int j = 0; j < 2 * TPB; ++j) tmem_ld1(lane_base + kColTB + col0 + l * TPB + j, tb_next[j]);
+    };
+    auto p_regs = [&](float (&a_t)[TPW], uint32_t (&lo)[16], uint32_t (&hi)[16], bool count) {
 #pragma unroll
       for (int tl = 0; tl < TPW; ++tl) {
         const uint32_t a2 = pack_bf16(a_t[tl], a_t[tl]);
-        l_sum += __uint_as_float(a2 << 16) * sum_bc;
+        if (count) l_sum += __uint_as_float(a2 << 16) * sum_bc;
 #pragma unroll
         for (int k2 = 0; k2 < NCH / 2; ++k2) {
           const int idx = tl * (NCH / 2) + k2;
@@ -842,12 +820,52 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
           else hi[idx - 16] = hmul2_bf16(a2, bc[k2]);
         }
       }
-      const uint32_t p_addr = lane_base + kColS + 64 * (l & 3) + 32 * wg;
-      tmem_st16(p_addr, lo);
-      tmem_st16(p_addr + 16, hi);
+    };
+    if (ok && n_light > 0) tb_fetch(0);
+    for (int l = 0; ok && l < n_light; l += 2) {
+      const int s = n_dense + l;
+      const bool two = l + 1 < n_light;
+      float a_t[2][TPW];  // exp2(temporal score - m) of this thread's key steps, both tiles
+      tmem_ld_wait();
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+#pragma unroll
+        for (int tl = 0; tl < TPW; ++tl) {
+          const int tt = tt_base + tl;
+          uint32_t raw = 0;
+#pragma unroll
+          for (int q = 0; q < TPB; ++q)
+            if (q == tt) raw = tb_next[u * TPB + q];
+          const float tb = p.c2 * (__uint_as_float(raw) + s_vr[col0 + (l + u) * TPB + tt]) + mc;
+          a_t[u][tl] = ex2(tb - m_used);
+        }
+      }
+      if (l + 2 < n_light) tb_fetch(l + 2);
+      if (l >= 4) {
+        // these buffers last held P of light tiles l-4 and l-3: a PV product frees the V slot it read
+        const int q = q_of_v(s - 4);
+        ok = warp_wait(&slot_free[q % NS], (q / NS) & 1, p.status, 35);
+        if (ok && two) ok = warp_wait(&slot_free[(q + 1) % NS], ((q + 1) / NS) & 1, p.status, 35);
+        if (!ok) break;
+        tc_fence_after();
+      }
+      uint32_t lo0[16], hi0[16], lo1[16], hi1[16];
+      const uint32_t p_addr0 = lane_base + kColS + 64 * (l & 3) + 32 * wg;
+      const uint32_t p_addr1 = lane_base + kColS + 64 * ((l + 1) & 3) + 32 * wg;
+      p_regs(a_t[0], lo0, hi0, true);
+      tmem_st16(p_addr0, lo0);
+      tmem_st16(p_addr0 + 16, hi0);
+      p_regs(a_t[1], lo1, hi1, two);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bars[kBarPlFull + (l & 3)]);
+      if (two) {
+        tmem_st16(p_addr1, lo1);
+        tmem_st16(p_addr1 + 16, hi1);
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(&bars[kBarPlFull + ((l + 1) & 3)]);
+      }
     }
     // ------------------------------- epilogue ---------------------------------
     if (ok) {
