@@ -98,6 +98,29 @@ __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, int* s
 // All 256 softmax threads.  Only ever called outside data-dependent control flow.
 __device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
+// Packed fp32 arithmetic (two lanes per instruction) and the three-input maximum: the dense tiles'
+// softmax is bound by instruction issue next to the exponentials, and these halve its fp32 stream.
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;"
+      : "=l"(reinterpret_cast<uint64_t&>(d))
+      : "l"(reinterpret_cast<const uint64_t&>(a)), "l"(reinterpret_cast<const uint64_t&>(b)),
+        "l"(reinterpret_cast<const uint64_t&>(c)));
+  return d;
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+  float2 d;
+  asm("add.rn.f32x2 %0, %1, %2;"
+      : "=l"(reinterpret_cast<uint64_t&>(d))
+      : "l"(reinterpret_cast<const uint64_t&>(a)), "l"(reinterpret_cast<const uint64_t&>(b)));
+  return d;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 __device__ __forceinline__ uint32_t hmul2_bf16(uint32_t a, uint32_t b) {
   uint32_t d;
   asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
@@ -396,10 +419,10 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
     }
     softmax_bar();  // scratch complete; the MMAs no longer need the raw Q tile
     // Gathered by |c_i - c_k| for this thread's columns:
-    //   cbl = cb - max (fp16x2, log2 domain) for dense tiles,  bc = exp2(cbl) (bf16x2) for light tiles.
-    __half2 cbl[NCH / 2];
-    uint32_t bc[NCH / 2];
-    float mc = 0.f, sum_bc = 0.f;
+    //   cbf = cb - max (fp32, log2 domain) for dense tiles; the light tiles use bc = exp2(cbf) (bf16x2),
+    //   formed when their phase starts (the two never live in registers together).
+    float cbf[NCH];
+    float mc = 0.f;
     {
       float g[NCH];
       float mx = -INFINITY;
@@ -434,19 +457,13 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
         mx = fmaxf(mx, s_max[(wg ^ 1) * 128 + row]);
       }
       mc = (mx == -INFINITY) ? 0.f : mx;
+      if (!ok) {
+#pragma unroll
+        for (int k = 0; k < NCH; ++k) cbf[k] = 0.f;
+      }
       if (ok) {
 #pragma unroll
-        for (int k2 = 0; k2 < NCH / 2; ++k2) cbl[k2] = __floats2half2_rn(g[2 * k2] - mc, g[2 * k2 + 1] - mc);
-        if (n_light > 0) {  // (the exponentials are only used by light tiles)
-#pragma unroll
-          for (int k2 = 0; k2 < NCH / 2; ++k2) {
-            bc[k2] = pack_bf16(ex2(g[2 * k2] - mc), ex2(g[2 * k2 + 1] - mc));
-            sum_bc += __uint_as_float(bc[k2] << 16) + __uint_as_float(bc[k2] & 0xffff0000u);
-          }
-        } else {
-#pragma unroll
-          for (int k2 = 0; k2 < NCH / 2; ++k2) bc[k2] = 0u;
-        }
+        for (int k = 0; k < NCH; ++k) cbf[k] = g[k] - mc;
         // Q' = (q+u) c2 in place (`attentions/attn.py:180-183`); each warpgroup converts half of the chunks
         const float4* u4 = reinterpret_cast<const float4*>(s_bias);
 #pragma unroll
@@ -541,12 +558,15 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
         uint32_t va[32], vb[32];
         auto max_chunk = [&](const uint32_t (&v)[32], int c) {
           const int tt = (32 * c) / CP;
+          const float2 w2 = make_float2(wmul[tt], wmul[tt]);
           float g0 = -INFINITY, g1 = -INFINITY;
 #pragma unroll
-          for (int jj = 0; jj < 32; jj += 2) {
-            const float2 cb = __half22float2(cbl[((32 * c + jj) % CP) / 2]);
-            g0 = fmaxf(g0, fmaf(__uint_as_float(v[jj]), wmul[tt], cb.x));
-            g1 = fmaxf(g1, fmaf(__uint_as_float(v[jj + 1]), wmul[tt], cb.y));
+          for (int jj = 0; jj < 32; jj += 4) {
+            const int k = (32 * c + jj) % CP;
+            const float2 t0 = ffma2(make_float2(__uint_as_float(v[jj]), __uint_as_float(v[jj + 1])), w2, make_float2(cbf[k], cbf[k + 1]));
+            const float2 t1 = ffma2(make_float2(__uint_as_float(v[jj + 2]), __uint_as_float(v[jj + 3])), w2, make_float2(cbf[k + 2], cbf[k + 3]));
+            g0 = fmax3(g0, t0.x, t0.y);
+            g1 = fmax3(g1, t1.x, t1.y);
           }
           if (valid_all[tt]) m_tile = fmaxf(m_tile, fmaxf(g0, g1) + tb_all[tt]);
         };
@@ -588,19 +608,20 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
         }
         // pass 2: P = exp2(S2 - m) as bf16 over the consumed S columns (chunk c lands in columns 16c..16c+15,
         // always behind the columns still to be read)
-        float psum = 0.f, psum1 = 0.f;
+        float2 psum2 = make_float2(0.f, 0.f);
         auto exp_chunk = [&](const uint32_t (&v)[32], int c) {
           const int tt = (32 * c) / CP;
           const float negmu = valid_all[tt] ? tb_all[tt] - m_used : -INFINITY;
+          const float2 w2 = make_float2(wmul[tt], wmul[tt]), n2 = make_float2(negmu, negmu);
           uint32_t pk[16];
 #pragma unroll
           for (int jj = 0; jj < 32; jj += 2) {
-            const float2 cb = __half22float2(cbl[((32 * c + jj) % CP) / 2]);
-            const float p0 = ex2(fmaf(__uint_as_float(v[jj]), wmul[tt], cb.x) + negmu);
-            const float p1 = ex2(fmaf(__uint_as_float(v[jj + 1]), wmul[tt], cb.y) + negmu);
-            psum += p0;
-            psum1 += p1;
-            pk[jj / 2] = pack_bf16(p0, p1);
+            const int k = (32 * c + jj) % CP;
+            float2 t = ffma2(make_float2(__uint_as_float(v[jj]), __uint_as_float(v[jj + 1])), w2, make_float2(cbf[k], cbf[k + 1]));
+            t = fadd2(t, n2);
+            const float2 e = make_float2(ex2(t.x), ex2(t.y));
+            psum2 = fadd2(psum2, e);
+            pk[jj / 2] = pack_bf16(e.x, e.y);
           }
           tmem_st16(s_addr + 16 * c, pk);
         };
@@ -615,8 +636,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
         exp_chunk(va, 2);
         tmem_ld_wait();
         exp_chunk(vb, 3);
-        psum += psum1;
-        l_sum += psum;
+        l_sum += psum2.x + psum2.y;
         tmem_st_wait();
         tc_fence_before();
         mbar_arrive(&bars[kBarPFull + wg]);
@@ -705,11 +725,11 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
         for (int tl = 0; tl < TPW; ++tl) gmax[tl] = -INFINITY;
 #pragma unroll
         for (int lc = 0; lc < 64; lc += 2) {
-          const int tl = lc / CP, k2 = (lc % NCH) / 2;
-          const float2 cb = __half22float2(cbl[k2]);
-          sreg[lc] = fmaf(sreg[lc], wmul[tl], cb.x);
-          sreg[lc + 1] = fmaf(sreg[lc + 1], wmul[tl], cb.y);
-          gmax[tl] = fmaxf(gmax[tl], fmaxf(sreg[lc], sreg[lc + 1]));
+          const int tl = lc / CP, k = lc % NCH;
+          const float2 t = ffma2(make_float2(sreg[lc], sreg[lc + 1]), make_float2(wmul[tl], wmul[tl]), make_float2(cbf[k], cbf[k + 1]));
+          sreg[lc] = t.x;
+          sreg[lc + 1] = t.y;
+          gmax[tl] = fmax3(gmax[tl], t.x, t.y);
         }
 #pragma unroll
         for (int tl = 0; tl < TPW; ++tl)
@@ -731,17 +751,18 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
       float negmu[TPW];
 #pragma unroll
       for (int tl = 0; tl < TPW; ++tl) negmu[tl] = valid[tl] ? tbv[tl] - m_used : -INFINITY;
-      float psum = 0.f;
+      float2 psum2 = make_float2(0.f, 0.f);
       uint32_t lo[16], hi[16];
 #pragma unroll
       for (int lc = 0; lc < 64; lc += 2) {
         const int tl = lc / CP;
-        const float p0 = ex2(sreg[lc] + negmu[tl]), p1 = ex2(sreg[lc + 1] + negmu[tl]);
-        psum += p0 + p1;
-        if (lc < 32) lo[lc / 2] = pack_bf16(p0, p1);
-        else hi[lc / 2 - 16] = pack_bf16(p0, p1);
+        const float2 t = fadd2(make_float2(sreg[lc], sreg[lc + 1]), make_float2(negmu[tl], negmu[tl]));
+        const float2 e = make_float2(ex2(t.x), ex2(t.y));
+        psum2 = fadd2(psum2, e);
+        if (lc < 32) lo[lc / 2] = pack_bf16(e.x, e.y);
+        else hi[lc / 2 - 16] = pack_bf16(e.x, e.y);
       }
-      l_sum += psum;
+      l_sum += psum2.x + psum2.y;
       tmem_st16(s_addr, lo);  // P (bf16) over this thread's own, already consumed S columns
       tmem_st16(s_addr + 16, hi);
       tmem_st_wait();
@@ -766,6 +787,13 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
     // rescale of O covers the whole phase, and the loop below carries no maximum.
     // Key step tk of the light tiles (0 <= tk < n_light * TPB) is temporal column col0 + tk.
     const int col0 = T - 1 - ti_abs;
+    uint32_t bc[NCH / 2];  // exp2(channel score - its maximum), bf16 pairs
+    float sum_bc = 0.f;
+#pragma unroll
+    for (int k2 = 0; k2 < NCH / 2; ++k2) {
+      bc[k2] = pack_bf16(ex2(cbf[2 * k2]), ex2(cbf[2 * k2 + 1]));
+      sum_bc += __uint_as_float(bc[k2] << 16) + __uint_as_float(bc[k2] & 0xffff0000u);
+    }
     if (ok && n_light > 0) {
       const int col1 = col0 + n_light * TPB;
       float m_light = -INFINITY;
