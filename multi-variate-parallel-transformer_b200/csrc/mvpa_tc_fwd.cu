@@ -121,6 +121,29 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   return d;
 }
 
+// 2^x for two lanes on the fp32 pipe instead of the special-function unit, which the dense tiles keep
+// saturated: round x to the nearest integer n with the 1.5 * 2^23 trick, a cubic for 2^(x - n) on
+// [-0.5, 0.5] (relative error 8e-5, well below the bf16 resolution of P), n added into the exponent
+// field.  Arguments below -126 (masked scores are -inf) give 2^-126, which vanishes in every sum.
+__device__ __forceinline__ float2 ex2_poly2(float2 x) {
+  constexpr float kMagic = 12582912.f;
+  x.x = fmaxf(x.x, -126.f);
+  x.y = fmaxf(x.y, -126.f);
+  const float2 y = fadd2(x, make_float2(kMagic, kMagic));
+  const float2 n = fadd2(y, make_float2(-kMagic, -kMagic));
+  const float2 r = ffma2(n, make_float2(-1.f, -1.f), x);
+  float2 q = ffma2(r, make_float2(0.05519810691f, 0.05519810691f), make_float2(0.24267712235f, 0.24267712235f));
+  q = ffma2(q, r, make_float2(0.69326180220f, 0.69326180220f));
+  q = ffma2(q, r, make_float2(0.99992275238f, 0.99992275238f));
+  return make_float2(__int_as_float(__float_as_int(q.x) + (__float_as_int(y.x) << 23)),
+                     __int_as_float(__float_as_int(q.y) + (__float_as_int(y.y) << 23)));
+}
+// Which column pairs of a 32-column chunk take the polynomial (kPolyOf8 of every 8 pairs) on the
+// alternating path, where two warps in their exponentials share one special-function unit: 2 of 8
+// measured best (3 of 8 about equal, 4 of 8 slower than none; no gain where the warpgroups split columns).
+constexpr int kPolyOf8 = 2;
+__device__ __forceinline__ constexpr bool poly_pair(int pair) { return ((pair % 8) * kPolyOf8) % 8 < kPolyOf8; }
+
 __device__ __forceinline__ uint32_t hmul2_bf16(uint32_t a, uint32_t b) {
   uint32_t d;
   asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
@@ -619,7 +642,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
             const int k = (32 * c + jj) % CP;
             float2 t = ffma2(make_float2(__uint_as_float(v[jj]), __uint_as_float(v[jj + 1])), w2, make_float2(cbf[k], cbf[k + 1]));
             t = fadd2(t, n2);
-            const float2 e = make_float2(ex2(t.x), ex2(t.y));
+            const float2 e = poly_pair(jj / 2) ? ex2_poly2(t) : make_float2(ex2(t.x), ex2(t.y));
             psum2 = fadd2(psum2, e);
             pk[jj / 2] = pack_bf16(e.x, e.y);
           }
