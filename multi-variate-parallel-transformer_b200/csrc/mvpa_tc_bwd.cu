@@ -12,7 +12,7 @@
 //
 // Same CTA shape as the forward (mvpa_tc_fwd.cu): 128 query rows of one (b,h); two softmax
 // warpgroups (thread = TMEM lane = query row, 64 key columns each), one TMA producer lane, one MMA
-// issuer lane; dense tiles (inside the content window) first, then light tiles.  Per dense tile
+// issuer warp (convergent code, the tcgen05 instructions guarded by the elected lane); dense tiles (inside the content window) first, then light tiles.  Per dense tile
 // three products: S = Q'K^T, dP = dO V^T, dQ += dS_w K (dS_w as bf16 in TMEM, K as MN-major
 // operand); a light tile needs dP only: its content term is zero-filled, so it contributes to the
 // relative-score gradients but not to dQ's content part, and P is the outer product of the forward.

@@ -9,16 +9,18 @@
 //            (`attentions/attn.py:309-315`) and writes P (bf16) back into TMEM for the PV
 //            product.  O is rescaled only when the running maximum moved by more than 2^8.
 //   warp 8   TMA producer (one lane): Q tile, relative keys, then the K/V ring
-//   warp 9   MMA issuer (one lane): S = Q'K^T and O += P V on tcgen05, plus the two small
-//            products that replace the reference's `_rel_bias` matrices
-//            (`attentions/attn.py:1305-1314`); allocates / frees TMEM
+//   warp 9   MMA issuer: S = Q'K^T and O += P V on tcgen05, plus the two small products that
+//            replace the reference's `_rel_bias` matrices (`attentions/attn.py:1305-1314`);
+//            allocates / frees TMEM.  The whole warp runs the issue loop in convergent code and
+//            the elected lane's predicate guards the tcgen05 instructions themselves.
 //
 // Key tiles are visited dense-first: the tiles that overlap the content window (and the
 // diagonal), then the "light" tiles that lie wholly outside it.  The reference zero-fills the
 // content term there (`attentions/attn.py:261-271`) but still computes it; here a light tile
 // loads no K, issues no QK^T and computes no exponential per pair: its probabilities are the
 // outer product  exp2(tb_i[t_k] - m) x exp2(cb_i[c_k])  of a per-time-step scalar and the row's
-// channel vector, formed with packed bf16 multiplies.
+// channel vector, formed with packed bf16 multiplies, two tiles per turn; one maximum over the
+// temporal scores of all light tiles (and at most one rescale of O) serves the whole phase.
 //
 // TMEM columns: [0,128) S0 / P0, [128,256) S1 / P1, [256,256+D) O, [384,512) raw temporal
 // products TBraw[row][j] = q.r_time[j]  (the bias part vt.r_time[j] is a per-column constant

@@ -94,7 +94,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
   return false;
 }
 
-// Variants on a shared-space address (the MMA-issuing thread keeps barrier addresses as integers
+// Variants on a shared-space address (the MMA-issuing warp keeps barrier addresses as integers
 // so that no generic-to-shared conversion sits in its instruction stream).
 __device__ __forceinline__ bool mbar_test_wait_a(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -132,10 +132,6 @@ __device__ __forceinline__ bool mbar_wait_a(uint32_t bar, uint32_t parity, int* 
   record_giveup(status, code);
   return false;
 }
-__device__ __forceinline__ void mma_commit_a(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
 // --------------------------------- TMA --------------------------------------
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
@@ -203,32 +199,6 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {  
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.
-__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                       uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// D[tmem] (+)= A[tmem] * B[smem]; A is K-major, one row per lane, packed 2 x 16-bit per column.
-__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                       uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
-      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// mbarrier arrives once every MMA issued so far by this thread has completed.
-__device__ __forceinline__ void mma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
-}
 
 // TMEM -> registers: each thread of a warp reads its own lane (row), N consecutive 32-bit columns.
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -310,81 +280,6 @@ __device__ __forceinline__ DescHalves make_desc_halves_sw128(uint32_t smem_addr,
   d.hi = ((sbo_bytes >> 4) & 0x3FFF) | (1u << 14) | (2u << 29);
   return d;
 }
-__device__ __forceinline__ void mma_ss_h(uint32_t d_tmem, DescHalves a, uint32_t a_off_bytes, DescHalves b,
-                                         uint32_t b_off_bytes, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
-      "mov.b64 da, {%1, %2};\n\t"
-      "mov.b64 db, {%3, %4};\n\t"
-      "setp.ne.b32 p, %6, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}" ::"r"(d_tmem),
-      "r"(a.lo + (a_off_bytes >> 4)), "r"(a.hi), "r"(b.lo + (b_off_bytes >> 4)), "r"(b.hi), "r"(idesc),
-      "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void mma_ts_h(uint32_t d_tmem, uint32_t a_tmem, DescHalves b, uint32_t b_off_bytes,
-                                         uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
-      "mov.b64 db, {%2, %3};\n\t"
-      "setp.ne.b32 p, %5, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}" ::"r"(d_tmem),
-      "r"(a_tmem), "r"(b.lo + (b_off_bytes >> 4)), "r"(b.hi), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
-// Four consecutive K-steps of  D[tmem] (+)= A[tmem] * B[smem]  in one instruction block: the
-// issuing thread is latency-bound, so everything but the MMAs themselves is kept out of its way.
-// A: 16 keys = 8 packed bf16x2 columns per step.  B: MN-major, `b_step16` descriptor units
-// (16-byte units) per step, starting at descriptor low word `b_lo`.
-__device__ __forceinline__ void mma_ts_x4(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
-                                          uint32_t b_step16, uint32_t idesc, uint32_t accumulate_first) {
-  asm volatile(
-      "{\n\t.reg .pred p0, p1;\n\t.reg .b64 db;\n\t.reg .b32 lo;\n\t"
-      "setp.ne.b32 p0, %6, 0;\n\t"
-      "setp.eq.b32 p1, 0, 0;\n\t"
-      "mov.b32 lo, %2;\n\t"
-      "mov.b64 db, {lo, %3};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %5, p0;\n\t"
-      "add.u32 lo, lo, %4;\n\t mov.b64 db, {lo, %3};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1 + 8], db, %5, p1;\n\t"
-      "add.u32 lo, lo, %4;\n\t mov.b64 db, {lo, %3};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1 + 16], db, %5, p1;\n\t"
-      "add.u32 lo, lo, %4;\n\t mov.b64 db, {lo, %3};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1 + 24], db, %5, p1;\n\t}" ::"r"(d_tmem),
-      "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(b_step16), "r"(idesc), "r"(accumulate_first)
-      : "memory");
-}
-
-// Same, with a non-blocking peek at an mbarrier phase folded in: the test is issued before the four
-// MMAs and its predicate is only read after them, so its ~150-cycle latency is hidden behind MMA
-// issue instead of stalling the (in-order) issuing thread.  Returns whether the phase had completed.
-__device__ __forceinline__ bool mma_ts_x4_peek(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
-                                               uint32_t b_step16, uint32_t idesc, uint32_t accumulate_first,
-                                               uint32_t peek_bar, uint32_t peek_parity) {
-  uint32_t ready;
-  asm volatile(
-      "{\n\t.reg .pred p0, p1, pr;\n\t.reg .b64 db;\n\t.reg .b32 lo;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 pr, [%8], %9;\n\t"
-      "setp.ne.b32 p0, %7, 0;\n\t"
-      "setp.eq.b32 p1, 0, 0;\n\t"
-      "mov.b32 lo, %3;\n\t"
-      "mov.b64 db, {lo, %4};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%1], [%2], db, %6, p0;\n\t"
-      "add.u32 lo, lo, %5;\n\t mov.b64 db, {lo, %4};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%1], [%2 + 8], db, %6, p1;\n\t"
-      "add.u32 lo, lo, %5;\n\t mov.b64 db, {lo, %4};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%1], [%2 + 16], db, %6, p1;\n\t"
-      "add.u32 lo, lo, %5;\n\t mov.b64 db, {lo, %4};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%1], [%2 + 24], db, %6, p1;\n\t"
-      "selp.u32 %0, 1, 0, pr;\n\t}"
-      : "=r"(ready)
-      : "r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(b_step16), "r"(idesc), "r"(accumulate_first),
-        "r"(peek_bar), "r"(peek_parity)
-      : "memory");
-  return ready != 0;
-}
-
 // ---------------------- warp-convergent issue (elected lane) ----------------------
 // The tcgen05 instructions take their descriptors and addresses from warp-uniform registers.  Issued
 // from a branch only one lane enters, each MMA costs that lane 80-160 cycles (more when the other warps
