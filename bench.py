@@ -488,9 +488,14 @@ def time_long_sample(torch, dist, dev, world, rank, flush, one_gpu_ms):
     def timed(fn, reps=6, warm=2):
         out = []
         for i in range(warm + reps):
-            flush.add_(1)
             dist.barrier()
             torch.cuda.synchronize()
+            # The L2 flush runs right before the timed region, three times: while the GPU is busy with it the
+            # host enqueues the step, so the events see the device time of the step and not the time Python
+            # takes to launch a dozen small operations onto an idle GPU (a model's host thread runs ahead of
+            # the GPU in the same way; the single-GPU time this is compared with is taken behind a flush too).
+            for _ in range(3):
+                flush.add_(1)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             fn()
@@ -506,6 +511,15 @@ def time_long_sample(torch, dist, dev, world, rank, flush, one_gpu_ms):
         total = timed(lambda: ms.time_sharded_attention(attentions.flashmvpa, q_loc, u, vt, z, kv_loc, rt, rc, None, T, C,
                                                         D ** -0.5, 10))
         gather = timed(lambda: ms.gather_kv(kv_loc, plan, T, C, heads=2 * Hkv, **kw))
+        # the same with this library's peer-load gather kernel (CUDA IPC mappings of the ranks' send buffers)
+        # instead of the NCCL collectives
+        try:
+            p2p = {"ms": timed(lambda: ms.time_sharded_attention(attentions.flashmvpa, q_loc, u, vt, z, kv_loc, rt, rc, None,
+                                                                  T, C, D ** -0.5, 10, transport="p2p")),
+                   "gather_ms": timed(lambda: ms.gather_kv(kv_loc, plan, T, C, heads=2 * Hkv, transport="p2p", **kw))}
+            p2p["speedup_vs_1gpu"] = one_gpu_ms / p2p["ms"]
+        except Exception as e:      # e.g. ranks that cannot map one another's memory
+            p2p = {"unavailable": repr(e)[:200]}
         full = ms.gather_kv(kv_loc, plan, T, C, heads=2 * Hkv, **kw)
         kf, vf = full[:, :, :Hkv].permute(0, 2, 1, 3), full[:, :, Hkv:].permute(0, 2, 1, 3)
 
@@ -516,7 +530,8 @@ def time_long_sample(torch, dist, dev, world, rank, flush, one_gpu_ms):
         attn = timed(attn_only)
     return {"ms": total, "tokens_per_s": T * C / (total * 1e-3), "gather_ms": gather, "attention_only_ms": attn,
             "exposed_gather_ms": max(0.0, total - attn), "speedup_vs_1gpu": one_gpu_ms / total, "one_gpu_ms": one_gpu_ms,
-            "gathered_bytes_per_rank": 2 * Hkv * D * 2 * T * C * (world - 1) // world,
+            "gathered_bytes_per_rank": 2 * Hkv * D * 2 * T * C * (world - 1) // world, "transport": "nccl",
+            "peer_load_transport": p2p,
             "limiter": "the K/V all-gather (2 x 33.5 MB per layer over NVLink): the attention of a rank's shard is shorter"}
 
 

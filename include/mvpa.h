@@ -206,6 +206,36 @@ int mvpa_wave_encode(const void* x, int64_t ld_x, int32_t x_dtype, const float* 
                      void* cuda_stream);
 
 /*
+ * Gather of row pieces from other GPUs' memory into this GPU's memory with plain peer loads over
+ * NVLink (no counterpart in the reference, whose only parallelism is data-parallel training,
+ * `configs/*.yaml:3-6`): piece i copies bytes[i] bytes from src[i] (a device pointer that may lie in a
+ * peer's memory, mapped into this process, e.g. through a CUDA IPC handle) to dst[i] (local memory).
+ * src, dst and bytes are HOST arrays of n_pieces <= MVPA_MAX_GATHER_PIECES entries; every pointer and
+ * size must be a multiple of 16 bytes.  One kernel launch, nothing allocated; the caller orders it
+ * against the producers of the pieces (the data must be complete before the launch) and keeps the
+ * sources alive and unchanged until it has finished.  Used by the time-sharded attention of one long
+ * sample to bring every rank's K/V rows into local HBM.
+ */
+#define MVPA_MAX_GATHER_PIECES 32
+int mvpa_peer_gather(void* const* dst, const void* const* src, const int64_t* bytes, int32_t n_pieces,
+                     void* cuda_stream);
+
+/*
+ * Flags between GPUs for `mvpa_peer_gather` (no counterpart in the reference): 32-bit counters in device
+ * memory that a peer has mapped.  `mvpa_peer_signal` stores `value` into each of the n remote slots after
+ * a system-wide fence, so everything enqueued earlier on the stream is visible to a peer that has seen the
+ * flag.  `mvpa_peer_wait` returns (on the stream) once each of the n local slots has reached `value`
+ * (compared as a wrapping counter); the wait is bounded: after `limit_us` microseconds (0 = two seconds)
+ * the kernel stores 1 to *status (device memory, may be NULL) and returns, so a missing peer surfaces as a
+ * status the host reads later, not as a hung GPU.  Both take HOST arrays of at most
+ * MVPA_MAX_GATHER_PIECES device pointers.  The waiting and the signalling kernels must run on different
+ * GPUs (one rank per GPU).
+ */
+int mvpa_peer_signal(uint32_t* const* remote_slots, int32_t n, uint32_t value, void* cuda_stream);
+int mvpa_peer_wait(const uint32_t* const* local_slots, int32_t n, uint32_t value, uint32_t limit_us,
+                   int32_t* status, void* cuda_stream);
+
+/*
  * Classification readout: out[b] = mean over channels of h[b, T-1] for h (B,T,C,E)
  * (`models/mvpformer.py:951-953`: `out[:, -1].mean(dim=1)`).
  */

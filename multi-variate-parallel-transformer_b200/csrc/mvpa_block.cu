@@ -554,6 +554,146 @@ int mvpa_wave_encode(const void* x, int64_t ld_x, int32_t x_dtype, const float* 
   return MVPA_OK;
 }
 
+// ---- gather of row pieces from peers' memory (plain loads over NVLink) ----
+struct GatherPieces {
+  const uint4* src[MVPA_MAX_GATHER_PIECES];
+  uint4* dst[MVPA_MAX_GATHER_PIECES];
+  int64_t n16[MVPA_MAX_GATHER_PIECES];  // 16-byte words per piece
+  int n;
+};
+// The pieces are cut into 64 KB chunks and the chunks dealt round-robin over the pieces, so at any time
+// the CTAs read from every source at once: each source GPU then serves its readers at an even share of its
+// link bandwidth (all ranks walking the pieces in the same order would all pull from one source at a time).
+// Four independent 16-byte loads per thread and turn keep enough bytes in flight for the link latency.
+constexpr int kGatherChunk16 = 4096;  // 16-byte words per chunk
+static __global__ void __launch_bounds__(512) peer_gather_kernel(const __grid_constant__ GatherPieces g, int64_t max_chunks) {
+  const int64_t n_slots = max_chunks * g.n;  // chunk c of piece p is slot c * n + p
+  for (int64_t slot = blockIdx.x; slot < n_slots; slot += gridDim.x) {
+    const int pc = (int)(slot % g.n);
+    const int64_t base = (slot / g.n) * kGatherChunk16;
+    const int64_t n = g.n16[pc] - base < kGatherChunk16 ? g.n16[pc] - base : kGatherChunk16;
+    if (n <= 0) continue;
+    const uint4* __restrict__ src = g.src[pc] + base;
+    uint4* __restrict__ dst = g.dst[pc] + base;
+    int i = threadIdx.x;
+    for (; i + 3 * 512 < n; i += 4 * 512) {
+      const uint4 a = __ldcg(src + i), b = __ldcg(src + i + 512), c = __ldcg(src + i + 1024), d = __ldcg(src + i + 1536);
+      dst[i] = a;
+      dst[i + 512] = b;
+      dst[i + 1024] = c;
+      dst[i + 1536] = d;
+    }
+    for (; i < n; i += 512) dst[i] = __ldcg(src + i);
+  }
+}
+
+int mvpa_peer_gather(void* const* dst, const void* const* src, const int64_t* bytes, int32_t n_pieces,
+                     void* cuda_stream) {
+  if (n_pieces < 0 || n_pieces > MVPA_MAX_GATHER_PIECES || (n_pieces > 0 && (!dst || !src || !bytes))) {
+    set_error("mvpa_peer_gather: between 0 and %d pieces, arrays not NULL", MVPA_MAX_GATHER_PIECES);
+    return MVPA_ERR_SHAPE;
+  }
+  GatherPieces g;
+  g.n = 0;
+  for (int i = 0; i < n_pieces; ++i) {
+    if (bytes[i] == 0) continue;
+    if (bytes[i] < 0 || bytes[i] % 16 != 0 || ((uintptr_t)dst[i] & 15) != 0 || ((uintptr_t)src[i] & 15) != 0 ||
+        !dst[i] || !src[i]) {
+      set_error("mvpa_peer_gather: piece %d: pointers and size must be non-NULL multiples of 16 bytes", i);
+      return MVPA_ERR_ALIGNMENT;
+    }
+    g.src[g.n] = (const uint4*)src[i];
+    g.dst[g.n] = (uint4*)dst[i];
+    g.n16[g.n] = bytes[i] / 16;
+    ++g.n;
+  }
+  if (g.n == 0) return MVPA_OK;
+  int64_t max_chunks = 0;
+  for (int i = 0; i < g.n; ++i) {
+    const int64_t c = (g.n16[i] + kGatherChunk16 - 1) / kGatherChunk16;
+    max_chunks = c > max_chunks ? c : max_chunks;
+  }
+  // whole waves of CTAs (two per SM), fewer for small transfers
+  const int64_t want = max_chunks * g.n, cap = 2 * (int64_t)device_sm_count();
+  const unsigned grid = (unsigned)(want > cap ? cap : want);
+  peer_gather_kernel<<<grid, 512, 0, (cudaStream_t)cuda_stream>>>(g, max_chunks);
+  count_launch();
+  MVPA_CUDA_CHECK(cudaGetLastError());
+  return MVPA_OK;
+}
+
+// ---- flags between GPUs ----
+struct FlagSlots {
+  uint32_t* slot[MVPA_MAX_GATHER_PIECES];
+  int n;
+};
+static __global__ void peer_signal_kernel(const __grid_constant__ FlagSlots f, uint32_t value) {
+  const int i = threadIdx.x;
+  if (i < f.n) {
+    __threadfence_system();  // what this stream wrote before is visible before the flag is
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f.slot[i]), "r"(value) : "memory");
+  }
+}
+static __global__ void peer_wait_kernel(const __grid_constant__ FlagSlots f, uint32_t value, uint64_t limit_ns,
+                                        int* status) {
+  const int i = threadIdx.x;
+  if (i < f.n) {
+    uint64_t t0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (;;) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f.slot[i]) : "memory");
+      if ((int32_t)(v - value) >= 0) break;
+      uint64_t t;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+      if (t - t0 > limit_ns) {  // give up: report and return, the context stays usable
+        if (status != nullptr) *status = 1;
+        break;
+      }
+      __nanosleep(200);
+    }
+  }
+  __threadfence_system();
+}
+
+static int flag_slots(FlagSlots& f, const void* const* slots, int32_t n, const char* what) {
+  if (n < 0 || n > MVPA_MAX_GATHER_PIECES || (n > 0 && !slots)) {
+    set_error("%s: between 0 and %d slots, array not NULL", what, MVPA_MAX_GATHER_PIECES);
+    return MVPA_ERR_SHAPE;
+  }
+  f.n = n;
+  for (int i = 0; i < n; ++i) {
+    if (!slots[i] || ((uintptr_t)slots[i] & 3) != 0) {
+      set_error("%s: slot %d is NULL or not 4-byte aligned", what, i);
+      return MVPA_ERR_ALIGNMENT;
+    }
+    f.slot[i] = (uint32_t*)slots[i];
+  }
+  return MVPA_OK;
+}
+
+int mvpa_peer_signal(uint32_t* const* remote_slots, int32_t n, uint32_t value, void* cuda_stream) {
+  FlagSlots f;
+  const int rc = flag_slots(f, (const void* const*)remote_slots, n, "mvpa_peer_signal");
+  if (rc != MVPA_OK || n == 0) return rc;
+  peer_signal_kernel<<<1, MVPA_MAX_GATHER_PIECES, 0, (cudaStream_t)cuda_stream>>>(f, value);
+  count_launch();
+  MVPA_CUDA_CHECK(cudaGetLastError());
+  return MVPA_OK;
+}
+
+int mvpa_peer_wait(const uint32_t* const* local_slots, int32_t n, uint32_t value, uint32_t limit_us, int32_t* status,
+                   void* cuda_stream) {
+  FlagSlots f;
+  const int rc = flag_slots(f, (const void* const*)local_slots, n, "mvpa_peer_wait");
+  if (rc != MVPA_OK || n == 0) return rc;
+  const uint64_t limit_ns = limit_us != 0 ? (uint64_t)limit_us * 1000ull : 2000000000ull;
+  peer_wait_kernel<<<1, MVPA_MAX_GATHER_PIECES, 0, (cudaStream_t)cuda_stream>>>(f, value, limit_ns, status);
+  count_launch();
+  MVPA_CUDA_CHECK(cudaGetLastError());
+  return MVPA_OK;
+}
+
 int mvpa_channel_mean(const void* h, void* out, int32_t B, int32_t T, int32_t C, int32_t E, int32_t dtype,
                       void* cuda_stream) {
   if (B <= 0 || T <= 0 || C <= 0 || E <= 0 || h == nullptr || out == nullptr) {

@@ -92,7 +92,8 @@ EXPORTS = ("mvpa_fwd", "mvpa_bwd", "mvpa_fwd_workspace_bytes", "mvpa_bwd_workspa
            "mvpa_last_error_string", "mvpa_launch_count", "mvpa_abi_version",
            "mvpa_workspace_status", "mvpa_fwd_noalloc", "mvpa_bwd_status", "mvpa_noalloc_status",
            "mvpa_selftest_wait_timeout", "mvpa_rmsnorm", "mvpa_silu_mul", "mvpa_wave_encode_size",
-           "mvpa_wave_encode", "mvpa_channel_mean", "mvpa_contrastive_logits")
+           "mvpa_wave_encode", "mvpa_channel_mean", "mvpa_contrastive_logits", "mvpa_peer_gather", "mvpa_peer_signal",
+           "mvpa_peer_wait")
 ABI_VERSION = 3   # mvpa_abi_version() of the header this shim was written against
 
 
@@ -142,6 +143,12 @@ def lib() -> ctypes.CDLL:
         L.mvpa_wave_encode.restype = ctypes.c_int
         L.mvpa_wave_encode.argtypes = [vp, i64, i32, ctypes.POINTER(f32), ctypes.POINTER(f32), vp, vp, i64, i32, i64,
                                        i32, f32, vp]
+        L.mvpa_peer_signal.restype = ctypes.c_int
+        L.mvpa_peer_signal.argtypes = [vp, i32, ctypes.c_uint32, vp]
+        L.mvpa_peer_wait.restype = ctypes.c_int
+        L.mvpa_peer_wait.argtypes = [vp, i32, ctypes.c_uint32, ctypes.c_uint32, vp, vp]
+        L.mvpa_peer_gather.restype = ctypes.c_int
+        L.mvpa_peer_gather.argtypes = [vp, vp, vp, i32, vp]
         L.mvpa_channel_mean.restype = ctypes.c_int
         L.mvpa_channel_mean.argtypes = [vp, vp, i32, i32, i32, i32, i32, vp]
         L.mvpa_contrastive_logits.restype = ctypes.c_int

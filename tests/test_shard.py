@@ -143,12 +143,17 @@ def _gpu_worker(rank, world, port, out_dir):
         u, vt, z, rt, rc = r(1, Hkv, 1, D), r(1, Hkv, 1, D), r(1, Hkv, 1, D), r(1, Hkv, T, D), r(1, Hkv, C, D)
         plan = ms.zigzag_chunks(T, C, world)
         cut = lambda x: [x[:, t0 * C:(t0 + n) * C].contiguous() if n else None for t0, n in plan[rank]]
-        outs = ms.time_sharded_attention(attentions.flashmvpa, cut(q), u, vt, z, cut(k), rt, rc, cut(v), T, C,
-                                         D ** -0.5, 10)
         full = attentions.flashmvpa(q.permute(0, 2, 1, 3), u, vt, z, k.permute(0, 2, 1, 3), rt, rc,
                                     v.permute(0, 2, 1, 3), causal=True, sm_scale=D ** -0.5,
                                     window_size=10).permute(0, 2, 1, 3)
-        same = all(torch.equal(o, full[:, t0 * C:(t0 + n) * C]) for (t0, n), o in zip(plan[rank], outs) if n)
+        same = True
+        kv = torch.cat([k, v], dim=2)
+        # both transports; the peer-load one twice in a row (its send buffers are reused: the second call must
+        # wait until every rank has read the first call's rows), with separate and with fused K/V
+        for transport, fused in (("nccl", False), ("p2p", False), ("p2p", False), ("p2p", True), ("p2p", True)):
+            outs = ms.time_sharded_attention(attentions.flashmvpa, cut(q), u, vt, z, cut(kv if fused else k), rt, rc,
+                                             None if fused else cut(v), T, C, D ** -0.5, 10, transport=transport)
+            same = same and all(torch.equal(o, full[:, t0 * C:(t0 + n) * C]) for (t0, n), o in zip(plan[rank], outs) if n)
         torch.cuda.synchronize()
         np.save(os.path.join(out_dir, f"same{rank}.npy"), np.array([int(same)]))
     finally:
@@ -157,8 +162,9 @@ def _gpu_worker(rank, world, port, out_dir):
 
 @pytest.mark.gpu
 def test_time_sharding_two_gpus_nccl_bit_equal_to_single_gpu(tmp_path):
-    """K/V all-gather over NCCL + per-rank query ranges: every rank's rows are bit-identical to the
-    single-GPU result (the kernels are deterministic and see the same K/V bytes)."""
+    """K/V all-gather (NCCL collectives, and this library's peer-load gather kernel over CUDA IPC mappings) +
+    per-rank query ranges: every rank's rows are bit-identical to the single-GPU result (the kernels are
+    deterministic and see the same K/V bytes)."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     port = 29500 + (os.getpid() % 2000) + 7
