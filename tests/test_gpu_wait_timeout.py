@@ -3,7 +3,8 @@
 `mvpa_selftest_wait_timeout` launches one warp that waits, with a one-millisecond deadline on the
 GPU's nanosecond timer, on an mbarrier nothing arrives at.  The kernel must come back, the status
 word must carry its code, `mvpa_workspace_status` must report MVPA_ERR_DEVICE, and the context
-must stay usable (a regular forward afterwards works)."""
+must stay usable (a regular forward afterwards works).  The same for the flags between GPUs of
+the peer-load transport (`mvpa_peer_wait`): a slot nothing writes makes the wait run out."""
 import ctypes
 import time
 
@@ -41,3 +42,36 @@ def test_selftest_argument_checks(cuda):
     ws = torch.zeros(256, dtype=torch.uint8, device=cuda)
     assert lib.mvpa_selftest_wait_timeout(ws.data_ptr(), 16, 1000, None) == -4
     assert lib.mvpa_selftest_wait_timeout(ws.data_ptr(), 256, 0, None) == -1
+
+
+def test_peer_flags_signal_wait_and_timeout(cuda):
+    """The flags of the peer-load transport on one GPU: a signal makes a later wait pass; a wait on a slot
+    nothing writes gives up after its deadline, sets the status word and leaves the context usable; the
+    gather kernel copies its pieces bit for bit."""
+    lib = nat.lib()
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    flags = torch.zeros(64, dtype=torch.int32, device=cuda)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda)
+    slot = lambda i: flags.data_ptr() + 4 * i
+    two = (ctypes.c_void_p * 2)(slot(0), slot(1))
+    nat.check(lib.mvpa_peer_signal(two, 2, 7, stream), "signal")
+    nat.check(lib.mvpa_peer_wait(two, 2, 7, 2000, ctypes.c_void_p(status.data_ptr()), stream), "wait")
+    nat.check(lib.mvpa_peer_wait(two, 2, 5, 2000, ctypes.c_void_p(status.data_ptr()), stream), "wait for an earlier step")
+    torch.cuda.synchronize()
+    assert flags[:2].tolist() == [7, 7] and status.item() == 0
+    one = (ctypes.c_void_p * 1)(slot(2))                             # nothing ever writes slot 2
+    t0 = time.perf_counter()
+    nat.check(lib.mvpa_peer_wait(one, 1, 1, 2000, ctypes.c_void_p(status.data_ptr()), stream), "wait that runs out")
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 1.0 and status.item() == 1
+    src = torch.arange(3 * 70000, dtype=torch.int32, device=cuda).view(3, 70000)     # 280 000 bytes per piece
+    dst = torch.zeros_like(src)
+    n = 3
+    nat.check(lib.mvpa_peer_gather((ctypes.c_void_p * n)(*[dst[i].data_ptr() for i in range(n)]),
+                                   (ctypes.c_void_p * n)(*[src[i].data_ptr() for i in range(n)]),
+                                   (ctypes.c_int64 * n)(280000, 16, 0), n, stream), "gather")
+    torch.cuda.synchronize()
+    assert torch.equal(dst[0], src[0]) and torch.equal(dst[1, :4], src[1, :4]) and int(dst[1, 4:].abs().sum()) == 0
+    assert int(dst[2].abs().sum()) == 0
+    assert lib.mvpa_peer_gather((ctypes.c_void_p * 1)(dst.data_ptr()), (ctypes.c_void_p * 1)(src.data_ptr()),
+                                (ctypes.c_int64 * 1)(24), 1, stream) == -3      # not a multiple of 16 bytes
