@@ -542,6 +542,64 @@ def time_long_sample(torch, dist, dev, world, rank, flush, one_gpu_ms):
                        "steps, which walks all 128 key tiles in one CTA"}
 
 
+def time_long_sample_model(torch, dist, dev, world, rank, flush):
+    """The block stack of BASELINE config 5 (24 layers, E 2048, 16 heads / 8 kv heads) on ONE 16k-token sample:
+    the fused forward on one GPU against `forward_time_sharded` with the sample's time axis spread over the
+    ranks (zig-zag chunks; per layer only K and V travel, through the library's peer-load kernels, while the
+    MLP gate runs).  Random-init weights, encoder outputs drawn on the device.  Strong scaling of one sample."""
+    import models
+    import mvpa_shard as ms
+    spec = MODELS["cfg5"]
+    a, T, C = spec["arch"], spec["T"], spec["C"]
+    E = a["n_embd"]
+    torch.manual_seed(777)                                    # the same weights on every rank
+    with torch.device(dev):
+        cfg = models.MVPFormerConfig(n_positions=128, n_channels=128, **a)
+        model = models.MVPFormerModel(cfg)
+    model = model.to(dev).to(torch.bfloat16).eval()
+    g = torch.Generator(device=dev).manual_seed(778)
+    emb = (torch.randn(1, T, C, E, device=dev, generator=g) * 0.5).to(torch.bfloat16)
+    plan = ms.zigzag_chunks(T, C, world)
+    mine = torch.cat([emb.view(T * C, E)[t0 * C:(t0 + n) * C] for t0, n in plan[rank]])
+
+    def timed(fn, reps=3, warm=2):
+        out = []
+        for i in range(warm + reps):
+            dist.barrier()
+            torch.cuda.synchronize()
+            flush.add_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            y = fn()
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= warm:
+                out.append(e0.elapsed_time(e1))
+        t = torch.tensor([statistics.mean(out)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()), y
+
+    with torch.no_grad():
+        one, ref = timed(lambda: model(inputs_embeds=emb).last_hidden_state)
+        res = {}
+        ref = ref.view(T * C, E)
+        want = torch.cat([ref[t0 * C:(t0 + n) * C] for t0, n in plan[rank]]).float()
+        for transport in ("p2p", "nccl"):
+            try:
+                ms_t, got = timed(lambda: model.forward_time_sharded(mine, T, C, transport=transport))
+                err = torch.tensor([float((got.float() - want).abs().max())], dtype=torch.float64, device=dev)
+                dist.all_reduce(err, op=dist.ReduceOp.MAX)
+                res[transport] = {"ms": ms_t, "speedup_vs_1gpu": one / ms_t, "tokens_per_s": T * C / (ms_t * 1e-3),
+                                  "max_abs_diff_vs_1gpu": float(err.item())}
+            except Exception as e:
+                res[transport] = {"unavailable": repr(e)[:200]}
+    best = res["p2p"] if "ms" in res["p2p"] else res["nccl"]
+    return {"one_gpu_ms": one, "ms": best.get("ms"), "speedup_vs_1gpu": best.get("speedup_vs_1gpu"),
+            "tokens_per_s": best.get("tokens_per_s"), "layers": a["n_layer"], "tokens": T * C,
+            "peer_load_transport": res["p2p"], "nccl_transport": res["nccl"],
+            "hidden_state_scale": float(want.abs().max())}
+
+
 def hbm_peak():
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
@@ -847,6 +905,7 @@ def main():
         del tt
         if world > 1:
             extra["long_sample_16k"] = time_long_sample(torch, dist, dev, world, rank, flush, ms_16k)
+            extra["model_long_sample_16k"] = time_long_sample_model(torch, dist, dev, world, rank, flush)
     if rank == 0:
         if not args.no_extra:
             ff = flops(**WORKLOADS["16k"][0])

@@ -116,10 +116,11 @@ class FlashMVPA(torch.autograd.Function):
         return (dq, du, dvt, dz, dk, drt, drc, dv, None, None, None)
 
 
-def flash_mvpa_into(out, q, u, vt, z, k, r_time, r_chan, v, sm_scale, window_size=10):
+def flash_mvpa_into(out, q, u, vt, z, k, r_time, r_chan, v, sm_scale, window_size=10, q_time_range=None):
     """Inference form of `flash_mvpa`: no autograd record, no log-sum-exp output, and the result goes into
     `out`, a caller-owned (B,H,N,D) tensor that may be a strided view (e.g. a column block of the buffer the
-    next projection reads).  u, vt, z (Hkv,D); r_time (Hkv,T,D); r_chan (Hkv,C,D).  No counterpart in the
+    next projection reads).  u, vt, z (Hkv,D); r_time (Hkv,T,D); r_chan (Hkv,C,D).  `q_time_range=(t0, n)`:
+    `q` and `out` hold only the tokens of time steps t0..t0+n-1 (see `flash_mvpa`).  No counterpart in the
     reference, whose operator always allocates its output (`attentions/attn.py:1047`)."""
     if not q.is_cuda:
         raise RuntimeError("flash_mvpa: tensors must be on a CUDA device (no CPU path)")
@@ -129,7 +130,8 @@ def flash_mvpa_into(out, q, u, vt, z, k, r_time, r_chan, v, sm_scale, window_siz
     es = out.element_size()
     if out.stride(-1) != 1 or any((st * es) % 16 for st in out.stride()[:-1]) or out.data_ptr() % 16 or out.shape != q.shape:
         raise RuntimeError("flash_mvpa_into: `out` must have q's shape, a contiguous last dimension and 16-byte aligned strides")
-    prob = _problem(q, k, r_time, r_chan, sm_scale, window_size)
+    q_time = (0, 0) if q_time_range is None else (int(q_time_range[0]), int(q_time_range[1]))
+    prob = _problem(q, k, r_time, r_chan, sm_scale, window_size, q_time)
     nbytes = lib.mvpa_fwd_workspace_bytes(ctypes.byref(prob))
     ws = torch.empty(max(nbytes, 16), device=q.device, dtype=torch.uint8)
     tq, tk, tv, to = _tensor(q), _tensor(k), _tensor(v), _tensor(out)

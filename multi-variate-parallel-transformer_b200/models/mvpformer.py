@@ -145,6 +145,40 @@ class MVPFormerBlock(torch.nn.Module):
         mvpa_ops.silu_mul(big[:, g0:g0 + I], big[:, g0 + I:g0 + 2 * I], cat[:, E:])
         return F.linear(cat, w_out)
 
+    @torch.no_grad()
+    def fused_branches_time_sharded(self, x, r_time, r_chan, T, C, rows, group, transport):
+        """The same for ONE sample whose time axis is spread over the ranks of `group` (`mvpa_shard`): x holds
+        this rank's tokens, its two zig-zag chunks one after the other (`rows` = tokens per chunk).  Everything
+        but the attention is local to a token; K and V of the other ranks' tokens are gathered per layer while
+        the MLP's gate runs, and the rank's two query ranges write straight into the buffer the output
+        projection reads."""
+        import mvpa_shard
+        a = self.attn
+        E, H, Hkv, D = a.embed_dim, a.num_heads, a.num_kv_heads, a.head_dim
+        I = self.mlp.gate_proj.out_features
+        KV = Hkv * D
+        w_in, w_out = self.fused_weights()
+        big = F.linear(x, w_in)                                          # (rows of this rank, E + 2 KV + 2 I)
+        cat = torch.empty((x.shape[0], E + I), dtype=x.dtype, device=x.device)
+        u, vt, z = (b.view(Hkv, D).to(x.dtype) for b in a.attn_bias.detach().split(KV))
+        bounds = [(0, rows[0]), (rows[0], rows[0] + rows[1])]
+        part = lambda lo, hi, c0, heads: big[lo:hi, c0:c0 + heads * D].view(1, hi - lo, heads, D) if hi > lo else None
+        q_loc = [part(lo, hi, 0, H) for lo, hi in bounds]
+        kv_loc = [part(lo, hi, E, 2 * Hkv) for lo, hi in bounds]         # K and V side by side: fused along the head axis
+        if transport == "nccl":
+            kv_loc = [t.contiguous() if t is not None else None for t in kv_loc]
+        outs = iter([cat[lo:hi, :E].view(1, hi - lo, H, D).permute(0, 2, 1, 3) for lo, hi in bounds if hi > lo])
+
+        def op(q, u_, vt_, z_, k, rt, rc, v, causal, sm_scale, window_size, q_time_range):
+            return flash_mvpa_into(next(outs), q, u_, vt_, z_, k, rt, rc, v, sm_scale, window_size, q_time_range)
+
+        g0 = E + 2 * KV
+        mvpa_shard.time_sharded_attention(
+            op, q_loc, u, vt, z, kv_loc, r_time, r_chan, None, T, C, 1.0 / (D ** 0.5), 10, group=group,
+            overlap=lambda: mvpa_ops.silu_mul(big[:, g0:g0 + I], big[:, g0 + I:g0 + 2 * I], cat[:, E:]),
+            transport=transport)
+        return F.linear(cat, w_out)
+
 
 class MVPFormerModel(torch.nn.Module):
     def __init__(self, config, gradient_checkpointing=False):
@@ -207,6 +241,42 @@ class MVPFormerModel(torch.nn.Module):
             hidden = self._fused_forward(hidden, position_ids, channel_ids)
         return SimpleNamespace(last_hidden_state=hidden.view(B, T, C, E), past_key_values=None, hidden_states=None,
                                attentions=None, cross_attentions=None)
+
+    @torch.no_grad()
+    def forward_time_sharded(self, embeds_local, T: int, C: int, group=None, transport: str = "p2p"):
+        """Inference on ONE sample of T x C tokens whose time axis is spread over the ranks of `group`
+        (one process per GPU; no counterpart in the reference).  `embeds_local` (n*C, E) holds the encoder
+        outputs of this rank's tokens: the time steps of its two zig-zag chunks (`mvpa_shard.zigzag_chunks(T,
+        C, world)[rank]`), first chunk first, token = t*C + c inside a chunk.  Returns the last hidden state
+        of the same tokens, (n*C, E).  Norms, projections and the MLP are local to a token; per layer only
+        K and V travel (`transport`: "p2p", this library's peer-load kernels, or "nccl")."""
+        import mvpa_shard
+        import torch.distributed as dist
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        plan = mvpa_shard.zigzag_chunks(T, C, world)
+        rows = [n * C for _, n in plan[rank]]
+        if embeds_local.shape[0] != sum(rows):
+            raise ValueError(f"rank {rank} owns {sum(rows)} tokens of this sample, got {embeds_local.shape[0]}")
+        dev = embeds_local.device
+        position_embeds = self.positional_embedding(torch.arange(T, dtype=torch.long, device=dev))
+        channel_embeds = self.channel_embedding(torch.arange(C, dtype=torch.long, device=dev))
+        L, Hkv, D = len(self.h), self.num_kv_heads, self.head_dim
+        w_pos, w_chan = self._rel_weights()
+        r_time = F.linear(position_embeds.to(embeds_local.dtype), w_pos).view(T, L, Hkv, D).permute(1, 2, 0, 3).contiguous()
+        r_chan = F.linear(channel_embeds.to(embeds_local.dtype), w_chan).view(C, L, Hkv, D).permute(1, 2, 0, 3).contiguous()
+        h = embeds_local.contiguous().clone()                             # the residual stream is updated in place
+        branches = None
+        import attentions.attn as attn_mod
+        check = attn_mod._CHECK_STATUS
+        attn_mod._CHECK_STATUS = False      # reading a status word back after every launch would stall the overlap
+        try:
+            for i, block in enumerate(self.h):
+                w = block.ln_1.weight.detach().to(h.dtype)
+                x = mvpa_ops.rmsnorm(h, w, block.ln_1.eps, add=branches, sum_out=h if branches is not None else None)
+                branches = block.fused_branches_time_sharded(x, r_time[i], r_chan[i], T, C, rows, group, transport)
+        finally:
+            attn_mod._CHECK_STATUS = check
+        return mvpa_ops.rmsnorm(h, self.ln_f.weight.detach().to(h.dtype), self.ln_f.eps, add=branches, sum_out=h)
 
     def enable_cuda_graph(self, flag: bool = True):
         """Inference with frozen weights: capture the fused forward of each input shape in a CUDA graph on

@@ -154,8 +154,24 @@ def _gpu_worker(rank, world, port, out_dir):
             outs = ms.time_sharded_attention(attentions.flashmvpa, cut(q), u, vt, z, cut(kv if fused else k), rt, rc,
                                              None if fused else cut(v), T, C, D ** -0.5, 10, transport=transport)
             same = same and all(torch.equal(o, full[:, t0 * C:(t0 + n) * C]) for (t0, n), o in zip(plan[rank], outs) if n)
+        # the whole block stack on one sample spread over the ranks, against the single-GPU fused forward
+        # (row-wise operations on fewer rows may pick other GEMM kernels: a tolerance, not bit equality)
+        import models
+        torch.manual_seed(11)
+        cfg = models.MVPFormerConfig(n_positions=64, n_channels=64, n_embd=256, n_layer=2, n_head=4, n_head_kv=2, n_inner=512)
+        model = models.MVPFormerModel(cfg).to(dev).to(torch.bfloat16).eval()
+        Tm, Cm = 32, 32
+        emb = (torch.randn(1, Tm, Cm, 256, generator=g) * 0.5).to(torch.bfloat16).to(dev)
+        ref = model(inputs_embeds=emb).last_hidden_state.view(Tm * Cm, 256)
+        mplan = ms.zigzag_chunks(Tm, Cm, world)
+        mine = torch.cat([emb.view(Tm * Cm, 256)[t0 * Cm:(t0 + n) * Cm] for t0, n in mplan[rank]])
+        want = torch.cat([ref[t0 * Cm:(t0 + n) * Cm] for t0, n in mplan[rank]])
+        worst = 0.0
+        for transport in ("p2p", "nccl"):
+            got = model.forward_time_sharded(mine, Tm, Cm, transport=transport)
+            worst = max(worst, float((got.float() - want.float()).abs().max()))
         torch.cuda.synchronize()
-        np.save(os.path.join(out_dir, f"same{rank}.npy"), np.array([int(same)]))
+        np.save(os.path.join(out_dir, f"same{rank}.npy"), np.array([int(same), worst, float(want.float().abs().max())]))
     finally:
         dist.destroy_process_group()
 
@@ -169,4 +185,7 @@ def test_time_sharding_two_gpus_nccl_bit_equal_to_single_gpu(tmp_path):
         pytest.skip("needs 2 GPUs")
     port = 29500 + (os.getpid() % 2000) + 7
     mp.spawn(_gpu_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
-    assert all(int(np.load(tmp_path / f"same{r}.npy")[0]) == 1 for r in range(2))
+    res = [np.load(tmp_path / f"same{r}.npy") for r in range(2)]
+    assert all(int(x[0]) == 1 for x in res)
+    # model level: bf16 hidden states of magnitude `scale`; 2 % of it covers other GEMM kernels on fewer rows
+    assert all(x[1] <= 0.02 * max(x[2], 1.0) for x in res), [(x[1], x[2]) for x in res]
