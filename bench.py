@@ -584,19 +584,21 @@ def time_long_sample_model(torch, dist, dev, world, rank, flush):
         res = {}
         ref = ref.view(T * C, E)
         want = torch.cat([ref[t0 * C:(t0 + n) * C] for t0, n in plan[rank]]).float()
-        for transport in ("p2p", "nccl"):
+        for transport in ("p2p_graph", "p2p", "nccl"):
             try:
-                ms_t, got = timed(lambda: model.forward_time_sharded(mine, T, C, transport=transport))
+                kw = dict(transport="p2p", graph=True) if transport == "p2p_graph" else dict(transport=transport)
+                ms_t, got = timed(lambda: model.forward_time_sharded(mine, T, C, **kw))
                 err = torch.tensor([float((got.float() - want).abs().max())], dtype=torch.float64, device=dev)
                 dist.all_reduce(err, op=dist.ReduceOp.MAX)
                 res[transport] = {"ms": ms_t, "speedup_vs_1gpu": one / ms_t, "tokens_per_s": T * C / (ms_t * 1e-3),
                                   "max_abs_diff_vs_1gpu": float(err.item())}
             except Exception as e:
                 res[transport] = {"unavailable": repr(e)[:200]}
-    best = res["p2p"] if "ms" in res["p2p"] else res["nccl"]
+    best = next(res[k] for k in ("p2p_graph", "p2p", "nccl") if "ms" in res[k] or k == "nccl")
     return {"one_gpu_ms": one, "ms": best.get("ms"), "speedup_vs_1gpu": best.get("speedup_vs_1gpu"),
             "tokens_per_s": best.get("tokens_per_s"), "layers": a["n_layer"], "tokens": T * C,
-            "peer_load_transport": res["p2p"], "nccl_transport": res["nccl"],
+            "peer_load_transport_cuda_graph": res["p2p_graph"], "peer_load_transport": res["p2p"],
+            "nccl_transport": res["nccl"],
             "hidden_state_scale": float(want.abs().max())}
 
 

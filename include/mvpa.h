@@ -222,18 +222,21 @@ int mvpa_peer_gather(void* const* dst, const void* const* src, const int64_t* by
 
 /*
  * Flags between GPUs for `mvpa_peer_gather` (no counterpart in the reference): 32-bit counters in device
- * memory that a peer has mapped.  `mvpa_peer_signal` stores `value` into each of the n remote slots after
- * a system-wide fence, so everything enqueued earlier on the stream is visible to a peer that has seen the
- * flag.  `mvpa_peer_wait` returns (on the stream) once each of the n local slots has reached `value`
- * (compared as a wrapping counter); the wait is bounded: after `limit_us` microseconds (0 = two seconds)
- * the kernel stores 1 to *status (device memory, may be NULL) and returns, so a missing peer surfaces as a
- * status the host reads later, not as a hung GPU.  Both take HOST arrays of at most
+ * memory that a peer has mapped.  The number signalled or waited for is `value`, plus `*base` when `base`
+ * (device memory, read when the kernel runs) is not NULL - a step counter kept on the device lets a CUDA
+ * graph replay the same launches step after step.  `mvpa_peer_signal` stores the number into each of the n
+ * remote slots after a system-wide fence, so everything enqueued earlier on the stream is visible to a peer
+ * that has seen the flag.  `mvpa_peer_wait` returns (on the stream) once each of the n local slots has
+ * reached the number (compared as a wrapping counter); the wait is bounded: after `limit_us` microseconds
+ * (0 = two seconds) the kernel stores 1 to *status (device memory, may be NULL) and returns, so a missing
+ * peer surfaces as a status the host reads later, not as a hung GPU.  Both take HOST arrays of at most
  * MVPA_MAX_GATHER_PIECES device pointers.  The waiting and the signalling kernels must run on different
  * GPUs (one rank per GPU).
  */
-int mvpa_peer_signal(uint32_t* const* remote_slots, int32_t n, uint32_t value, void* cuda_stream);
-int mvpa_peer_wait(const uint32_t* const* local_slots, int32_t n, uint32_t value, uint32_t limit_us,
-                   int32_t* status, void* cuda_stream);
+int mvpa_peer_signal(uint32_t* const* remote_slots, int32_t n, uint32_t value, const uint32_t* base,
+                     void* cuda_stream);
+int mvpa_peer_wait(const uint32_t* const* local_slots, int32_t n, uint32_t value, const uint32_t* base,
+                   uint32_t limit_us, int32_t* status, void* cuda_stream);
 
 /*
  * Classification readout: out[b] = mean over channels of h[b, T-1] for h (B,T,C,E)

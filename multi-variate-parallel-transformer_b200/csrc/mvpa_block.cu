@@ -627,16 +627,18 @@ struct FlagSlots {
   uint32_t* slot[MVPA_MAX_GATHER_PIECES];
   int n;
 };
-static __global__ void peer_signal_kernel(const __grid_constant__ FlagSlots f, uint32_t value) {
+static __global__ void peer_signal_kernel(const __grid_constant__ FlagSlots f, uint32_t value, const uint32_t* base) {
   const int i = threadIdx.x;
+  if (base != nullptr) value += *base;
   if (i < f.n) {
     __threadfence_system();  // what this stream wrote before is visible before the flag is
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f.slot[i]), "r"(value) : "memory");
   }
 }
-static __global__ void peer_wait_kernel(const __grid_constant__ FlagSlots f, uint32_t value, uint64_t limit_ns,
-                                        int* status) {
+static __global__ void peer_wait_kernel(const __grid_constant__ FlagSlots f, uint32_t value, const uint32_t* base,
+                                        uint64_t limit_ns, int* status) {
   const int i = threadIdx.x;
+  if (base != nullptr) value += *base;
   if (i < f.n) {
     uint64_t t0;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
@@ -672,23 +674,24 @@ static int flag_slots(FlagSlots& f, const void* const* slots, int32_t n, const c
   return MVPA_OK;
 }
 
-int mvpa_peer_signal(uint32_t* const* remote_slots, int32_t n, uint32_t value, void* cuda_stream) {
+int mvpa_peer_signal(uint32_t* const* remote_slots, int32_t n, uint32_t value, const uint32_t* base,
+                     void* cuda_stream) {
   FlagSlots f;
   const int rc = flag_slots(f, (const void* const*)remote_slots, n, "mvpa_peer_signal");
   if (rc != MVPA_OK || n == 0) return rc;
-  peer_signal_kernel<<<1, MVPA_MAX_GATHER_PIECES, 0, (cudaStream_t)cuda_stream>>>(f, value);
+  peer_signal_kernel<<<1, MVPA_MAX_GATHER_PIECES, 0, (cudaStream_t)cuda_stream>>>(f, value, base);
   count_launch();
   MVPA_CUDA_CHECK(cudaGetLastError());
   return MVPA_OK;
 }
 
-int mvpa_peer_wait(const uint32_t* const* local_slots, int32_t n, uint32_t value, uint32_t limit_us, int32_t* status,
-                   void* cuda_stream) {
+int mvpa_peer_wait(const uint32_t* const* local_slots, int32_t n, uint32_t value, const uint32_t* base,
+                   uint32_t limit_us, int32_t* status, void* cuda_stream) {
   FlagSlots f;
   const int rc = flag_slots(f, (const void* const*)local_slots, n, "mvpa_peer_wait");
   if (rc != MVPA_OK || n == 0) return rc;
   const uint64_t limit_ns = limit_us != 0 ? (uint64_t)limit_us * 1000ull : 2000000000ull;
-  peer_wait_kernel<<<1, MVPA_MAX_GATHER_PIECES, 0, (cudaStream_t)cuda_stream>>>(f, value, limit_ns, status);
+  peer_wait_kernel<<<1, MVPA_MAX_GATHER_PIECES, 0, (cudaStream_t)cuda_stream>>>(f, value, base, limit_ns, status);
   count_launch();
   MVPA_CUDA_CHECK(cudaGetLastError());
   return MVPA_OK;

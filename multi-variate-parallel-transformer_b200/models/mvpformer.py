@@ -243,13 +243,36 @@ class MVPFormerModel(torch.nn.Module):
                                attentions=None, cross_attentions=None)
 
     @torch.no_grad()
-    def forward_time_sharded(self, embeds_local, T: int, C: int, group=None, transport: str = "p2p"):
+    def forward_time_sharded(self, embeds_local, T: int, C: int, group=None, transport: str = "p2p", graph: bool = False):
         """Inference on ONE sample of T x C tokens whose time axis is spread over the ranks of `group`
         (one process per GPU; no counterpart in the reference).  `embeds_local` (n*C, E) holds the encoder
         outputs of this rank's tokens: the time steps of its two zig-zag chunks (`mvpa_shard.zigzag_chunks(T,
         C, world)[rank]`), first chunk first, token = t*C + c inside a chunk.  Returns the last hidden state
         of the same tokens, (n*C, E).  Norms, projections and the MLP are local to a token; per layer only
-        K and V travel (`transport`: "p2p", this library's peer-load kernels, or "nccl")."""
+        K and V travel (`transport`: "p2p", this library's peer-load kernels, or "nccl").  `graph=True` (peer-load
+        transport, frozen weights): the whole forward is captured in a CUDA graph on first use and replayed -
+        its step counters live on the device, so every replay orders itself against the other ranks' replays;
+        the result is the graph's own buffer, overwritten by the next call."""
+        if graph and transport == "p2p":
+            key = ("sharded", tuple(embeds_local.shape), embeds_local.dtype, embeds_local.device.index, T, C, id(group))
+            entry = self._graphs.get(key)
+            if entry is None:
+                static_in = embeds_local.clone()
+                cur = torch.cuda.current_stream(embeds_local.device)
+                side = torch.cuda.Stream(device=embeds_local.device)
+                side.wait_stream(cur)
+                with torch.cuda.stream(side):              # warm-up: builds the send buffers and mappings (collective)
+                    self.forward_time_sharded(static_in, T, C, group, transport)
+                cur.wait_stream(side)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    static_out = self.forward_time_sharded(static_in, T, C, group, transport)
+                entry = (g, static_in, static_out)
+                self._graphs[key] = entry
+            g, static_in, static_out = entry
+            static_in.copy_(embeds_local)
+            g.replay()
+            return static_out
         import mvpa_shard
         import torch.distributed as dist
         world, rank = dist.get_world_size(group), dist.get_rank(group)

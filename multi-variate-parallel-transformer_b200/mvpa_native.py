@@ -144,9 +144,9 @@ def lib() -> ctypes.CDLL:
         L.mvpa_wave_encode.argtypes = [vp, i64, i32, ctypes.POINTER(f32), ctypes.POINTER(f32), vp, vp, i64, i32, i64,
                                        i32, f32, vp]
         L.mvpa_peer_signal.restype = ctypes.c_int
-        L.mvpa_peer_signal.argtypes = [vp, i32, ctypes.c_uint32, vp]
+        L.mvpa_peer_signal.argtypes = [vp, i32, ctypes.c_uint32, vp, vp]
         L.mvpa_peer_wait.restype = ctypes.c_int
-        L.mvpa_peer_wait.argtypes = [vp, i32, ctypes.c_uint32, ctypes.c_uint32, vp, vp]
+        L.mvpa_peer_wait.argtypes = [vp, i32, ctypes.c_uint32, vp, ctypes.c_uint32, vp, vp]
         L.mvpa_peer_gather.restype = ctypes.c_int
         L.mvpa_peer_gather.argtypes = [vp, vp, vp, i32, vp]
         L.mvpa_channel_mean.restype = ctypes.c_int

@@ -88,7 +88,9 @@ class KVGather:
         self._events = events
 
     def wait(self, half: int = 1) -> torch.Tensor:
-        for ev in self._events[:half + 1]:
+        # (a third event, where present, marks the end of the communication stream's work for the step; the
+        # last wait takes it along so that the stream is joined again, as a CUDA graph capture requires)
+        for ev in self._events[:half + 1] + (self._events[2:] if half >= 1 else []):
             if ev is not None:
                 torch.cuda.current_stream(self.full.device).wait_event(ev)
         return self.full
@@ -142,7 +144,7 @@ class PeerKV:
         from torch.multiprocessing.reductions import reduce_tensor
         world, rank = dist.get_world_size(group), dist.get_rank(group)
         assert world <= 32, "at most 32 ranks (pieces per gather launch)"
-        self.world, self.rank, self.group, self.step = world, rank, group, 0
+        self.world, self.rank, self.group = world, rank, group
         self.rows = [[plan[r][i][1] * C for i in range(2)] for r in range(world)]
         item = torch.empty((), dtype=dtype).element_size()
         row_bytes = heads * dim * item
@@ -192,6 +194,10 @@ class PeerKV:
         self._status_ptr = base[rank] + 512
         self._status = self._all[nbytes(rank) + 512:nbytes(rank) + 516].view(torch.int32)
         self._pieces = {}                                             # argument arrays of the gather launches, per receive buffer
+        # The step counter lives on the device (the flag kernels add it to the number they are given), so the
+        # same launches serve every step and a CUDA graph can replay them.
+        self._step = torch.zeros(1, dtype=torch.int32, device=device)
+        self.joined, self.joined_capturing = None, False              # event: the communication stream is done with the step
 
     @classmethod
     def get(cls, plan, C, heads, dim, dtype, device, batch, group, tag=0):
@@ -205,22 +211,27 @@ class PeerKV:
         import ctypes
         return (ctypes.c_void_p * len(ptrs))(*ptrs), len(ptrs)
 
+    def next_step(self) -> None:
+        """Advances the step counter on the current stream (which has waited for the previous step's `joined`)."""
+        self._step.add_(1)
+
     def signal(self, which: str, device) -> None:
         """Tells every rank (on the current stream, after everything enqueued before) that this rank's rows
         of the current step are written (`which="written"`) or that it has read theirs (`"read"`)."""
         import ctypes
         import mvpa_native as _nat
         arr, n = self._slots(self._written_there if which == "written" else self._read_there)
-        _nat.check(_nat.lib().mvpa_peer_signal(arr, n, self.step, ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)),
-                   "mvpa_peer_signal")
+        _nat.check(_nat.lib().mvpa_peer_signal(arr, n, 0, ctypes.c_void_p(self._step.data_ptr()),
+                                               ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)), "mvpa_peer_signal")
 
-    def wait(self, which: str, step: int, device) -> None:
-        """Holds the current stream until every rank has signalled `which` for `step` (at most two seconds:
-        after that the status word is set and the stream goes on; `check()` reports it)."""
+    def wait(self, which: str, back: int, device) -> None:
+        """Holds the current stream until every rank has signalled `which` for the step `back` steps ago (at
+        most two seconds: after that the status word is set and the stream goes on; `check()` reports it)."""
         import ctypes
         import mvpa_native as _nat
         arr, n = self._slots(self._written_here if which == "written" else self._read_here)
-        _nat.check(_nat.lib().mvpa_peer_wait(arr, n, step, 0, ctypes.c_void_p(self._status_ptr),
+        _nat.check(_nat.lib().mvpa_peer_wait(arr, n, (-back) & 0xFFFFFFFF, ctypes.c_void_p(self._step.data_ptr()), 0,
+                                             ctypes.c_void_p(self._status_ptr),
                                              ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)), "mvpa_peer_wait")
 
     def check(self) -> None:
@@ -283,9 +294,15 @@ def start_kv_gather(local: Sequence[Optional[torch.Tensor]], plan: List[List[Tup
     if transport == "p2p":
         px = PeerKV.get(plan, C, heads, dim, dtype, device, batch, group, tag)   # `tag` keeps K's and V's buffers apart
         cur = torch.cuda.current_stream(device)
-        px.step += 1
-        if px.step > 1:
-            px.wait("read", px.step - 1, device)             # the peers have copied the previous rows
+        capturing = torch.cuda.is_current_stream_capturing()
+        if px.joined is not None and px.joined_capturing == capturing:
+            # the communication stream has read the previous step's counter.  (An event recorded outside a graph
+            # capture cannot be waited for inside one, nor the other way round; at those two boundaries the
+            # previous step has been joined to the current stream already - `KVGather.wait(1)` - and plain stream
+            # order does the rest.)
+            cur.wait_event(px.joined)
+        px.next_step()
+        px.wait("read", 1, device)                           # the peers have copied the previous rows (step 0: nothing to wait for)
         for i in range(2):
             if local[i] is not None and local[i].data_ptr() != px.send[i].data_ptr():
                 px.send[i].copy_(local[i])                   # (a caller may produce its rows in `send[i]` directly)
@@ -294,13 +311,17 @@ def start_kv_gather(local: Sequence[Optional[torch.Tensor]], plan: List[List[Tup
         full.record_stream(comm)
         events = []
         with torch.cuda.stream(comm):
-            px.wait("written", px.step, device)              # every rank's rows of this step are complete
+            px.wait("written", 0, device)                    # every rank's rows of this step are complete
             for half in range(2):
                 _peer_gather_half(full, px, plan, half, C)
                 ev = torch.cuda.Event()
                 ev.record(comm)
                 events.append(ev)
             px.signal("read", device)
+            px.joined = torch.cuda.Event()
+            px.joined.record(comm)
+            px.joined_capturing = capturing
+        events.append(px.joined)
         return KVGather(full, events)
     comm.wait_stream(torch.cuda.current_stream(device))      # the local rows were produced on the current stream
     full.record_stream(comm)

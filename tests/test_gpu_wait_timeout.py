@@ -54,14 +54,17 @@ def test_peer_flags_signal_wait_and_timeout(cuda):
     status = torch.zeros(1, dtype=torch.int32, device=cuda)
     slot = lambda i: flags.data_ptr() + 4 * i
     two = (ctypes.c_void_p * 2)(slot(0), slot(1))
-    nat.check(lib.mvpa_peer_signal(two, 2, 7, stream), "signal")
-    nat.check(lib.mvpa_peer_wait(two, 2, 7, 2000, ctypes.c_void_p(status.data_ptr()), stream), "wait")
-    nat.check(lib.mvpa_peer_wait(two, 2, 5, 2000, ctypes.c_void_p(status.data_ptr()), stream), "wait for an earlier step")
+    nat.check(lib.mvpa_peer_signal(two, 2, 7, None, stream), "signal")
+    nat.check(lib.mvpa_peer_wait(two, 2, 7, None, 2000, ctypes.c_void_p(status.data_ptr()), stream), "wait")
+    nat.check(lib.mvpa_peer_wait(two, 2, 5, None, 2000, ctypes.c_void_p(status.data_ptr()), stream), "wait for an earlier step")
+    base = torch.tensor([4], dtype=torch.int32, device=cuda)        # a step counter on the device: 4 + 3 = 7, 4 - 1 = 3
+    nat.check(lib.mvpa_peer_wait(two, 2, 3, ctypes.c_void_p(base.data_ptr()), 2000, ctypes.c_void_p(status.data_ptr()), stream), "wait, device base")
+    nat.check(lib.mvpa_peer_wait(two, 2, 0xFFFFFFFF, ctypes.c_void_p(base.data_ptr()), 2000, ctypes.c_void_p(status.data_ptr()), stream), "wait, base - 1")
     torch.cuda.synchronize()
     assert flags[:2].tolist() == [7, 7] and status.item() == 0
     one = (ctypes.c_void_p * 1)(slot(2))                             # nothing ever writes slot 2
     t0 = time.perf_counter()
-    nat.check(lib.mvpa_peer_wait(one, 1, 1, 2000, ctypes.c_void_p(status.data_ptr()), stream), "wait that runs out")
+    nat.check(lib.mvpa_peer_wait(one, 1, 1, None, 2000, ctypes.c_void_p(status.data_ptr()), stream), "wait that runs out")
     torch.cuda.synchronize()
     assert time.perf_counter() - t0 < 1.0 and status.item() == 1
     src = torch.arange(3 * 70000, dtype=torch.int32, device=cuda).view(3, 70000)     # 280 000 bytes per piece

@@ -167,8 +167,9 @@ def _gpu_worker(rank, world, port, out_dir):
         mine = torch.cat([emb.view(Tm * Cm, 256)[t0 * Cm:(t0 + n) * Cm] for t0, n in mplan[rank]])
         want = torch.cat([ref[t0 * Cm:(t0 + n) * Cm] for t0, n in mplan[rank]])
         worst = 0.0
-        for transport in ("p2p", "nccl"):
-            got = model.forward_time_sharded(mine, Tm, Cm, transport=transport)
+        for kw in (dict(transport="p2p"), dict(transport="nccl"), dict(transport="p2p", graph=True),
+                   dict(transport="p2p", graph=True)):                  # capture, then a replay
+            got = model.forward_time_sharded(mine, Tm, Cm, **kw)
             worst = max(worst, float((got.float() - want.float()).abs().max()))
         torch.cuda.synchronize()
         np.save(os.path.join(out_dir, f"same{rank}.npy"), np.array([int(same), worst, float(want.float().abs().max())]))
