@@ -175,6 +175,13 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
   // scheduler are in different phases (one in its exponentials, the other loading or reducing)
   // and no barrier is needed inside a tile; the accumulators are merged before the light tiles.
   constexpr bool ALT = (D == 64) && (CP <= 64);
+  // Split accumulators (head_dim 64 with 128 channel slots): both warpgroups work on every dense tile, each
+  // on its 64 key columns with its OWN running maximum, row sum and O accumulator (O_0 / O_1, 2 x 64 TMEM
+  // columns; the PV product of a tile is issued as two groups of four K-steps).  No maximum exchange and no
+  // barrier inside a tile; the two accumulators are merged once before the light tiles.  (Measured against
+  // the alternating path at 64 and 32 channel slots it is 1-5 % slower there, and 2.6 % faster than the
+  // exchange at 128 slots; head_dim 128 has no TMEM columns for a second accumulator.)
+  constexpr bool SPLIT = (D == 64) && !ALT;
   // With at most 64 channel slots the prologue's scratch rows are padded instead of rotated, and each
   // thread's columns hold every channel slot (no maximum exchange between the warpgroups).
   constexpr bool PAD = CP <= 64;
@@ -377,7 +384,8 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
         const uint32_t d_o = ALT ? tm + kColO + 64 * (s & 1) : tm + kColO;
         const uint32_t acc0 = ALT ? (uint32_t)(s > 1) : (uint32_t)(s > 0);
         mma_ts_x4_w(el, d_o, a0, b_lo, dv0.hi, 2048 >> 4, idesc_o, acc0);
-        mma_ts_x4_w(el, d_o, a0 + (ALT ? 32 : 64), b_lo + 4 * (2048 >> 4), dv0.hi, 2048 >> 4, idesc_o, 1u);
+        mma_ts_x4_w(el, SPLIT ? d_o + 64 : d_o, a0 + (ALT ? 32 : 64), b_lo + 4 * (2048 >> 4), dv0.hi, 2048 >> 4, idesc_o,
+                    SPLIT ? acc0 : 1u);
         mma_commit_w(el, a_free + 8 * v_sl);
         advance_v(dn ? 2 : 1);  // a dense successor's V is two loads on, a light successor's one
       }
@@ -520,14 +528,16 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
       if (!warp_wait(&slot_free[qp % NS], (qp / NS) & 1, p.status, 33)) return false;
       tc_fence_after();
       const float alpha = need ? ex2(m_used - m_tile) : 1.f;
+      // (split accumulators: all D columns of this warpgroup's own O; otherwise its half of the one O)
+      constexpr int own0 = SPLIT ? 64 : DW, own_n = SPLIT ? D : DW;
 #pragma unroll
-      for (int c0 = 0; c0 < DW; c0 += 32) {
+      for (int c0 = 0; c0 < own_n; c0 += 32) {
         uint32_t v[32];
-        tmem_ld32(lane_base + kColO + wg * DW + c0, v);
+        tmem_ld32(lane_base + kColO + wg * own0 + c0, v);
         tmem_ld_wait();
 #pragma unroll
         for (int jj = 0; jj < 32; ++jj) v[jj] = __float_as_uint(__uint_as_float(v[jj]) * alpha);
-        tmem_st32(lane_base + kColO + wg * DW + c0, v);
+        tmem_st32(lane_base + kColO + wg * own0 + c0, v);
       }
       tmem_st_wait();
       l_sum *= alpha;
@@ -760,12 +770,17 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
         for (int tl = 0; tl < TPW; ++tl)
           if (valid[tl]) m_part = fmaxf(m_part, gmax[tl] + tbv[tl]);
       }
-      // the two column halves of a row must agree on the tile maximum
-      s_max[(buf * 2 + wg) * 128 + row] = m_part;
-      if (!ok) *s_giveup = 1;
-      softmax_bar();
-      if (*s_giveup != 0) { ok = false; break; }  // some warp's wait ran out: everyone leaves together
-      const float m_tile = fmaxf(m_part, s_max[(buf * 2 + (wg ^ 1)) * 128 + row]);
+      float m_tile = m_part;
+      if constexpr (SPLIT) {
+        if (!ok) break;  // (no barrier inside this loop: the flag is raised at the merge below)
+      } else {
+        // the two column halves of a row must agree on the tile maximum
+        s_max[(buf * 2 + wg) * 128 + row] = m_part;
+        if (!ok) *s_giveup = 1;
+        softmax_bar();
+        if (*s_giveup != 0) { ok = false; break; }  // some warp's wait ran out: everyone leaves together
+        m_tile = fmaxf(m_part, s_max[(buf * 2 + (wg ^ 1)) * 128 + row]);
+      }
       if (s == 0) {
         m_used = (m_tile == -INFINITY) ? 0.f : m_tile;
       } else if (!maybe_rescale(s, m_tile)) {
@@ -793,6 +808,40 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const TcArgs p) {
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bars[kBarPFull + buf]);
+    }
+    if constexpr (SPLIT) {
+      // ---- merge the two accumulators: O_0 <- O_0 2^(m_0 - m) + O_1 2^(m_1 - m); each warpgroup takes half
+      //      of the columns; the row sum moves to the first warpgroup ----
+      s_merge[wg * 128 + row] = m_used;
+      s_merge[256 + wg * 128 + row] = l_sum;
+      if (!ok) *s_giveup = 1;
+      softmax_bar();
+      if (*s_giveup != 0) ok = false;
+      if (ok && n_dense > 0) {
+        const float m_other = s_merge[(wg ^ 1) * 128 + row], l_other = s_merge[256 + (wg ^ 1) * 128 + row];
+        const float m_new = fmaxf(m_used, m_other);
+        const float a_self = ex2(m_used - m_new), a_oth = ex2(m_other - m_new);
+        const int q1 = q_of_v(n_dense - 1);
+        ok = warp_wait(&slot_free[q1 % NS], (q1 / NS) & 1, p.status, 36);
+        if (ok) {
+          tc_fence_after();
+          const float a_0 = wg == 0 ? a_self : a_oth, a_1 = wg == 0 ? a_oth : a_self;
+          uint32_t v0[32], v1[32];
+          tmem_ld32(lane_base + kColO + wg * DW, v0);
+          tmem_ld32(lane_base + kColO + 64 + wg * DW, v1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj)
+            v0[jj] = __float_as_uint(__uint_as_float(v0[jj]) * a_0 + __uint_as_float(v1[jj]) * a_1);
+          tmem_st32(lane_base + kColO + wg * DW, v0);
+          tmem_st_wait();
+          tc_fence_before();
+        }
+        l_sum = wg == 0 ? l_sum * a_self + l_other * a_oth : 0.f;
+        m_used = m_new;
+      }
+      // (each warpgroup goes on with its own half of the merged columns; the first light PV product needs both
+      // warpgroups' arrival, so it cannot start before both halves are merged)
     }
 
     }  // !ALT
