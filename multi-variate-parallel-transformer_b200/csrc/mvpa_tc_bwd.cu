@@ -1554,7 +1554,7 @@ int launch(const BwdArgs& bw, float* cs_dq, int* status, float* relc, unsigned l
   if (!(D == 64 && CP <= 64))  // (the kernel keeps these sums in shared memory otherwise)
     MVPA_CUDA_CHECK(cudaMemsetAsync(bw.dtbg, 0, sizeof(float) * (size_t)a.B * a.H * a.N * a.T, s));
   rel_const_kernel<D><<<a.Hkv, 256, 0, s>>>((const __nv_bfloat16*)a.vt, (const __nv_bfloat16*)a.z,
-                                           (const __nv_bfloat16*)a.rt, (const __nv_bfloat16*)a.rc, relc, a.T, a.C);
+                                           (const __nv_bfloat16*)a.rt, (const __nv_bfloat16*)a.rc, relc, a.T, a.C, nullptr);
   const unsigned grid = (unsigned)t.n_qt * a.B * a.H;
   tc_bwd_q_kernel<D, CP><<<grid, kThreads, smem, s>>>(maps, t);
   count_launch(2);

@@ -1086,9 +1086,8 @@ int launch(const Args& a, int* status, cudaStream_t s) {
   static_assert(smem <= 232448, "shared memory budget");
   static_assert(Cfg<D>::EARLY >= 2, "the first tile's K and V load while the prologue runs");
   MVPA_CUDA_CHECK(cudaFuncSetAttribute(tc_fwd_kernel<D, CP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  MVPA_CUDA_CHECK(cudaMemsetAsync(status, 0, 256, s));
   rel_const_kernel<D><<<a.Hkv, 256, 0, s>>>(t.vt, t.z, (const __nv_bfloat16*)a.rt, (const __nv_bfloat16*)a.rc, relc, a.T,
-                                           a.C);
+                                           a.C, status);  // (clears the status words too)
   count_launch();
   const unsigned grid = (unsigned)t.q_tiles * a.B * a.H;
   tc_fwd_kernel<D, CP><<<grid, kThreads, smem, s>>>(maps, t);

@@ -16,7 +16,11 @@ static __global__ void __launch_bounds__(256) rel_const_kernel(const __nv_bfloat
                                                                const __nv_bfloat16* __restrict__ z,
                                                                const __nv_bfloat16* __restrict__ rt,
                                                                const __nv_bfloat16* __restrict__ rc,
-                                                               float* __restrict__ relc, int T, int C) {
+                                                               float* __restrict__ relc, int T, int C,
+                                                               int* __restrict__ status_words) {
+  // (also clears the 64 status words of the kernels that follow, where the caller asks for it: one memset
+  // node less in front of them)
+  if (status_words != nullptr && blockIdx.x == 0 && threadIdx.x < 64) status_words[threadIdx.x] = 0;
   const int hk = blockIdx.x, j = threadIdx.x & 127;
   const bool is_t = threadIdx.x < 128;
   const int rows = is_t ? T : C;
