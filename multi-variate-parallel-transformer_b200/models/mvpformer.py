@@ -264,9 +264,12 @@ class MVPFormerModel(torch.nn.Module):
                 with torch.cuda.stream(side):              # warm-up: builds the send buffers and mappings (collective)
                     self.forward_time_sharded(static_in, T, C, group, transport)
                 cur.wait_stream(side)
+                import mvpa_shard as _ms
+                _ms.PeerKV.forget_events()                 # events of earlier work cannot be waited for inside a capture
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g):
                     static_out = self.forward_time_sharded(static_in, T, C, group, transport)
+                _ms.PeerKV.forget_events()                 # ... nor those of the capture outside it
                 entry = (g, static_in, static_out)
                 self._graphs[key] = entry
             g, static_in, static_out = entry

@@ -207,6 +207,13 @@ class PeerKV:
             cls._cache[key] = cls(plan, C, heads, dim, dtype, device, batch, group)
         return cls._cache[key]
 
+    @classmethod
+    def forget_events(cls) -> None:
+        """Drops the "communication stream is done" events of all buffers.  Called with every stream joined
+        (before and after a CUDA graph capture): stream order alone then orders the next step."""
+        for px in cls._cache.values():
+            px.joined = None
+
     def _slots(self, ptrs):
         import ctypes
         return (ctypes.c_void_p * len(ptrs))(*ptrs), len(ptrs)
